@@ -1,0 +1,78 @@
+"""Architecture-neutral description of a model: which parts each layer is made of,
+with which sizes, which tensors of the weight files they own, and in which order
+the layers run.
+
+A configuration class (one per architecture, see `registry.py`) turns the keys of
+its own config.json into a `ModelSpec`. Everything below the configuration (weight
+loading, random weights, the cache, the model runtime) reads only the spec, so none
+of it knows the architecture's name.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Optional
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """One part of a layer.
+
+    kind     name under which the part's class is registered (`parts.registry`)
+    params   the part's sizes and constants (everything it needs besides weights)
+    tensors  the part's own logical tensor names -> tensor names in the weight files
+    """
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+    tensors: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: an arrangement (`block`) of two norms, a mixer and a feed-forward."""
+    block: str
+    mixer_norm: PartSpec
+    mixer: PartSpec
+    feed_forward_norm: PartSpec
+    feed_forward: PartSpec
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One run of a layer.
+
+    layer       index into `ModelSpec.layers`; a layer may be named by several entries
+                (its weights are then shared, each entry has a cache of its own)
+    cache_from  index of an earlier schedule entry whose cache this run reads instead
+                of writing one of its own; None means its own cache
+    """
+    layer: int
+    cache_from: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    vocab_size: int
+    hidden_size: int
+    max_positions: int
+    embedding: PartSpec
+    layers: tuple
+    schedule: tuple
+    final_norm: PartSpec
+    head: PartSpec
+    stop_token_ids: tuple = ()
+
+    def validate(self) -> None:
+        if not self.schedule:
+            raise ValueError("model spec: the schedule is empty")
+        for pos, entry in enumerate(self.schedule):
+            if not 0 <= entry.layer < len(self.layers):
+                raise ValueError(f"model spec: schedule entry {pos} names layer {entry.layer}, "
+                                 f"but there are {len(self.layers)} layers")
+            if entry.cache_from is not None:
+                if not 0 <= entry.cache_from < pos:
+                    raise ValueError(f"model spec: schedule entry {pos} reads the cache of entry "
+                                     f"{entry.cache_from}, which does not run before it")
+                if self.schedule[entry.cache_from].cache_from is not None:
+                    raise ValueError(f"model spec: schedule entry {pos} reads the cache of entry "
+                                     f"{entry.cache_from}, which has no cache of its own")

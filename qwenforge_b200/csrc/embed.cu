@@ -1,0 +1,68 @@
+// Row gathers: token embedding into the float32 residual stream, and the gather of the
+// rows whose logits are wanted.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                    int vocab, int width, int* err) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    const bool bad = id < 0 || id >= vocab;
+    if (bad) {
+        if (threadIdx.x == 0) atomicOr(err, QF_ERR_TOKEN_RANGE);
+        id = 0;
+    }
+    const T* row = table + (size_t)id * width;
+    float* dst = out + (size_t)t * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = bad ? 0.f : Num<T>::to_f(row[c]);
+}
+
+// out[r] = hidden[rows[r]] (+ delta[rows[r]]): the residual stream with its pending update, at the wanted rows.
+template <typename T>
+__global__ void gather_rows_kernel(const float* __restrict__ hidden, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, float* __restrict__ out, int n_rows_in, int width,
+                                   int* err) {
+    const int r = blockIdx.x;
+    int src = rows[r];
+    const bool bad = src < 0 || src >= n_rows_in;
+    if (bad) {
+        if (threadIdx.x == 0) atomicOr(err, QF_ERR_ROW_RANGE);
+        src = 0;
+    }
+    const float* h = hidden + (size_t)src * width;
+    const T* d = delta ? delta + (size_t)src * width : nullptr;
+    float* dst = out + (size_t)r * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = h[c];
+        if (d) v += Num<T>::to_f(d[c]);
+        dst[c] = bad ? 0.f : v;
+    }
+}
+
+template <typename T>
+static int embed_launch(const int* ids, const void* table, float* out, int n_tokens, int vocab, int width, int* err,
+                        cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    embed_gather_kernel<T><<<n_tokens, 256, 0, stream>>>(ids, (const T*)table, out, vocab, width, err);
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+static int gather_launch(const float* hidden, const void* delta, const int* rows, float* out, int n_out, int n_in,
+                         int width, int* err, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    gather_rows_kernel<T><<<n_out, 256, 0, stream>>>(hidden, (const T*)delta, rows, out, n_in, width, err);
+    return (int)cudaGetLastError();
+}
+
+QF_EXPORT int qf_embed_gather(int is_bf16, const int* ids, const void* table, float* out, int n_tokens, int vocab,
+                              int width, int* err, cudaStream_t stream) {
+    return is_bf16 ? embed_launch<bf16>(ids, table, out, n_tokens, vocab, width, err, stream)
+                   : embed_launch<float>(ids, table, out, n_tokens, vocab, width, err, stream);
+}
+
+QF_EXPORT int qf_gather_rows(int is_bf16, const float* hidden, const void* delta, const int* rows, float* out,
+                             int n_out, int n_in, int width, int* err, cudaStream_t stream) {
+    return is_bf16 ? gather_launch<bf16>(hidden, delta, rows, out, n_out, n_in, width, err, stream)
+                   : gather_launch<float>(hidden, delta, rows, out, n_out, n_in, width, err, stream);
+}

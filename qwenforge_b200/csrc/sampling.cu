@@ -1,0 +1,93 @@
+// Next-token choice from float32 logits, one block per row.
+//   temperature <= 0 : argmax, the lowest id on ties
+//   temperature  > 0 : Gumbel-max,  argmax_i( logit_i / T - log(-log(u_i)) ), which draws i with
+//                      probability softmax(logits / T)_i. u_i comes from a counter-based integer hash of
+//                      (seed, sequence id, step, i), so a sequence's draws do not depend on the batch
+//                      it is in, on its row in that batch, or on how many steps other sequences took.
+#include <float.h>
+
+#include "common.cuh"
+
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16;
+    x *= 0x7FEB352Du;
+    x ^= x >> 15;
+    x *= 0x846CA68Bu;
+    x ^= x >> 16;
+    return x;
+}
+
+__device__ __forceinline__ uint32_t row_key(unsigned long long seed, long long seq_id, int step) {
+    uint32_t key = mix32((uint32_t)seed ^ 0x9E3779B9u);
+    key = mix32(key ^ (uint32_t)(seed >> 32));
+    key = mix32(key ^ (uint32_t)seq_id);
+    key = mix32(key ^ (uint32_t)((unsigned long long)seq_id >> 32) ^ 0x85EBCA6Bu);
+    key = mix32(key ^ (uint32_t)step);
+    return key;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride, float temperature,
+              unsigned long long seed, const long long* __restrict__ seq_ids, const int* __restrict__ steps,
+              int* __restrict__ out) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * row_stride;
+    const bool sample = temperature > 0.f;
+    const uint32_t key = sample ? row_key(seed, seq_ids[row], steps[row]) : 0u;
+    const float inv_t = sample ? 1.0f / temperature : 1.0f;
+    float bv = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float s = x[i];
+        if (sample) {
+            const uint32_t bits = mix32(key ^ mix32((uint32_t)i ^ 0x27D4EB2Fu));
+            const float u = ((float)(bits >> 9) + 0.5f) * (1.0f / 8388608.0f);
+            s = s * inv_t - logf(-logf(u));
+        }
+        if (s > bv || (s == bv && i < bi)) {
+            bv = s;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        best_v[warp] = bv;
+        best_i[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const int nwarps = blockDim.x >> 5;
+        bv = lane < nwarps ? best_v[lane] : -FLT_MAX;
+        bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+// logits: [rows][row_stride >= vocab] float32; seq_ids [rows] int64 and steps [rows] int32 are read only when sampling.
+QF_EXPORT int qf_sample(const float* logits, int rows, int vocab, long long row_stride, float temperature,
+                        unsigned long long seed, const long long* seq_ids, const int* steps, int* out,
+                        cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, row_stride, temperature, seed, seq_ids, steps, out);
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,88 @@
+"""What one step runs: a batch of sequences that either all start (whole prompts, unequal lengths)
+or all go on (one or more further tokens each), laid out without padding.
+
+Token t of the flat batch belongs to batch entry `tok_seq[t]` and stands at absolute position
+`tok_pos[t]` of its sequence; entry s owns tokens `cu_q[s] .. cu_q[s+1]-1` and the cache slot
+`slots[s]` (-1 marks a padding entry: it is computed, touches no cache and changes no result).
+All of it goes to the device in one copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepContext:
+    n_seqs: int
+    n_tokens: int
+    max_q_len: int
+    token_ids: torch.Tensor          # int32 [T]
+    tok_seq: torch.Tensor            # int32 [T]
+    tok_pos: torch.Tensor            # int32 [T]
+    slots: torch.Tensor              # int32 [n]
+    cu_q: torch.Tensor               # int32 [n + 1]
+    want_rows: Optional[torch.Tensor]  # int32 [R] flat token indices whose logits are wanted
+    err: torch.Tensor                # int32 [1] device error word
+    dtype: torch.dtype
+    attention: str = "auto"          # "auto": fastest kernel that takes the shape; "generic": the SIMT kernel
+    # host copies, for parts that plan on the host (absent when a captured graph replays the step)
+    host_slots: Optional[list] = None
+    host_starts: Optional[list] = None
+    host_q_lens: Optional[list] = None
+
+    @property
+    def is_decode(self) -> bool:
+        return self.max_q_len == 1
+
+
+def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]],
+                  err: torch.Tensor, dtype: torch.dtype, device, attention: str = "auto") -> StepContext:
+    """entries: (slot, start_position, token ids) per batch entry; want: per entry, the places among its
+    tokens whose logits are wanted (None: the last token of every entry with a real slot)."""
+    n = len(entries)
+    ids: list[int] = []
+    tok_seq: list[int] = []
+    tok_pos: list[int] = []
+    slots: list[int] = []
+    cu_q = [0]
+    rows: list[int] = []
+    for s, (slot, start, tokens) in enumerate(entries):
+        q = len(tokens)
+        if q == 0:
+            raise ValueError(f"step: entry {s} brings no tokens")
+        base = cu_q[-1]
+        ids.extend(int(t) for t in tokens)
+        tok_seq.extend([s] * q)
+        tok_pos.extend(range(start, start + q))
+        slots.append(slot)
+        cu_q.append(base + q)
+        if want is None:
+            if slot >= 0:
+                rows.append(base + q - 1)
+        else:
+            for place in want[s]:
+                if not 0 <= place < q:
+                    raise ValueError(f"step: entry {s} wants place {place} of {q} tokens")
+                rows.append(base + place)
+    total = cu_q[-1]
+    packed = torch.tensor(ids + tok_seq + tok_pos + slots + cu_q + rows, dtype=torch.int32)
+    if torch.device(device).type == "cuda":
+        packed = packed.pin_memory()
+    dev = packed.to(device, non_blocking=True)
+    o = 0
+
+    def take(count):
+        nonlocal o
+        piece = dev[o:o + count]
+        o += count
+        return piece
+
+    return StepContext(
+        n_seqs=n, n_tokens=total, max_q_len=max(len(e[2]) for e in entries),
+        token_ids=take(total), tok_seq=take(total), tok_pos=take(total), slots=take(n), cu_q=take(n + 1),
+        want_rows=take(len(rows)) if rows else None, err=err, dtype=dtype, attention=attention,
+        host_slots=list(slots), host_starts=[e[1] for e in entries], host_q_lens=[len(e[2]) for e in entries],
+    )

@@ -1,0 +1,234 @@
+"""Python entry of every CUDA kernel: argument checks, pointer passing, error codes.
+
+Each function checks dtypes, shapes and contiguity on the host, then calls the exported C
+function of its library with raw device pointers and the current stream. There is no other
+implementation behind these names: tensors that are not on a CUDA device are refused, and a
+missing or failing kernel library raises `KernelLibraryError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import library
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_LL = ctypes.c_longlong
+_ULL = ctypes.c_ulonglong
+_F = ctypes.c_float
+
+ERR_TOKEN_RANGE = 1
+ERR_NO_PAGE = 2
+ERR_ROW_RANGE = 4
+
+_ERROR_TEXT = {
+    ERR_TOKEN_RANGE: "a token id lies outside the embedding table",
+    ERR_NO_PAGE: "a position was read or written whose cache page is not held by its sequence",
+    ERR_ROW_RANGE: "a wanted row lies outside the step's tokens",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def describe_error_word(word: int) -> str:
+    return "; ".join(text for bit, text in _ERROR_TEXT.items() if word & bit) or f"unknown error word {word}"
+
+
+def require_cuda(device, what: str = "this operation") -> None:
+    """There is no CPU execution path: anything that is to compute must live on a CUDA device."""
+    if torch.device(device).type != "cuda":
+        raise KernelError(f"{what} is on {device}: this library computes on CUDA devices only "
+                          "(there is no CPU execution path)")
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available; this library has no CPU execution path")
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> _P:
+    return _P(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _P:
+    return _P(0) if t is None else _P(t.data_ptr())
+
+
+def _dev(name: str, t: torch.Tensor, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}: the kernels of this library run on CUDA devices only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+def _is_bf16(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 1
+    if dtype == torch.float32:
+        return 0
+    raise KernelError(f"activation dtype {dtype} is not supported (bfloat16 or float32)")
+
+
+class KvSiteArgs:
+    """What the kernels need to address one schedule entry's keys and values (see `cache.KvSite`)."""
+    __slots__ = ("storage", "table", "page_elems", "table_stride", "kv_heads", "head_dim")
+
+    def __init__(self, storage: torch.Tensor, table: torch.Tensor, kv_heads: int, head_dim: int):
+        # storage: [pages, 2, kv_heads, PAGE, head_dim]; table: [slots, max_pages] int32
+        self.storage = storage
+        self.table = table
+        self.page_elems = storage.stride(0)
+        self.table_stride = table.stride(0)
+        self.kv_heads = kv_heads
+        self.head_dim = head_dim
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+    """out[t] = float32(table[ids[t]]); ids int32 [T], table [V, W], out float32 [T, W]."""
+    _dev("ids", ids, torch.int32)
+    _dev("table", table)
+    _dev("out", out, torch.float32)
+    n, (vocab, width) = ids.numel(), table.shape
+    if out.shape != (n, width):
+        raise KernelError(f"embed_gather: out is {tuple(out.shape)}, expected {(n, width)}")
+    _check(library("embed").qf_embed_gather(_I(_is_bf16(table.dtype)), _ptr(ids), _ptr(table), _ptr(out), _I(n),
+                                            _I(vocab), _I(width), _ptr(err), _stream()), "embed_gather")
+
+
+def gather_rows(hidden: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, out: torch.Tensor,
+                err: torch.Tensor) -> None:
+    """out[r] = hidden[rows[r]] + delta[rows[r]] in float32; delta may be None."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("rows", rows, torch.int32)
+    _dev("out", out, torch.float32)
+    n_in, width = hidden.shape
+    is_bf16 = 0
+    if delta is not None:
+        _dev("delta", delta)
+        is_bf16 = _is_bf16(delta.dtype)
+        if delta.shape != hidden.shape:
+            raise KernelError("gather_rows: delta and hidden differ in shape")
+    if out.shape != (rows.numel(), width):
+        raise KernelError("gather_rows: out has the wrong shape")
+    _check(library("embed").qf_gather_rows(_I(is_bf16), _ptr(hidden), _ptr(delta), _ptr(rows), _ptr(out),
+                                           _I(rows.numel()), _I(n_in), _I(width), _ptr(err), _stream()), "gather_rows")
+
+
+def add_rms_norm(hidden: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                 out: torch.Tensor) -> None:
+    """hidden += delta (if given); out = rmsnorm(hidden) * weight. hidden float32 [R, W]; out, weight, delta share a dtype."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("weight", weight)
+    _dev("out", out, weight.dtype)
+    rows, width = hidden.shape
+    if weight.shape != (width,) or out.shape != hidden.shape:
+        raise KernelError("add_rms_norm: shapes of weight/out do not match hidden")
+    if delta is not None:
+        _dev("delta", delta, weight.dtype)
+        if delta.shape != hidden.shape:
+            raise KernelError("add_rms_norm: delta and hidden differ in shape")
+    _check(library("norm").qf_add_rms_norm(_I(_is_bf16(weight.dtype)), _ptr(hidden), _ptr(delta), _ptr(weight),
+                                           _ptr(out), _I(rows), _I(width), _F(eps), _stream()), "add_rms_norm")
+
+
+def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = x @ weight.T (+ bias) in true float32 (FFMA; no TF32). x [M, K], weight [N, K], out [M, N]; rows may be strided."""
+    for name, t in (("x", x), ("weight", weight), ("out", out)):
+        _dev(name, t, torch.float32, contiguous=False)
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_f32: {name} must be 2-d with unit inner stride")
+    (m, k), (n, k2) = x.shape, weight.shape
+    if k != k2 or out.shape != (m, n):
+        raise KernelError(f"gemm_f32: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not agree")
+    if bias is not None:
+        _dev("bias", bias, torch.float32)
+        if bias.shape != (n,):
+            raise KernelError("gemm_f32: bias has the wrong shape")
+    _check(library("gemm_f32").qf_gemm_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _I(m), _I(n), _I(k),
+                                           _I(x.stride(0)), _I(weight.stride(0)), _I(out.stride(0)), _stream()),
+           "gemm_f32")
+
+
+def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
+                     inv_freq: Optional[torch.Tensor], rot_dim: int, n_heads: int, q_out: torch.Tensor,
+                     site: KvSiteArgs, write_cache: bool, err: torch.Tensor) -> None:
+    """Rotate q and k heads of qkv [T, (NH + 2 KVH) D] by position, write q to q_out [T, NH D] and k, v into the cache."""
+    _dev("qkv", qkv)
+    _dev("q_out", q_out, qkv.dtype)
+    _dev("cache", site.storage, qkv.dtype)
+    _dev("tok_seq", tok_seq, torch.int32)
+    _dev("tok_pos", tok_pos, torch.int32)
+    _dev("slots", slots, torch.int32)
+    n = qkv.shape[0]
+    d, kvh = site.head_dim, site.kv_heads
+    if qkv.shape[1] != (n_heads + 2 * kvh) * d or q_out.shape != (n, n_heads * d):
+        raise KernelError("rope_cache_write: qkv/q_out widths do not match the head counts")
+    if inv_freq is not None:
+        _dev("inv_freq", inv_freq, torch.float32)
+        if inv_freq.numel() * 2 != rot_dim:
+            raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 frequencies")
+    _check(library("rope_cache").qf_rope_cache_write(
+        _I(_is_bf16(qkv.dtype)), _ptr(qkv), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
+        _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
+        _LL(site.page_elems), _I(site.table_stride), _I(kvh), _I(d), _I(1 if write_cache else 0), _I(n), _ptr(err),
+        _stream()), "rope_cache_write")
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
+                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
+                      window: int, err: torch.Tensor) -> None:
+    """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math)."""
+    _dev("q", q)
+    _dev("out", out, q.dtype)
+    _dev("cache", site.storage, q.dtype)
+    d = site.head_dim
+    if d > 256:
+        raise KernelError(f"attention_generic: head_dim {d} > 256 is not supported")
+    if q.shape[1] != n_heads * d or out.shape != q.shape:
+        raise KernelError("attention_generic: q/out widths do not match the head count")
+    _check(library("attention_generic").qf_attention_generic(
+        _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
+        _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
+        _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _stream()), "attention_generic")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _dev("gate_up", gate_up)
+    _dev("out", out, gate_up.dtype)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2):
+        raise KernelError("swiglu: out must be [rows, width / 2]")
+    _check(library("activation").qf_swiglu(_I(_is_bf16(gate_up.dtype)), _ptr(gate_up), _ptr(out), _I(rows),
+                                           _I(two_i // 2), _stream()), "swiglu")
+
+
+def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optional[torch.Tensor],
+           steps: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[r] = argmax (temperature <= 0) or a Gumbel-max draw keyed by (seed, seq_ids[r], steps[r])."""
+    _dev("logits", logits, torch.float32, contiguous=False)
+    _dev("out", out, torch.int32)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be 2-d with unit inner stride")
+    rows, vocab = logits.shape
+    if out.numel() != rows:
+        raise KernelError("sample: out must have one element per row")
+    if temperature > 0:
+        if seq_ids is None or steps is None:
+            raise KernelError("sample: sampling needs seq_ids and steps")
+        _dev("seq_ids", seq_ids, torch.int64)
+        _dev("steps", steps, torch.int32)
+        if seq_ids.numel() != rows or steps.numel() != rows:
+            raise KernelError("sample: seq_ids and steps must have one element per row")
+    _check(library("sampling").qf_sample(_ptr(logits), _I(rows), _I(vocab), _LL(logits.stride(0)),
+                                         _F(max(float(temperature), 0.0)), _ULL(seed & 0xFFFFFFFFFFFFFFFF),
+                                         _ptr(seq_ids), _ptr(steps), _ptr(out), _stream()), "sample")

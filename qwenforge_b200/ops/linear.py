@@ -1,0 +1,45 @@
+"""Dense projections: y = x W^T (+ b).
+
+float32 runs this library's own FFMA kernel (true 32-bit, a fixed order of additions for
+every output element). bfloat16 calls the cuBLAS matrix product through torch, the same
+library call the reference makes for its projections (student_engine.py:563, :664, :666,
+:727, :736), until the tensor-core kernel of this library covers the shape.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import kernels
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K], weight [N, K] -> [M, N]. `out_dtype=torch.float32` asks a bfloat16 product for
+    float32 results (accumulated in float32 and not rounded to bfloat16), as the logits need."""
+    if not x.is_cuda:
+        raise kernels.KernelError(f"linear: input on {x.device}; this library computes on CUDA devices only")
+    m, n = x.shape[0], weight.shape[0]
+    if x.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((m, n), device=x.device, dtype=torch.float32)
+        kernels.gemm_f32(x, weight, bias, out)
+        return out
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise kernels.KernelError(f"linear: dtypes {x.dtype} x {weight.dtype} are not supported")
+    if out_dtype == torch.float32:
+        result = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        if bias is not None:
+            result += bias.float()
+        if out is not None:
+            out.copy_(result)
+            return out
+        return result
+    if out is not None:
+        if bias is None:
+            torch.mm(x, weight.t(), out=out)
+        else:
+            torch.addmm(bias, x, weight.t(), out=out)
+        return out
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,105 @@
+"""Grouped-query softmax attention over the cache (student_engine.py:556-599, :795-832).
+
+  qkv = x Wqkv^T + bqkv            one product on the row-concatenated q, k, v weights (:505-520)
+  q, k rotated by position         the position part; fused into the cache-write kernel when it is rotary
+  k, v appended to the cache       at the token's own position of its own sequence
+  ctx = softmax(q k^T * scale) v   query head i reads kv head i // (NH / KVH); key j visible iff
+                                   max(0, p - window + 1) <= j <= p for a query at position p
+  out = ctx Wo^T (+ bo)
+
+Nothing here is specific to one model: head counts, head size, biases, scale, window and the
+position part all come from the spec. A step's queries attend to the cache only, which already
+holds the step's own keys: whole prompts, continuations and single tokens are the same code.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import KvNeed
+from .base import Mixer, TensorSpec
+from .registry import build_part, register_part
+
+
+class GqaAttention(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, out_bias, scale, window, position (PartSpec | None).
+    tensors: q_weight, k_weight, v_weight, o_weight (+ q_bias, k_bias, v_bias, o_bias when enabled)."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["num_heads"])
+        self.n_kv = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.out_bias = bool(p.get("out_bias", False))
+        self.scale = float(p.get("scale") or self.head_dim ** -0.5)
+        self.window = int(p.get("window") or 0)
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"gqa_attention: {self.n_heads} heads are not divisible by {self.n_kv} kv heads")
+        if self.head_dim > 256:
+            raise ValueError(f"gqa_attention: head_dim {self.head_dim} > 256 is not supported by the attention kernels")
+        self.position = build_part("position", p["position"]) if p.get("position") is not None else None
+        self.q_width = self.n_heads * self.head_dim
+        self.kv_width = self.n_kv * self.head_dim
+        self.qkv_weight = self.qkv_bias_t = self.o_weight = self.o_bias_t = None
+
+    def sub_parts(self):
+        return [self.position] if self.position is not None else []
+
+    def tensor_specs(self):
+        specs = [
+            TensorSpec(self.file_name("q_weight"), (self.q_width, self.hidden)),
+            TensorSpec(self.file_name("k_weight"), (self.kv_width, self.hidden)),
+            TensorSpec(self.file_name("v_weight"), (self.kv_width, self.hidden)),
+            TensorSpec(self.file_name("o_weight"), (self.hidden, self.q_width)),
+        ]
+        if self.qkv_bias:
+            specs += [
+                TensorSpec(self.file_name("q_bias"), (self.q_width,), init="bias"),
+                TensorSpec(self.file_name("k_bias"), (self.kv_width,), init="bias"),
+                TensorSpec(self.file_name("v_bias"), (self.kv_width,), init="bias"),
+            ]
+        if self.out_bias:
+            specs.append(TensorSpec(self.file_name("o_bias"), (self.hidden,), init="bias"))
+        return specs
+
+    def kernel_libraries(self, dtype):
+        libs = {"rope_cache", "attention_generic"}
+        if dtype == torch.float32:
+            libs.add("gemm_f32")
+        return libs
+
+    def cache_need(self):
+        return KvNeed(self.n_kv, self.head_dim, self.window)
+
+    def bind(self, tensors, dtype, device):
+        t = lambda logical: tensors[self.file_name(logical)]
+        self.qkv_weight = torch.cat((t("q_weight"), t("k_weight"), t("v_weight")), dim=0).contiguous()
+        if self.qkv_bias:
+            self.qkv_bias_t = torch.cat((t("q_bias"), t("k_bias"), t("v_bias")), dim=0).contiguous()
+        self.o_weight = t("o_weight")
+        if self.out_bias:
+            self.o_bias_t = t("o_bias")
+
+    def forward(self, x, ctx, site, writes_cache):
+        n = x.shape[0]
+        qkv = ops.linear(x, self.qkv_weight, self.qkv_bias_t)
+        rotary = self.position.fused_rotary() if self.position is not None else None
+        if self.position is not None and rotary is None:
+            q_view = qkv[:, :self.q_width].view(n, self.n_heads, self.head_dim)
+            k_view = qkv[:, self.q_width:self.q_width + self.kv_width].view(n, self.n_kv, self.head_dim)
+            self.position.apply(q_view, k_view, ctx)
+        inv_freq, rot_dim = rotary if rotary is not None else (None, 0)
+        q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
+        args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
+        ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args,
+                             writes_cache, ctx.err)
+        attended = torch.empty_like(q)
+        ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                              ctx.max_q_len, self.scale, self.window, ctx.err)
+        return ops.linear(attended, self.o_weight, self.o_bias_t)
+
+
+register_part("mixer", "gqa_attention", GqaAttention)

@@ -1,0 +1,60 @@
+"""Token embedding into the float32 residual stream (student_engine.py:690) and the output head
+(:733-736: logits = normed W^T, no bias; W is the embedding table when the model ties them, :359)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, TensorSpec
+from .registry import register_part
+
+
+class TokenEmbedding(Part):
+    """params: vocab_size, width. tensors: weight [vocab_size, width]."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vocab = int(self.params["vocab_size"])
+        self.width = int(self.params["width"])
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.file_name("weight"), (self.vocab, self.width))]
+
+    def kernel_libraries(self, dtype):
+        return {"embed"}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.file_name("weight")]
+
+    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
+        hidden = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
+        ops.embed_gather(token_ids, self.weight, hidden, ctx.err)
+        return hidden
+
+
+class LinearHead(Part):
+    """params: vocab_size, width, tied. tensors: weight [vocab_size, width] (the embedding's tensor when tied).
+    Returns float32 logits in both precisions."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vocab = int(self.params["vocab_size"])
+        self.width = int(self.params["width"])
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.file_name("weight"), (self.vocab, self.width))]
+
+    def kernel_libraries(self, dtype):
+        return {"gemm_f32"} if dtype == torch.float32 else set()
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors[self.file_name("weight")]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, None, out_dtype=torch.float32)
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "linear_head", LinearHead)

@@ -1,0 +1,6 @@
+from .loader import WeightsError, kept_dtype, load_weights, merge_specs, weight_files
+from .random_init import random_state, write_random_model
+from .safetensors_io import SafetensorsFile, save_safetensors
+
+__all__ = ["WeightsError", "kept_dtype", "load_weights", "merge_specs", "weight_files", "random_state",
+           "write_random_model", "SafetensorsFile", "save_safetensors"]
