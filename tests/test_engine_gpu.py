@@ -1,0 +1,253 @@
+"""The engine against the plain implementation on a GPU, in float32 and in bfloat16: each request alone and
+whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests end earlier,
+one batch after another so that slots and pages are used again; long decoding; the first tokens of a
+sequence; greedy generation through the entry point."""
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests.helpers import CONFIGS, SMALL_64, SMALL_128, assert_logits_close, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+ALL_CONFIGS = dict(CONFIGS, small_64=SMALL_64, small_128=SMALL_128)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for i, (name, config) in enumerate(ALL_CONFIGS.items()):
+        out[name] = make_model_dir(config, seed=i, folder=tmp_path_factory.mktemp(name))
+    return out
+
+
+_models = {}
+
+
+def get_model(folders, name, dtype, attention="auto"):
+    from qwenforge_b200.engine import Model
+    key = (name, dtype, attention)
+    if key not in _models:
+        _models[key] = Model.from_dir(folders[name][0], dtype, "cuda", attention)
+    return _models[key]
+
+
+def plain_logits(folders, name, tokens):
+    return plain.forward_logits(ALL_CONFIGS[name], folders[name][1], tokens)
+
+
+def lengths_for(name):
+    limit = ALL_CONFIGS[name]["max_position_embeddings"]
+    return [n for n in (1, 5, 33, 64, 65, 130, 200) if n <= limit]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ALL_CONFIGS))
+def test_whole_requests_alone(folders, name, dtype):
+    model = get_model(folders, name, dtype)
+    cache = model.new_cache(1024, 4)
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    for i, n in enumerate(lengths_for(name)):
+        tokens = random_tokens(vocab, n, 100 + i)
+        slot = cache.open()
+        logits = model.step(cache, [(slot, tokens)], want=[list(range(n))])
+        model.raise_on_kernel_error()
+        assert_logits_close(logits, plain_logits(folders, name, tokens), dtype, f"{name} whole {n}")
+        cache.close(slot)
+    assert cache.slots.n_free == cache.max_seqs and all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ALL_CONFIGS))
+def test_last_32_one_by_one(folders, name, dtype):
+    model = get_model(folders, name, dtype)
+    cache = model.new_cache(1024, 4)
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    for i, n in enumerate([40, 97, 130]):
+        tokens = random_tokens(vocab, n, 200 + i)
+        ref = plain_logits(folders, name, tokens)
+        slot = cache.open()
+        head = n - 32
+        got = [model.step(cache, [(slot, tokens[:head])], want=[list(range(head))])]
+        for t in range(head, n):
+            got.append(model.step(cache, [(slot, tokens[t:t + 1])]))
+        model.raise_on_kernel_error()
+        got = torch.cat(got)
+        assert_logits_close(got, ref, dtype, f"{name} last-32 of {n}")
+        if dtype == torch.float32:
+            # the same positions computed whole: equal beyond the plain comparison's tolerance
+            slot2 = cache.open()
+            whole = model.step(cache, [(slot2, tokens)], want=[list(range(n))])
+            assert float((whole - got).abs().max()) <= 1e-5 * float(ref.abs().max())
+            cache.close(slot2)
+        cache.close(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(ALL_CONFIGS))
+def test_unequal_batches_with_slot_reuse(folders, name, dtype):
+    """Three batches one after another in a cache with 4 slots and few pages; in each, prompts of unequal
+    lengths start together, then decode one token each; shorter requests end earlier."""
+    model = get_model(folders, name, dtype)
+    cache = model.new_cache(64 * 9, 4)
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    batches = [[(5, 9), (70, 3), (17, 12), (1, 6)], [(33, 4), (64, 8), (2, 2)], [(100, 5), (63, 7), (9, 1), (40, 10)]]
+    seed = 300
+    for batch in batches:
+        seqs = []
+        for prompt_len, n_decode in batch:
+            seed += 1
+            tokens = random_tokens(vocab, prompt_len + n_decode, seed)
+            seqs.append(dict(tokens=tokens, prompt=prompt_len, total=prompt_len + n_decode, fed=0, got=[],
+                             slot=cache.open()))
+        logits = model.step(cache, [(s["slot"], s["tokens"][:s["prompt"]]) for s in seqs],
+                            want=[list(range(s["prompt"])) for s in seqs])
+        offset = 0
+        for s in seqs:
+            s["got"].append(logits[offset:offset + s["prompt"]])
+            offset += s["prompt"]
+            s["fed"] = s["prompt"]
+        live = list(seqs)
+        while live:
+            logits = model.step(cache, [(s["slot"], [s["tokens"][s["fed"]]]) for s in live])
+            for row, s in enumerate(live):
+                s["got"].append(logits[row:row + 1])
+                s["fed"] += 1
+            for s in [s for s in live if s["fed"] == s["total"]]:
+                cache.close(s["slot"])
+            live = [s for s in live if s["fed"] < s["total"]]
+        model.raise_on_kernel_error()
+        for s in seqs:
+            assert_logits_close(torch.cat(s["got"]), plain_logits(folders, name, s["tokens"]), dtype,
+                                f"{name} batch request {s['prompt']}+{s['total'] - s['prompt']}")
+    assert cache.slots.n_free == cache.max_seqs and all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_entries_change_nothing(folders, dtype):
+    name = "tiny_b"
+    model = get_model(folders, name, dtype)
+    cache = model.new_cache(1024, 4)
+    tokens = random_tokens(ALL_CONFIGS[name]["vocab_size"], 20, 7)
+    a, b = cache.open(), cache.open()
+    alone = model.step(cache, [(a, tokens)], want=[list(range(20))])
+    padded = model.step(cache, [(-1, [0, 0, 0]), (b, tokens), (-1, [1])], want=[[], list(range(20)), []])
+    model.raise_on_kernel_error()
+    assert torch.equal(alone, padded) if dtype == torch.float32 else float((alone - padded).abs().max()) < 1e-2
+    d1 = model.step(cache, [(a, [5])])
+    d2 = model.step(cache, [(-1, [9]), (b, [5])], want=[[], [0]])
+    assert torch.equal(d1, d2) if dtype == torch.float32 else float((d1 - d2).abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_w", "small_64"])
+def test_long_decoding(folders, name, dtype):
+    """A short prompt, then token after token across several pages (and, for tiny_w, far beyond the window)."""
+    model = get_model(folders, name, dtype)
+    cache = model.new_cache(512, 2)
+    total = min(300, ALL_CONFIGS[name]["max_position_embeddings"])
+    tokens = random_tokens(ALL_CONFIGS[name]["vocab_size"], total, 11)
+    slot = cache.open()
+    got = [model.step(cache, [(slot, tokens[:3])], want=[[0, 1, 2]])]
+    for t in range(3, total):
+        got.append(model.step(cache, [(slot, [tokens[t]])]))
+    model.raise_on_kernel_error()
+    assert_logits_close(torch.cat(got), plain_logits(folders, name, tokens), dtype, f"{name} long decode")
+    if name == "tiny_w":  # pages that left the window were given back
+        group = [g for g in cache.kv_groups if g.need.window > 0][0]
+        assert group.pages_held(slot) <= (37 + 63) // 64 + 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens(folders, dtype):
+    """Positions 0, 1, 2 of a sequence fed one by one, and a one-token prompt in a batch."""
+    for name in CONFIGS:
+        model = get_model(folders, name, dtype)
+        cache = model.new_cache(512, 4)
+        tokens = random_tokens(ALL_CONFIGS[name]["vocab_size"], 4, 13)
+        slot, other = cache.open(), cache.open()
+        got = []
+        for t in range(4):
+            entries = [(slot, [tokens[t]])] + ([(other, [1, 2, 3])] if t == 0 else [(other, [4])])
+            got.append(model.step(cache, entries)[0:1])
+        model.raise_on_kernel_error()
+        assert_logits_close(torch.cat(got), plain_logits(folders, name, tokens), dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_far_key_among_hundreds(folders, dtype, tmp_path):
+    """Random weights spread attention thinly over hundreds of keys, which would hide a key that is lost or read
+    from the wrong place. Here the query and key projections are scaled up so that the softmax is sharp and single
+    keys decide the result; the plain implementation itself confirms that replacing ONE far token moves the last
+    position's logits by much more than the tolerance, so an engine that misreads that key cannot pass."""
+    import json
+
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.weights import save_safetensors
+    name = "tiny_a"
+    config = ALL_CONFIGS[name]
+    weights = {k: v.clone() for k, v in folders[name][1].items()}
+    for key in weights:
+        if any(part in key for part in ("q_proj", "k_proj")):
+            weights[key] *= 15.0
+    n = 330
+    tokens = random_tokens(config["vocab_size"], n, 17)
+    ref = plain.forward_logits(config, weights, tokens)
+    rel, abs_ = (2e-5, 2e-6) if dtype == torch.float32 else (4e-2, 2e-2)
+    bound = abs_ + rel * float(ref.abs().max())
+    sensitivity = 0.0
+    for far in range(0, 128, 4):
+        moved = list(tokens)
+        moved[far] = (moved[far] + 1) % config["vocab_size"]
+        sensitivity = max(sensitivity, float((plain.forward_logits(config, weights, moved)[-1] - ref[-1]).abs().max()))
+    assert sensitivity > 2.5 * bound, f"no far key matters enough ({sensitivity:.3e} vs {bound:.3e}) for this test to see a fault"
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    save_safetensors(tmp_path / "model.safetensors", weights)
+    model = Model.from_dir(tmp_path, dtype, "cuda")
+    cache = model.new_cache(512, 2)
+    slot = cache.open()
+    got = [model.step(cache, [(slot, tokens[:200])], want=[list(range(200))])]
+    for t in range(200, n):
+        got.append(model.step(cache, [(slot, [tokens[t]])]))
+    model.raise_on_kernel_error()
+    assert_logits_close(torch.cat(got), ref, dtype, "sharp attention over far keys")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_through_entry_point(folders, name, dtype):
+    from qwenforge_b200.engine import StudentEngine
+    engine = StudentEngine(str(folders[name][0]), device="cuda", dtype=dtype)
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 400 + n) for n in (5, 11, 17, 1, 30)]
+    got = engine.generate_ids(prompts, max_new_tokens=8, batch_size=3, ignore_eos=True)
+    assert [len(t) for t in got] == [8] * 5
+    if dtype == "float32":
+        want = [plain.greedy_generate(ALL_CONFIGS[name], folders[name][1], p, 8) for p in prompts]
+        assert got == want
+    else:  # bfloat16 may legitimately leave the greedy path at a near-tie: check every step's choice against the
+        for p, out in zip(prompts, got):  # plain logits of the sequence the engine actually produced
+            ref = plain.forward_logits(ALL_CONFIGS[name], folders[name][1], p + out)[len(p) - 1:-1]
+            for r, token in zip(ref, out):
+                assert float(r.max() - r[token]) <= 2e-2 + 4e-2 * float(r.abs().max())
+    # stop tokens: generation ends with the first stop token, which is kept
+    stop = got[0][2]
+    again = engine.generate_ids(prompts[:1], max_new_tokens=8, stop_token_ids=[stop])
+    assert again[0] == got[0][:got[0].index(stop) + 1]
+    # strings in, strings out, in the reference's contract
+    texts = engine.generate(["hello", "a b c"], max_new_tokens=4, batch_size=2)
+    assert isinstance(texts, list) and len(texts) == 2 and all(isinstance(t, str) and t for t in texts)
+    assert engine.generate([], 4) == [] and engine.generate(["x"], 0) == [""]
+
+
+def test_temperature_sampling_is_independent_of_batching(folders):
+    from qwenforge_b200.engine import StudentEngine
+    engine = StudentEngine(str(folders["tiny_a"][0]), device="cuda", dtype="float32", seed=5)
+    prompts = [random_tokens(256, n, 500 + n) for n in (4, 9, 2, 13)]
+    together = engine.generate_ids(prompts, 10, batch_size=4, temperature=0.9, ignore_eos=True)
+    apart = engine.generate_ids(prompts, 10, batch_size=1, temperature=0.9, ignore_eos=True)
+    assert together == apart
+    other_seed = engine.generate_ids(prompts, 10, batch_size=4, temperature=0.9, seed=6, ignore_eos=True)
+    assert other_seed != together
+    greedy = engine.generate_ids(prompts, 10, batch_size=4, ignore_eos=True)
+    assert greedy != together

@@ -1,0 +1,283 @@
+"""Each CUDA kernel alone against its plain reference (tests/kernel_refs.py), at sizes other than the
+engine's: odd widths, head sizes 16/24/40/64/128, group sizes 1/5/7/33, lengths around page and tile edges."""
+import math
+
+import pytest
+import torch
+
+from tests import kernel_refs as ref
+from tests.helpers import max_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 2e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from qwenforge_b200 import ops
+    return ops
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,width,n", [(37, 50, 9), (1000, 896, 33), (5, 7, 1)])
+def test_embed_gather(ops, dtype, vocab, width, n):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, width, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (n,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(n, width, device=DEV)
+    e = err_word()
+    ops.embed_gather(ids, table, out, e)
+    want = torch.empty_like(out)
+    ref.embed_gather(ids, table, want, None)
+    assert torch.equal(out, want) and int(e) == 0
+    ids[0] = vocab  # out of range: flagged, never read
+    ops.embed_gather(ids, table, out, e)
+    assert int(e) & ops.ERR_TOKEN_RANGE
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gather_rows(ops, dtype):
+    g = torch.Generator().manual_seed(1)
+    hidden = torch.randn(19, 70, generator=g).to(DEV)
+    delta = torch.randn(19, 70, generator=g).to(dtype).to(DEV)
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, 70, device=DEV)
+    e = err_word()
+    ops.gather_rows(hidden, delta, rows, out, e)
+    assert torch.equal(out, hidden[rows.long()] + delta[rows.long()].float()) and int(e) == 0
+    ops.gather_rows(hidden, None, rows, out, e)
+    assert torch.equal(out, hidden[rows.long()])
+    rows[1] = 19
+    ops.gather_rows(hidden, None, rows, out, e)
+    assert int(e) & ops.ERR_ROW_RANGE
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(5, 64, 1e-6), (3, 120, 1e-5), (17, 896, 1e-6), (2, 3584, 1e-6), (1, 1, 1e-3)])
+def test_add_rms_norm(ops, dtype, rows, width, eps):
+    g = torch.Generator().manual_seed(2)
+    hidden = (torch.randn(rows, width, generator=g) * 3).to(DEV)
+    delta = torch.randn(rows, width, generator=g).to(dtype).to(DEV)
+    weight = (1 + 0.1 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    for d in (delta, None):
+        h1, h2 = hidden.clone(), hidden.clone()
+        out = torch.empty(rows, width, dtype=dtype, device=DEV)
+        want = torch.empty_like(out)
+        ops.add_rms_norm(h1, d, weight, eps, out)
+        ref.add_rms_norm(h2, d, weight, eps, want)
+        assert torch.equal(h1, h2)  # the residual sum is a plain float32 addition
+        assert max_err(out, want) <= tol(dtype) * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (7, 200, 120), (70, 65, 33), (33, 1152, 896), (130, 50, 4864)])
+def test_gemm_f32(ops, m, n, k):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(m, k, generator=g).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(DEV)
+    b = torch.randn(n, generator=g).to(DEV)
+    out = torch.empty(m, n, device=DEV)
+    want = torch.empty_like(out)
+    ops.gemm_f32(x, w, b, out)
+    ref.gemm_f32(x, w, b, want)
+    assert max_err(out, want) <= 1e-6 * math.sqrt(k) * float(want.abs().max()) + 1e-6
+    # a row's result does not depend on the rows around it: bitwise
+    one = torch.empty(1, n, device=DEV)
+    ops.gemm_f32(x[m // 2:m // 2 + 1], w, b, one)
+    assert torch.equal(one[0], out[m // 2])
+    # strided input rows
+    wide = torch.randn(m, k + 5, generator=g).to(DEV)
+    ops.gemm_f32(wide[:, :k], w, None, out)
+    ref.gemm_f32(wide[:, :k], w, None, want)
+    assert max_err(out, want) <= 1e-6 * math.sqrt(k) * float(want.abs().max()) + 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,inter", [(3, 200), (17, 4864), (1, 1)])
+def test_swiglu(ops, dtype, rows, inter):
+    g = torch.Generator().manual_seed(4)
+    gu = (torch.randn(rows, 2 * inter, generator=g) * 2).to(dtype).to(DEV)
+    out = torch.empty(rows, inter, dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    ops.swiglu(gu, out)
+    ref.swiglu(gu, want)
+    assert max_err(out, want) <= tol(dtype) * max(1.0, float(want.float().abs().max()))
+
+
+class FakeSite:
+    """A paged key/value store like the cache's, with pages handed out in a scrambled order."""
+
+    def __init__(self, n_slots, max_len, kvh, d, dtype, seed=0):
+        per_seq = (max_len + 63) // 64
+        n_pages = n_slots * per_seq + 3
+        g = torch.Generator().manual_seed(seed)
+        self.storage = torch.zeros(n_pages, 2, kvh, 64, d, dtype=dtype, device=DEV)
+        perm = torch.randperm(n_pages, generator=g)[: n_slots * per_seq].to(torch.int32)
+        self.table = perm.view(n_slots, per_seq).to(DEV)
+        self.kv_heads, self.head_dim = kvh, d
+
+
+def fill_site(site, slot, length, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    kvh, d = site.kv_heads, site.head_dim
+    k = torch.randn(length, kvh, d, generator=g).to(dtype).to(DEV)
+    v = torch.randn(length, kvh, d, generator=g).to(dtype).to(DEV)
+    pos = torch.arange(length, device=DEV)
+    pages = site.table[slot, pos // 64].long()
+    site.storage[pages, 0, :, pos % 64, :] = k
+    site.storage[pages, 1, :, pos % 64, :] = v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,d,rot", [(4, 2, 16, 16), (5, 1, 24, 24), (7, 1, 64, 64), (4, 2, 128, 64), (3, 3, 40, 0)])
+def test_rope_cache_write(ops, dtype, nh, kvh, d, rot):
+    g = torch.Generator().manual_seed(5)
+    q_lens, starts, slots = [3, 1, 70], [0, 63, 60], [2, -1, 0]
+    site_a = FakeSite(3, 256, kvh, d, dtype)
+    site_b = FakeSite(3, 256, kvh, d, dtype)
+    site_b.table = site_a.table
+    n = sum(q_lens)
+    qkv = torch.randn(n, (nh + 2 * kvh) * d, generator=g).to(dtype).to(DEV)
+    tok_seq = torch.tensor(sum(([i] * q for i, q in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(sum((list(range(s, s + q)) for s, q in zip(starts, q_lens)), []), dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    inv_freq = None
+    if rot:
+        inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    q1 = torch.empty(n, nh * d, dtype=dtype, device=DEV)
+    q2 = torch.empty_like(q1)
+    e = err_word()
+    a = ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d)
+    ops.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, rot, nh, q1, a, True, e)
+    ref.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, rot, nh, q2, site_b, True, None)
+    assert int(e) == 0
+    assert max_err(q1, q2) <= tol(dtype) * 5
+    assert max_err(site_a.storage, site_b.storage) <= tol(dtype) * 5
+    # without the write flag the cache stays as it is
+    before = site_a.storage.clone()
+    ops.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, rot, nh, q1, a, False, e)
+    assert torch.equal(before, site_a.storage)
+
+
+def run_attention(ops, fn_name, dtype, nh, kvh, d, q_lens, starts, window, slots=None, seed=6):
+    n_seqs = len(q_lens)
+    slots = slots if slots is not None else list(range(n_seqs))[::-1]
+    max_len = max(s + q for s, q in zip(starts, q_lens))
+    site = FakeSite(n_seqs, max_len, kvh, d, dtype, seed)
+    for slot, s, q in zip(slots, starts, q_lens):
+        if slot >= 0:
+            fill_site(site, slot, s + q, seed + slot, dtype)
+    g = torch.Generator().manual_seed(seed)
+    n = sum(q_lens)
+    q = torch.randn(n, nh * d, generator=g).to(dtype).to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(sum((list(range(s, s + ql)) for s, ql in zip(starts, q_lens)), []), dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    out = torch.full((n, nh * d), 7.0, dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    e = err_word()
+    args = ops.KvSiteArgs(site.storage, site.table, kvh, d)
+    scale = d ** -0.5
+    getattr(ops, fn_name)(q, out, cu, tok_pos, slots_t, args, nh, n_seqs, max(q_lens), scale, window, e)
+    ref.attention_generic(q, want, cu, tok_pos, slots_t, site, nh, n_seqs, max(q_lens), scale, window, None)
+    assert int(e) == 0
+    return out, want
+
+
+ATTN_SHAPES = [
+    # nh, kvh, d, q_lens, starts, window
+    (4, 2, 16, [5, 11, 17], [0, 0, 0], 0),
+    (5, 1, 24, [1, 7, 19, 33], [0, 0, 0, 0], 0),
+    (5, 1, 24, [1, 1, 1], [0, 63, 200], 0),              # decode at page edges
+    (14, 2, 64, [130, 3], [0, 125], 0),                  # a continuation that crosses a page
+    (4, 4, 40, [70], [10], 0),                           # no grouping, odd head size
+    (33, 1, 16, [9, 2], [5, 0], 0),                      # a group larger than a block's rows
+    (6, 3, 16, [100, 1, 40], [0, 90, 30], 37),           # window, not a multiple of anything
+    (8, 2, 128, [65, 1], [0, 300], 64),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,d,q_lens,starts,window", ATTN_SHAPES)
+def test_attention_generic(ops, dtype, nh, kvh, d, q_lens, starts, window):
+    out, want = run_attention(ops, "attention_generic", dtype, nh, kvh, d, q_lens, starts, window)
+    assert max_err(out, want) <= tol(dtype) * 3
+
+
+def test_attention_generic_padding_entry(ops):
+    out, want = run_attention(ops, "attention_generic", torch.float32, 4, 2, 16, [3, 2, 4], [0, 0, 7], 0, slots=[1, -1, 0])
+    assert max_err(out, want) <= 1e-5
+    assert float(out[3:5].abs().max()) == 0.0
+
+
+def test_attention_generic_far_key_stands_out(ops):
+    """One key far back among hundreds is made to dominate: the output must be that key's value."""
+    dtype, nh, kvh, d, length = torch.float32, 2, 1, 32, 700
+    site = FakeSite(1, length, kvh, d, dtype, 9)
+    fill_site(site, 0, length, 3, dtype)
+    far = 17
+    page, off = int(site.table[0, far // 64]), far % 64
+    site.storage[page, 0, 0, off] = 0
+    site.storage[page, 0, 0, off, 0] = 50.0
+    q = torch.zeros(1, nh * d, device=DEV)
+    q[0, 0] = 40.0
+    q[0, d] = 40.0
+    out = torch.empty_like(q)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([length - 1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0], dtype=torch.int32, device=DEV)
+    e = err_word()
+    ops.attention_generic(q, out, cu, pos, slots, ops.KvSiteArgs(site.storage, site.table, kvh, d), nh, 1, 1,
+                          d ** -0.5, 0, e)
+    value = site.storage[page, 1, 0, off]
+    assert max_err(out[0, :d], value) < 1e-4 and max_err(out[0, d:], value) < 1e-4
+    # with a window that excludes it, it must vanish
+    ops.attention_generic(q, out, cu, pos, slots, ops.KvSiteArgs(site.storage, site.table, kvh, d), nh, 1, 1,
+                          d ** -0.5, length - far - 1, e)
+    assert max_err(out[0, :d], value) > 1e-2
+
+
+@pytest.mark.parametrize("vocab", [5, 384, 151936])
+def test_sample_greedy_and_gumbel(ops, vocab):
+    from tests import plain_qwen2 as plain
+    g = torch.Generator().manual_seed(8)
+    rows = 6
+    logits = (torch.randn(rows, vocab + 3, generator=g) * 3).to(DEV)[:, :vocab]  # strided rows
+    logits[2, 1] = logits[2, vocab - 1] = 99.0  # a tie: the lowest id wins
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 0.0, 0, None, None, out)
+    best = logits.argmax(-1).tolist()
+    assert [t for r, t in enumerate(out.tolist()) if r != 2] == [t for r, t in enumerate(best) if r != 2]
+    assert out[2].item() == 1
+    seq_ids = torch.tensor([3, 1 << 40, 5, 3, 9, 0], dtype=torch.int64, device=DEV)
+    steps = torch.tensor([0, 1, 2, 0, 7, 4], dtype=torch.int32, device=DEV)
+    ops.sample(logits, 0.7, 1234, seq_ids, steps, out)
+    n_check = rows if vocab < 100000 else 2
+    for r in range(n_check):
+        token, scores = plain.sample_token(logits[r].cpu(), 0.7, 1234, int(seq_ids[r]), int(steps[r]))
+        # the kernel's logarithms are float32: accept its choice if its score is within rounding of the best
+        assert float(scores[token] - scores[int(out[r])]) <= 1e-4, (r, token, int(out[r]))
+    # the draw of a row depends on (seed, sequence, step) only: row 3 has the key of row 0 but other logits
+    alone = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops.sample(logits[0:1], 0.7, 1234, seq_ids[0:1], steps[0:1], alone)
+    assert alone.item() == out[0].item()
+
+
+def test_sample_distribution(ops):
+    """Over many steps the draws follow softmax(logits / T)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]], device=DEV).repeat(4000, 1)
+    seq_ids = torch.zeros(4000, dtype=torch.int64, device=DEV)
+    steps = torch.arange(4000, dtype=torch.int32, device=DEV)
+    out = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 1.3, 77, seq_ids, steps, out)
+    freq = torch.bincount(out.long().cpu(), minlength=5).double() / 4000
+    want = torch.softmax(logits[0].double().cpu() / 1.3, -1)
+    assert float((freq - want).abs().max()) < 0.03
