@@ -1,0 +1,123 @@
+"""The step function, the cache and the loops above them on the CPU, with every CUDA kernel replaced by its plain
+reference (tests/kernel_refs.py, through the `reference_kernels` fixture). This checks the host side: the batch
+layout, positions, page tables, slot reuse, the order of the schedule. The kernels themselves are checked on a GPU."""
+import io
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests.helpers import CONFIGS, make_model_dir, max_err, random_tokens
+
+
+def build(config, tmp_path, seed=0):
+    from qwenforge_b200.engine import Model
+    folder, weights = make_model_dir(config, seed, tmp_path)
+    return Model.from_dir(folder, "float32", "cpu"), weights, folder
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_every_cut_gives_the_plain_logits(reference_kernels, name, tmp_path):
+    config = CONFIGS[name]
+    model, weights, _ = build(config, tmp_path)
+    cache = model.new_cache(64 * 8, 3)
+    vocab = config["vocab_size"]
+    seqs = [random_tokens(vocab, n, 10 + n) for n in (70, 5, 33, 101, 64)]
+    refs = [plain.forward_logits(config, weights, s) for s in seqs]
+    for round_ in range(2):                               # the second round runs in slots and pages used before
+        for begin in range(0, len(seqs), 3):
+            batch = list(range(begin, min(begin + 3, len(seqs))))
+            slots = {i: cache.open() for i in batch}
+            heads = {i: max(1, len(seqs[i]) - 4 - i) for i in batch}
+            logits = model.step(cache, [(slots[i], seqs[i][:heads[i]]) for i in batch],
+                                want=[list(range(heads[i])) for i in batch])
+            got = {i: [] for i in batch}
+            o = 0
+            for i in batch:
+                got[i].append(logits[o:o + heads[i]])
+                o += heads[i]
+            fed = dict(heads)
+            live = [i for i in batch if fed[i] < len(seqs[i])]
+            while live:
+                logits = model.step(cache, [(slots[i], [seqs[i][fed[i]]]) for i in live])
+                for row, i in enumerate(live):
+                    got[i].append(logits[row:row + 1])
+                    fed[i] += 1
+                for i in [i for i in live if fed[i] == len(seqs[i])]:
+                    cache.close(slots.pop(i))
+                live = [i for i in live if fed[i] < len(seqs[i])]
+            for i in list(slots):
+                cache.close(slots.pop(i))
+            for i in batch:
+                assert max_err(torch.cat(got[i]), refs[i]) < 2e-6, (name, round_, i)
+    assert cache.slots.n_free == cache.max_seqs and all(g.pages.n_free == g.pages.n_pages for g in cache.kv_groups)
+
+
+def test_step_refuses_what_it_cannot_hold(reference_kernels, tmp_path):
+    from qwenforge_b200.cache import CacheFull
+    config = CONFIGS["tiny_a"]
+    model, _, _ = build(config, tmp_path)
+    cache = model.new_cache(128, 2)
+    slot = cache.open()
+    with pytest.raises(CacheFull):
+        model.step(cache, [(slot, [1] * 129)])
+    assert cache.lengths[slot] == 0 and cache.kv_groups[0].pages.n_free == 2   # nothing half-done
+    with pytest.raises(ValueError, match="exceeds model limit"):
+        big = model.new_cache(1024, 2)
+        model.step(big, [(big.open(), [1] * 385)])
+    with pytest.raises(ValueError, match="twice"):
+        model.step(cache, [(slot, [1]), (slot, [2])])
+    with pytest.raises(ValueError, match="brings no tokens"):
+        model.step(cache, [(slot, [])])
+
+
+def test_generation_through_the_entry_point(reference_kernels, tmp_path, monkeypatch):
+    from qwenforge_b200.engine import StudentEngine
+    config = CONFIGS["tiny_b"]
+    folder, weights = make_model_dir(config, 4, tmp_path)
+    engine = StudentEngine(str(folder), device="cpu", dtype="float32")
+    prompts = [random_tokens(config["vocab_size"], n, 20 + n) for n in (3, 9, 1, 14)]
+    got = engine.generate_ids(prompts, max_new_tokens=[5, 2, 6, 4], batch_size=3, ignore_eos=True)
+    want = [plain.greedy_generate(config, weights, p, b) for p, b in zip(prompts, (5, 2, 6, 4))]
+    assert got == want
+    assert not engine.cache.live_slots()
+    sampled = engine.generate_ids(prompts, 5, batch_size=2, temperature=0.8, seed=3, ignore_eos=True)
+    again = engine.generate_ids(prompts, 5, batch_size=4, temperature=0.8, seed=3, ignore_eos=True)
+    assert sampled == again and sampled != engine.generate_ids(prompts, 5, batch_size=4, ignore_eos=True)
+    with pytest.raises(TypeError, match="list\\[str\\]"):
+        engine.generate("not a list", 3)
+    texts = engine.generate(["ab", "c"], 3, batch_size=2, suite_name="ignored")
+    assert len(texts) == 2 and all(isinstance(t, str) and len(t) == 3 for t in texts)
+
+
+def test_replay_in_process(reference_kernels, tmp_path):
+    from qwenforge_b200.engine.replay import replay
+    config = CONFIGS["tiny_a"]
+    model, weights, _ = build(config, tmp_path / "m")
+    cache = model.new_cache(128, 2)
+    a, b = random_tokens(256, 20, 1), random_tokens(256, 7, 2)
+    steps = [dict(step=0, entries=[dict(id="a", tokens=a[:19], want=[0, 18]), dict(id="b", tokens=b[:6], want=[])], end=[]),
+             dict(step=1, entries=[dict(id="a", tokens=a[19:], want=[0]), dict(id="b", tokens=b[6:], want=[0])], end=["a", "b"]),
+             dict(step=2, entries=[dict(id="c", tokens=b, want=[6])], end=["c"])]
+    out = tmp_path / "o"
+    out.mkdir()
+    said = []
+    replay(model, cache, io.StringIO("".join(json.dumps(s) + "\n" for s in steps)), out, report=said.append)
+    assert said == ["done 0", "done 1", "done 2"]
+    ra, rb = plain.forward_logits(config, weights, a), plain.forward_logits(config, weights, b)
+    read = lambda n: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 256).copy())
+    assert max_err(read(0), ra[[0, 18]]) < 2e-6
+    assert max_err(read(1), torch.stack((ra[19], rb[6]))) < 2e-6
+    assert max_err(read(2), rb[6:7]) < 2e-6
+    assert not cache.live_slots()
+
+
+def test_no_cpu_path_in_the_package(tmp_path):
+    """Without the fixture the package refuses to compute anywhere but on a CUDA device."""
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.ops import KernelError
+    folder, _ = make_model_dir(CONFIGS["tiny_a"], 0, tmp_path)
+    with pytest.raises(KernelError, match="no CPU execution path|CUDA devices only"):
+        Model.from_dir(folder, "float32", "cpu")

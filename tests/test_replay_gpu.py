@@ -1,0 +1,102 @@
+"""bin/trace_run as a user runs it: a subprocess, JSON steps on standard input, logits files out. The same requests
+are replayed whole, with the last 32 tokens one by one, and in unequal batches whose requests end at different steps."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_qwen2 as plain
+from tests.helpers import TINY_A, TINY_W, assert_logits_close, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def run_trace(model_dir, dtype, steps, out_dir, max_tokens):
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+                           "--out", str(out_dir), "--max-tokens", str(max_tokens)],
+                          input=text, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.splitlines() if line.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    return done
+
+
+def read(out_dir, step, vocab):
+    data = np.fromfile(Path(out_dir) / f"{step}.f32", dtype="<f4")
+    return torch.from_numpy(data.reshape(-1, vocab).copy())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("config", [TINY_A, TINY_W], ids=["tiny_a", "tiny_w"])
+def test_three_ways_of_cutting(config, dtype, tmp_path):
+    folder, weights = make_model_dir(config, 2, tmp_path / "model")
+    vocab = config["vocab_size"]
+    torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+    requests = {f"r{i}": random_tokens(vocab, n, 50 + i) for i, n in enumerate((40, 97, 130, 64, 33))}
+    refs = {k: plain.forward_logits(config, weights, v) for k, v in requests.items()}
+
+    # 1. each request alone and whole
+    steps = [dict(step=i, entries=[dict(id=k, tokens=v, want=list(range(len(v))))], end=[k])
+             for i, (k, v) in enumerate(requests.items())]
+    run_trace(folder, dtype, steps, tmp_path / "whole", max_tokens=192)
+    for i, k in enumerate(requests):
+        assert_logits_close(read(tmp_path / "whole", i, vocab), refs[k], torch_dtype, f"whole {k}")
+
+    # 2. all but the last 32 tokens in one step, then one by one; a step that wants nothing writes no file
+    k, v = "r2", requests["r2"]
+    head = len(v) - 32
+    steps = [dict(step=0, entries=[dict(id=k, tokens=v[:head], want=[])], end=[])]
+    steps += [dict(step=1 + t, entries=[dict(id=k, tokens=[v[head + t]], want=[0])], end=[k] if t == 31 else [])
+              for t in range(32)]
+    run_trace(folder, dtype, steps, tmp_path / "tail", max_tokens=192)
+    assert not (tmp_path / "tail" / "0.f32").exists()
+    tail = torch.cat([read(tmp_path / "tail", 1 + t, vocab) for t in range(32)])
+    assert_logits_close(tail, refs[k][head:], torch_dtype, "last 32 one by one")
+
+    # 3. two batches of unequal lengths, one after the other, in a cache too small for both: prompts minus 8 tokens
+    #    start together, then one token each; shorter requests end earlier
+    steps, n = [], 0
+    collected = {k: [] for k in requests}
+    plan = []
+    for batch in (["r0", "r1", "r2"], ["r3", "r4", "r1"]):
+        heads = {k: len(requests[k]) - 8 - (3 if k == "r0" else 0) for k in batch}
+        steps.append(dict(step=n, entries=[dict(id=f"{k}@{n}", tokens=requests[k][:heads[k]], want=list(range(heads[k])))
+                                           for k in batch], end=[]))
+        plan.append((n, [(k, heads[k]) for k in batch]))
+        first = n
+        n += 1
+        fed = dict(heads)
+        while any(fed[k] < len(requests[k]) for k in batch):
+            live = [k for k in batch if fed[k] < len(requests[k])]
+            entries = [dict(id=f"{k}@{first}", tokens=[requests[k][fed[k]]], want=[0]) for k in live]
+            for k in live:
+                fed[k] += 1
+            steps.append(dict(step=n, entries=entries, end=[f"{k}@{first}" for k in live if fed[k] == len(requests[k])]))
+            plan.append((n, [(k, 1) for k in live]))
+            n += 1
+    run_trace(folder, dtype, steps, tmp_path / "batches", max_tokens=64 * 6)
+    for step, parts in plan:
+        data = read(tmp_path / "batches", step, vocab)
+        o = 0
+        for k, count in parts:
+            collected[k].append(data[o:o + count])
+            o += count
+        assert o == data.shape[0]
+    for k in requests:
+        got = torch.cat(collected[k])
+        want = torch.cat([refs[k]] * (got.shape[0] // refs[k].shape[0]))
+        assert_logits_close(got, want, torch_dtype, f"batched {k}")
+
+
+def test_too_small_a_cache_fails_loudly(tmp_path):
+    folder, _ = make_model_dir(TINY_A, 2, tmp_path / "model")
+    text = json.dumps(dict(step=0, entries=[dict(id="a", tokens=list(range(70)), want=[0])], end=[])) + "\n"
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                           "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=text, capture_output=True,
+                          text=True, timeout=600)
+    assert done.returncode != 0 and "CacheFull" in done.stderr
