@@ -1,0 +1,245 @@
+"""Measurement of qwenforge_b200 on one B200: decode tokens per second of a random-weight Qwen2.5-0.5B
+(batch 8, context 4096 by default), with the prefill rate at 2,048 tokens, the decode step's HBM roofline,
+decode at batch 1 and 64, and the same decode rate end to end through the Python entry point.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+One decode step = one token for every sequence of the batch. The K timed steps are the last K steps before
+the context length is reached, so the cache is read at (almost) its full length. Timed with CUDA events on
+the launching stream; the step's operands (about 1 GB of weights plus the cache) are far larger than the
+126 MB L2, so no flush is needed between steps. Prints ONE JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=256)
+    p.add_argument("--warmup", type=int, default=16)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--preset", default="qwen2.5-0.5b")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=4096)
+    p.add_argument("--prefill-tokens", type=int, default=2048)
+    p.add_argument("--layers", type=int, default=None, help="run fewer layers than the preset has (both numbers are reported)")
+    p.add_argument("--dtype", default="bfloat16")
+    p.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
+    return p.parse_args()
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": float(data.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])),
+                "bf16_tflops": float(data.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])), "source": "measured"}
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.proc.wait()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(mhz)}
+
+
+def model_numbers(config, layers_run):
+    """Bytes and FLOPs of one step from the configuration (bf16 weights, bf16 cache)."""
+    h, i, d = config.hidden_size, config.intermediate_size, config.head_dim
+    nh, kvh, v = config.num_attention_heads, config.num_key_value_heads, config.vocab_size
+    per_layer = (nh + 2 * kvh) * d * h + (nh + 2 * kvh) * d + nh * d * h + 3 * i * h + 2 * h
+    head = v * h
+    weight_bytes = 2 * (layers_run * per_layer + head + h)
+    kv_bytes_per_token = layers_run * 2 * kvh * d * 2
+    linear_flops_per_token = 2 * layers_run * ((nh + 2 * kvh) * d * h + nh * d * h + 3 * i * h)
+    return dict(weight_bytes=weight_bytes, kv_bytes_per_token=kv_bytes_per_token,
+                linear_flops_per_token=linear_flops_per_token, head_flops_per_row=2 * head,
+                attn_flops=lambda t: layers_run * 4 * nh * d * t * (t + 1) // 2)
+
+
+def timed_decode(model, cache, batch, context, steps, warmup, vocab, torch, sampler=None):
+    """Prefill `batch` prompts so that warmup + steps decode steps end at `context`; returns ms per timed step."""
+    from qwenforge_b200.sampling import Sampler
+    sampler = sampler or Sampler()
+    prompt_len = context - steps - warmup
+    g = torch.Generator().manual_seed(1234)
+    slots = [cache.open() for _ in range(batch)]
+    cache.reserve([(s, context) for s in slots])
+    tokens = None
+    for begin in range(0, batch, 8):  # prefill in chunks of 8 prompts to bound activation memory
+        chunk = slots[begin:begin + 8]
+        prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in chunk]
+        logits = model.step(cache, list(zip(chunk, prompts)))
+        first = sampler(logits).tolist()
+        tokens = first if tokens is None else tokens + first
+
+    def one_step(tokens):
+        logits = model.step(cache, [(s, [t]) for s, t in zip(slots, tokens)])
+        return sampler(logits).tolist()
+
+    for _ in range(warmup):
+        tokens = one_step(tokens)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        tokens = one_step(tokens)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    model.raise_on_kernel_error()
+    for s in slots:
+        cache.close(s)
+    return ms
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference has no setup.py or pyproject.toml, so pip cannot install it into baseline/_ref; "
+                          "its entry point also needs the Qwen2.5-0.5B-Instruct tokenizer and weights, which are not on "
+                          "the box (no network)"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this library runs on ONE GPU; --gpus N > 1 is not supported")
+        return 2
+
+    import torch
+
+    from qwenforge_b200.config import preset_config, preset_dict
+    from qwenforge_b200.engine import Model, StudentEngine
+    from qwenforge_b200.ops import kernels
+    from qwenforge_b200.weights import write_random_model
+
+    pk = peaks()
+    full = preset_config(args.preset)
+    layers_cfg = full.num_hidden_layers
+    layers_run = args.layers or layers_cfg
+    config = preset_config(args.preset, num_hidden_layers=layers_run)
+    numbers = model_numbers(config, layers_run)
+    steps, warmup, batch, context = args.steps, max(args.warmup, 3), args.batch, args.context
+
+    with tempfile.TemporaryDirectory(prefix="qf_bench_") as folder, torch.inference_mode():
+        write_random_model(config, seed=0, out_dir=folder, store_dtype=torch.bfloat16)
+        model = Model.from_dir(folder, args.dtype, "cuda:0")
+        vocab = config.vocab_size
+        cache = model.new_cache(max(batch, 64 if not args.no_points else batch) * context, 64)
+
+        # ---- prefill of 2,048 tokens, one sequence
+        g = torch.Generator().manual_seed(7)
+        prompt = torch.randint(0, vocab, (args.prefill_tokens,), generator=g).tolist()
+        times = []
+        for rep in range(5):
+            slot = cache.open()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            model.step(cache, [(slot, prompt)])
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            cache.close(slot)
+        prefill_ms = sorted(times[2:])[len(times[2:]) // 2]
+        t = args.prefill_tokens
+        prefill_flops = numbers["linear_flops_per_token"] * t + numbers["attn_flops"](t) + numbers["head_flops_per_row"]
+        prefill = {"value": round(t / prefill_ms * 1e3, 1), "tokens": t, "ms": round(prefill_ms, 3),
+                   "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+        # ---- the headline: decode at the default batch, with clocks sampled meanwhile
+        launches_before = kernels.launches
+        with ClockSampler() as clocks:
+            ms = timed_decode(model, cache, batch, context, steps, warmup, vocab, torch)
+        launches = kernels.launches - launches_before
+        gpu_launches = int(round(launches * steps / (steps + warmup + 1)))  # the timed steps' share
+        value = batch * 1e3 / ms
+        mean_ctx = context - steps / 2
+        step_bytes = numbers["weight_bytes"] + batch * mean_ctx * numbers["kv_bytes_per_token"]
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
+
+        points, e2e = {}, None
+        if not args.no_points:
+            for b in (1, 64):
+                k = min(steps, 128)
+                points[f"decode_b{b}"] = round(b * 1e3 / timed_decode(model, cache, b, context, k, 4, vocab, torch), 1)
+            # ---- end to end through the entry point: host token ids in, host token ids out, every step
+            del cache
+            engine = StudentEngine(folder, device="cuda:0", dtype=args.dtype)
+            k = min(steps, 128)
+            prompts = [torch.randint(0, vocab, (context - k - 1,), generator=g).tolist() for _ in range(batch)]
+            engine.generate_ids(prompts[:1], 4, ignore_eos=True)  # warm-up
+            engine.generate_ids(prompts, k + 1, batch_size=batch, ignore_eos=True)
+            loop = engine.last_loop
+            e2e = {"value": round(loop.decoded_tokens / loop.decode_seconds, 1), "unit": "tokens/s",
+                   "h2d_bytes_per_step": 4 * (6 * batch + 1), "d2h_bytes_per_step": 4 * (batch + 1)}
+
+    line = {
+        "metric": "decode tokens/s (batch %d, context %d)" % (batch, context), "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if args.dtype.startswith("bf") else "fp32",
+        "data": "synthetic (seeded uniform-random token ids, seeded random weights)",
+        "config": {"model": args.preset, "layers": layers_run, "layers_in_config": layers_cfg,
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+                   "global_batch": batch, "seq_len": context, "prefill_tokens": args.prefill_tokens,
+                   "parallelism": "single GPU", "l2": "operands larger than L2 (weights ~1 GB per step); no flush",
+                   "tied_head": config.tie_word_embeddings},
+        "clocks": clocks.summary(), "gpu_launches": gpu_launches, "prefill": prefill, "roofline": roofline,
+        "points": points, "e2e": e2e,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -17,6 +17,7 @@ The loop is written against a small `Stepper` interface, so its decisions can be
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Optional, Protocol, Sequence
 
@@ -56,6 +57,8 @@ class GenerationLoop:
         self.bos_token_id = bos_token_id
         self.steps_run = 0            # decode steps of the last call, for callers that measure
         self.prompt_steps_run = 0
+        self.decode_seconds = 0.0     # host time of those decode steps (each ends with the tokens on the host)
+        self.decoded_tokens = 0
 
     def _stops(self, token: int) -> bool:
         return not self.ignore_eos and token in self.stop_token_ids
@@ -67,7 +70,8 @@ class GenerationLoop:
         if len(budgets) != n:
             raise ValueError("max_new_tokens must be one number or one per prompt")
         results = [SequenceResult() for _ in range(n)]
-        self.steps_run = self.prompt_steps_run = 0
+        self.steps_run = self.prompt_steps_run = self.decoded_tokens = 0
+        self.decode_seconds = 0.0
         size = max(int(batch_size), 1)
         for begin in range(0, n, size):
             self._run_batch(list(range(begin, min(begin + size, n))), prompts, budgets, results)
@@ -101,11 +105,14 @@ class GenerationLoop:
                                              [s.index for s in live], [0] * len(live))
             self.prompt_steps_run += 1
             live = self._take(live, chosen)
+            started = time.perf_counter()
             while live:
                 chosen = stepper.step_and_choose([(s.slot, [s.result.tokens[-1]]) for s in live],
                                                  [s.index for s in live], [len(s.result.tokens) for s in live])
                 self.steps_run += 1
+                self.decoded_tokens += len(live)
                 live = self._take(live, chosen)
+            self.decode_seconds += time.perf_counter() - started
         finally:
             for s in live:  # only after an exception: normal ends have closed their slots already
                 stepper.close(s.slot)

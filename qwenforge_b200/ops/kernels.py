@@ -48,7 +48,12 @@ def require_cuda(device, what: str = "this operation") -> None:
         raise KernelError("no CUDA device is available; this library has no CPU execution path")
 
 
+launches = 0  # kernels of this library launched by this process (the measurement reads it)
+
+
 def _check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
