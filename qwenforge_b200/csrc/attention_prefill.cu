@@ -1,0 +1,230 @@
+// Causal grouped-query flash attention for spans of new tokens over the paged cache (bf16): whole prompts of
+// unequal lengths, and continuations whose earlier keys already lie in the cache. The span's own keys were
+// written to the cache before this kernel runs, so all keys come from one place.
+//
+// A block (4 warps) serves 64 consecutive query tokens of one (sequence, query head); each warp owns 16 rows.
+// Key/value pages (64 positions) of the head's kv head stream through shared memory with double-buffered
+// cp.async, from the first page that any row's window reaches to the page of the last row's own position.
+// S = Q K^T and O += P V run on the tensor cores (m16n8k16, bf16 in, float32 accumulate); the online softmax
+// is float32 with base-2 exponentials (the scale folded in). A query at position p sees keys j with
+// max(0, p - window + 1) <= j <= p.
+#include "mma.cuh"
+
+#define PF_WARPS 4
+#define PF_THREADS (PF_WARPS * 32)
+#define PF_BM 64
+
+template <int D>
+__global__ void __launch_bounds__(PF_THREADS)
+prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
+                     const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
+                     float scale_log2, int window, int* err) {
+    constexpr int LD = D + 8;
+    constexpr int KS = D / 16;
+    constexpr int NT = D / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][64][LD]
+    bf16* v_s = k_s + 2 * QF_PAGE * LD;             // [2][64][LD]
+
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+    const int tile = gridDim.x - 1 - blockIdx.x;    // long rows first
+    const int row0 = tile * PF_BM;
+    if (row0 >= q_len) return;
+    const int n_rows = min(PF_BM, q_len - row0);
+    const int slot = slots[seq];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int q_width = n_heads * D;
+    const int kvh = head / (n_heads / site.kv_heads);
+
+    if (slot < 0) {
+        for (int i = threadIdx.x; i < n_rows * D; i += PF_THREADS)
+            out[(size_t)(q_begin + row0 + i / D) * q_width + (size_t)head * D + i % D] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos0 = tok_pos[q_begin + row0];             // position of the tile's first row
+    const int last_pos = pos0 + n_rows - 1;
+    const int lo_min = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int p_begin = lo_min / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
+
+    // this thread's two rows
+    const int r[2] = {16 * warp + (lane >> 2), 16 * warp + (lane >> 2) + 8};
+    const bool row_ok[2] = {r[0] < n_rows, r[1] < n_rows};
+    const int row_pos[2] = {pos0 + r[0], pos0 + r[1]};
+    const int row_lo[2] = {window > 0 ? max(0, row_pos[0] - window + 1) : 0, window > 0 ? max(0, row_pos[1] - window + 1) : 0};
+    // the warp's rows span positions [warp_first, warp_last]
+    const int warp_first = pos0 + 16 * warp, warp_last = min(pos0 + 16 * warp + 15, last_pos);
+    const int warp_lo = window > 0 ? max(0, warp_first - window + 1) : 0;
+    const bool warp_active = 16 * warp < n_rows;
+
+    uint32_t qa[KS][4];
+    {
+        const int c = 2 * (lane & 3);
+        const bf16* q0 = q + (size_t)(q_begin + row0 + r[0]) * q_width + (size_t)head * D;
+        const bf16* q1 = q + (size_t)(q_begin + row0 + r[1]) * q_width + (size_t)head * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + c) : 0u;
+            qa[ks][1] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + c) : 0u;
+            qa[ks][2] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + 8 + c) : 0u;
+            qa[ks][3] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + 8 + c) : 0u;
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
+
+    const int* table_row = site.table + (long long)slot * site.table_stride;
+    auto load_page = [&](int page_index, int buf) {
+        const int page = table_row[page_index];
+        const bool held = page >= 0;
+        if (!held && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
+        const bf16* kp = site.base + (long long)(held ? page : 0) * site.page_elems + (long long)kvh * QF_PAGE * D;
+        const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
+        constexpr int CH = D / 8;
+        for (int i = threadIdx.x; i < QF_PAGE * CH; i += PF_THREADS) {
+            const int rr = i / CH, c = (i % CH) * 8;
+            cp_async_16(k_s + ((size_t)buf * QF_PAGE + rr) * LD + c, kp + rr * D + c, held);
+            cp_async_16(v_s + ((size_t)buf * QF_PAGE + rr) * LD + c, vp + rr * D + c, held);
+        }
+    };
+
+    load_page(p_begin, 0);
+    cp_async_commit();
+    for (int p = p_begin; p < p_end; ++p) {
+        const int buf = (p - p_begin) & 1;
+        if (p + 1 < p_end) load_page(p + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* kb = k_s + (size_t)buf * QF_PAGE * LD;
+        const bf16* vb = v_s + (size_t)buf * QF_PAGE * LD;
+        const int key0 = p * QF_PAGE;
+        if (warp_active && key0 <= warp_last && key0 + QF_PAGE > warp_lo) {
+            float s[8][4];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int t2 = 0; t2 < 4; ++t2) {  // 16 keys per ldmatrix.x4
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, kb + (size_t)(16 * t2 + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
+                    mma_bf16_16816(s[2 * t2], qa[ks], kf[0], kf[1]);
+                    mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
+                }
+            }
+            // a page that every row of the warp sees whole needs no mask
+            const bool full = key0 + QF_PAGE - 1 <= warp_first && key0 >= (window > 0 ? max(0, warp_last - window + 1) : 0);
+            float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
+                    const bool ok0 = full || (kj <= row_pos[0] && kj >= row_lo[0]);
+                    const bool ok1 = full || (kj <= row_pos[1] && kj >= row_lo[1]);
+                    s[t][e] = ok0 ? s[t][e] * scale_log2 : QF_NEG_BIG;
+                    s[t][2 + e] = ok1 ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                    mx[0] = fmaxf(mx[0], s[t][e]);
+                    mx[1] = fmaxf(mx[1], s[t][2 + e]);
+                }
+            }
+            float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                corr[i] = exp2f(m_run[i] - m_new);
+                m_run[i] = m_new;
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    // a masked score is QF_NEG_BIG: its exponential is 0 unless the whole row is masked so far,
+                    // in which case the maximum is QF_NEG_BIG too and the difference would be 0
+                    s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
+                    s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
+                    sum[0] += s[t][e];
+                    sum[1] += s[t][2 + e];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+                sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+                l_run[i] = l_run[i] * corr[i] + sum[i];
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                o[nt][0] *= corr[0];
+                o[nt][1] *= corr[0];
+                o[nt][2] *= corr[1];
+                o[nt][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+                uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                  pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                for (int nt = 0; nt < NT; nt += 2) {
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vb + (size_t)(16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
+                    mma_bf16_16816(o[nt], pa, vf[0], vf[1]);
+                    mma_bf16_16816(o[nt + 1], pa, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!row_ok[i]) continue;
+        const float inv = l_run[i] > 0.f ? 1.0f / l_run[i] : 0.f;
+        bf16* dst = out + (size_t)(q_begin + row0 + r[i]) * q_width + (size_t)head * D + 2 * (lane & 3);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+            *reinterpret_cast<uint32_t*>(dst + 8 * nt) = pack_bf16(o[nt][2 * i] * inv, o[nt][2 * i + 1] * inv);
+    }
+}
+
+template <int D>
+static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
+                  const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
+                  int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
+    const size_t smem = (size_t)4 * QF_PAGE * (D + 8) * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
+    dim3 grid((max_q_len + PF_BM - 1) / PF_BM, n_heads, n_seqs);
+    prefill_flash_kernel<D><<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site,
+                                                                n_heads, scale * 1.4426950408889634f, window, err);
+    return (int)cudaGetLastError();
+}
+
+// Same arguments as the generic attention kernel, bf16 only. cudaErrorInvalidValue for a head size without an
+// instantiation (the caller then uses the generic kernel).
+QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
+                                   void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
+                                   int head_dim, int n_heads, int n_seqs, int max_q_len, float scale, int window,
+                                   int* err, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
+#define QF_CASE(DIM)                                                                                                 \
+    case DIM:                                                                                                        \
+        return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
+                           n_seqs, max_q_len, scale, window, err, stream);
+    switch (head_dim) {
+        QF_CASE(32)
+        QF_CASE(64)
+        QF_CASE(96)
+        QF_CASE(128)
+        default:
+            return (int)cudaErrorInvalidValue;
+    }
+#undef QF_CASE
+}

@@ -39,6 +39,7 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.err = None
+        self.decode_scratch = None
         self._bound = False
 
     # ------------------------------------------------------------------ structure
@@ -68,6 +69,7 @@ class Model:
         for part in self.parts():
             part.bind(tensors, self.dtype, self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.decode_scratch = ops.DecodeScratch(self.device)
         self._bound = True
         return self
 
@@ -131,7 +133,7 @@ class Model:
             raise ValueError("step: a slot appears twice in one batch")
         cache.reserve(grow)
         cache.flush()
-        ctx = build_context(triples, want, self.err, self.dtype, self.device, self.attention)
+        ctx = build_context(triples, want, self.err, self.dtype, self.device, self.attention, self.decode_scratch)
         logits = self.forward(ctx, cache)
         for slot, tokens in entries:
             if slot >= 0:

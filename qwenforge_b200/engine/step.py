@@ -19,6 +19,7 @@ class StepContext:
     n_seqs: int
     n_tokens: int
     max_q_len: int
+    max_kv_len: int                  # upper bound of any sequence's length after this step
     token_ids: torch.Tensor          # int32 [T]
     tok_seq: torch.Tensor            # int32 [T]
     tok_pos: torch.Tensor            # int32 [T]
@@ -28,6 +29,7 @@ class StepContext:
     err: torch.Tensor                # int32 [1] device error word
     dtype: torch.dtype
     attention: str = "auto"          # "auto": fastest kernel that takes the shape; "generic": the SIMT kernel
+    decode_scratch: Optional[object] = None   # ops.DecodeScratch shared by the model's attention layers
     # host copies, for parts that plan on the host (absent when a captured graph replays the step)
     host_slots: Optional[list] = None
     host_starts: Optional[list] = None
@@ -39,7 +41,8 @@ class StepContext:
 
 
 def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]],
-                  err: torch.Tensor, dtype: torch.dtype, device, attention: str = "auto") -> StepContext:
+                  err: torch.Tensor, dtype: torch.dtype, device, attention: str = "auto",
+                  decode_scratch=None) -> StepContext:
     """entries: (slot, start_position, token ids) per batch entry; want: per entry, the places among its
     tokens whose logits are wanted (None: the last token of every entry with a real slot)."""
     n = len(entries)
@@ -82,7 +85,9 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
 
     return StepContext(
         n_seqs=n, n_tokens=total, max_q_len=max(len(e[2]) for e in entries),
+        max_kv_len=max(e[1] + len(e[2]) for e in entries),
         token_ids=take(total), tok_seq=take(total), tok_pos=take(total), slots=take(n), cu_q=take(n + 1),
         want_rows=take(len(rows)) if rows else None, err=err, dtype=dtype, attention=attention,
+        decode_scratch=decode_scratch,
         host_slots=list(slots), host_starts=[e[1] for e in entries], host_q_lens=[len(e[2]) for e in entries],
     )

@@ -206,6 +206,74 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         _I(n_seqs), _I(max_q_len), _F(scale), _I(window), _ptr(err), _stream()), "attention_generic")
 
 
+FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
+                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
+                      window: int, err: torch.Tensor) -> None:
+    """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128."""
+    _dev("q", q, torch.bfloat16)
+    _dev("out", out, torch.bfloat16)
+    _dev("cache", site.storage, torch.bfloat16)
+    d = site.head_dim
+    if d not in FAST_ATTENTION_HEAD_DIMS:
+        raise KernelError(f"attention_prefill: head_dim {d} has no tensor-core kernel (have {FAST_ATTENTION_HEAD_DIMS}); "
+                          "use attention_generic")
+    if q.shape[1] != n_heads * d or out.shape != q.shape:
+        raise KernelError("attention_prefill: q/out widths do not match the head count")
+    _check(library("attention_prefill").qf_attention_prefill(
+        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
+        _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(max_q_len),
+        _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill")
+
+
+class DecodeScratch:
+    """Scratch of the split-K decode attention: float32 partial numerators and (max, sum) pairs per
+    (sequence, head, split), and the ticket counters (kept zero between calls by the kernel itself).
+    One instance is shared by all layers of a model: they run one after another on one stream."""
+
+    def __init__(self, device):
+        self.device = device
+        self.part_o = self.part_ml = self.counters = None
+
+    def ensure(self, n_seqs: int, n_heads: int, n_splits: int, head_dim: int, n_counters: int) -> None:
+        rows = n_seqs * n_heads * n_splits
+        if self.part_o is None or self.part_o.numel() < rows * head_dim:
+            self.part_o = torch.empty(rows * head_dim, dtype=torch.float32, device=self.device)
+        if self.part_ml is None or self.part_ml.numel() < rows * 2:
+            self.part_ml = torch.empty(rows * 2, dtype=torch.float32, device=self.device)
+        if self.counters is None or self.counters.numel() < n_counters:
+            self.counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
+                     slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, scale: float, window: int,
+                     n_splits: int, scratch: DecodeScratch, err: torch.Tensor) -> None:
+    """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128."""
+    _dev("q", q, torch.bfloat16)
+    _dev("out", out, torch.bfloat16)
+    _dev("cache", site.storage, torch.bfloat16)
+    d = site.head_dim
+    if d not in FAST_ATTENTION_HEAD_DIMS:
+        raise KernelError(f"attention_decode: head_dim {d} has no tensor-core kernel (have {FAST_ATTENTION_HEAD_DIMS}); "
+                          "use attention_generic")
+    if q.shape != (n_seqs, n_heads * d) or out.shape != q.shape:
+        raise KernelError("attention_decode: wants exactly one token per sequence, q [n_seqs, n_heads * head_dim]")
+    if not 1 <= n_splits <= 256:
+        raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..256")
+    group = n_heads // site.kv_heads
+    n_counters = n_seqs * site.kv_heads * ((group + 15) // 16)
+    if n_splits > 1:
+        scratch.ensure(n_seqs, n_heads, n_splits, d, n_counters)
+    _check(library("attention_decode").qf_attention_decode(
+        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
+        _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _F(scale),
+        _I(window), _I(n_splits), _ptr(scratch.part_o if n_splits > 1 else None),
+        _ptr(scratch.part_ml if n_splits > 1 else None), _ptr(scratch.counters if n_splits > 1 else None), _ptr(err),
+        _stream()), "attention_decode")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     _dev("gate_up", gate_up)

@@ -16,9 +16,12 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..cache import KvNeed
+from ..cache import PAGE_TOKENS, KvNeed
 from .base import Mixer, TensorSpec
 from .registry import build_part, register_part
+
+
+SM_COUNT = 148  # streaming multiprocessors of a B200
 
 
 class GqaAttention(Mixer):
@@ -69,6 +72,8 @@ class GqaAttention(Mixer):
         libs = {"rope_cache", "attention_generic"}
         if dtype == torch.float32:
             libs.add("gemm_f32")
+        elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
+            libs |= {"attention_decode", "attention_prefill"}
         return libs
 
     def cache_need(self):
@@ -97,9 +102,26 @@ class GqaAttention(Mixer):
         ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args,
                              writes_cache, ctx.err)
         attended = torch.empty_like(q)
-        ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                              ctx.max_q_len, self.scale, self.window, ctx.err)
+        fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16
+                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS)
+        if fast and ctx.is_decode:
+            ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                                 self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
+        elif fast:
+            ops.attention_prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                                  ctx.max_q_len, self.scale, self.window, ctx.err)
+        else:
+            ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                                  ctx.max_q_len, self.scale, self.window, ctx.err)
         return ops.linear(attended, self.o_weight, self.o_bias_t)
+
+    def decode_splits(self, ctx) -> int:
+        """How many blocks share one (sequence, kv head): enough to fill the GPU about twice, at most one per page
+        of the longest key range. Depends on the batch's shape only (it is fixed inside a captured graph)."""
+        span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + PAGE_TOKENS)
+        pages = max(1, -(-span // PAGE_TOKENS))
+        blocks = ctx.n_seqs * self.n_kv * (-(-(self.n_heads // self.n_kv) // 16))
+        return max(1, min(pages, 64, -(-2 * SM_COUNT // blocks)))
 
 
 register_part("mixer", "gqa_attention", GqaAttention)

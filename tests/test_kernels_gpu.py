@@ -281,3 +281,94 @@ def test_sample_distribution(ops):
     freq = torch.bincount(out.long().cpu(), minlength=5).double() / 4000
     want = torch.softmax(logits[0].double().cpu() / 1.3, -1)
     assert float((freq - want).abs().max()) < 0.03
+
+
+# ------------------------------------------------------------------------------------------------ tensor-core attention
+
+FAST_PREFILL_SHAPES = [
+    # nh, kvh, d, q_lens, starts, window
+    (14, 2, 64, [130, 3, 64], [0, 125, 0], 0),
+    (7, 1, 64, [1, 65, 200], [0, 63, 1], 0),
+    (4, 2, 128, [70, 129], [10, 0], 0),
+    (6, 3, 32, [100, 1, 40], [0, 90, 30], 37),          # window
+    (8, 2, 96, [65, 17], [300, 5], 64),
+    (33, 1, 32, [9, 2], [5, 0], 0),
+    (16, 2, 128, [257], [0], 100),
+]
+
+
+@pytest.mark.parametrize("nh,kvh,d,q_lens,starts,window", FAST_PREFILL_SHAPES)
+def test_attention_prefill(ops, nh, kvh, d, q_lens, starts, window):
+    out, want = run_attention(ops, "attention_prefill", torch.bfloat16, nh, kvh, d, q_lens, starts, window)
+    assert max_err(out, want) <= 3e-2
+
+
+def test_attention_prefill_padding_entry_and_refusal(ops):
+    out, want = run_attention(ops, "attention_prefill", torch.bfloat16, 4, 2, 64, [3, 2, 70], [0, 0, 7], 0, slots=[1, -1, 0])
+    assert max_err(out, want) <= 3e-2 and float(out[3:5].float().abs().max()) == 0.0
+    with pytest.raises(ops.KernelError, match="head_dim 24"):
+        run_attention(ops, "attention_prefill", torch.bfloat16, 5, 1, 24, [4], [0], 0)
+
+
+def run_decode(ops, nh, kvh, d, lengths, window, n_splits, slots=None, seed=12):
+    n = len(lengths)
+    slots = slots if slots is not None else list(range(n))[::-1]
+    site = FakeSite(n, max(lengths), kvh, d, torch.bfloat16, seed)
+    for slot, length in zip(slots, lengths):
+        if slot >= 0:
+            fill_site(site, slot, length, seed + slot, torch.bfloat16)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(n, nh * d, generator=g).to(torch.bfloat16).to(DEV)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([length - 1 for length in lengths], dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    out = torch.full((n, nh * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    want = torch.empty_like(out)
+    e = err_word()
+    args = ops.KvSiteArgs(site.storage, site.table, kvh, d)
+    scratch = ops.DecodeScratch(DEV)
+    for _ in range(2):  # twice with the same scratch: the ticket counters must come back to zero
+        out.fill_(7.0)
+        ops.attention_decode(q, out, cu, tok_pos, slots_t, args, nh, n, d ** -0.5, window, n_splits, scratch, e)
+    ref.attention_generic(q, want, cu, tok_pos, slots_t, site, nh, n, 1, d ** -0.5, window, None)
+    assert int(e) == 0
+    if n_splits > 1:
+        assert int(scratch.counters.abs().max()) == 0
+    return out, want
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 64])
+@pytest.mark.parametrize("nh,kvh,d,lengths,window", [
+    (14, 2, 64, [1, 64, 65, 700], 0),
+    (7, 1, 64, [4096, 130], 0),
+    (16, 4, 128, [300, 1, 129], 0),
+    (40, 2, 32, [200, 77], 0),               # a group of 20: two chunks of query heads
+    (6, 3, 96, [500, 36, 1], 37),            # window
+    (8, 2, 128, [1000], 64),
+])
+def test_attention_decode(ops, nh, kvh, d, lengths, window, n_splits):
+    out, want = run_decode(ops, nh, kvh, d, lengths, window, n_splits)
+    assert max_err(out, want) <= 3e-2
+
+
+def test_attention_decode_padding_and_far_key(ops):
+    out, want = run_decode(ops, 4, 2, 64, [100, 50, 9], 0, 3, slots=[1, -1, 0])
+    assert max_err(out, want) <= 3e-2 and float(out[1].float().abs().max()) == 0.0
+    # one far key dominates: the output is its value, through every split
+    nh, kvh, d, length = 2, 1, 64, 3000
+    site = FakeSite(1, length, kvh, d, torch.bfloat16, 9)
+    fill_site(site, 0, length, 3, torch.bfloat16)
+    far = 70
+    page, off = int(site.table[0, far // 64]), far % 64
+    site.storage[page, 0, 0, off] = 0
+    site.storage[page, 0, 0, off, 0] = 60.0
+    q = torch.zeros(1, nh * d, dtype=torch.bfloat16, device=DEV)
+    q[0, 0] = q[0, d] = 40.0
+    out = torch.empty_like(q)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([length - 1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0], dtype=torch.int32, device=DEV)
+    ops.attention_decode(q, out, cu, pos, slots, ops.KvSiteArgs(site.storage, site.table, kvh, d), nh, 1, d ** -0.5, 0,
+                         16, ops.DecodeScratch(DEV), err_word())
+    value = site.storage[page, 1, 0, off]
+    assert max_err(out[0, :d], value) < 2e-2 and max_err(out[0, d:], value) < 2e-2
