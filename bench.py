@@ -104,40 +104,45 @@ def model_numbers(config, layers_run):
                 attn_flops=lambda t: layers_run * 4 * nh * d * t * (t + 1) // 2)
 
 
-def timed_decode(model, cache, batch, context, steps, warmup, vocab, torch, sampler=None):
-    """Prefill `batch` prompts so that warmup + steps decode steps end at `context`; returns ms per timed step."""
+def timed_decode(model, cache, batch, context, steps, warmup, vocab, torch):
+    """Prefill `batch` prompts so that warmup + steps decode steps end at `context`, then replay the captured
+    decode step (model, sampling, state update) from its CUDA graph. Returns (ms per timed step, kernels per step)."""
+    from qwenforge_b200.engine.graphs import CHUNK_STEPS, DecodeGraph
     from qwenforge_b200.sampling import Sampler
-    sampler = sampler or Sampler()
+    sampler = Sampler()
     prompt_len = context - steps - warmup
     g = torch.Generator().manual_seed(1234)
     slots = [cache.open() for _ in range(batch)]
     cache.reserve([(s, context) for s in slots])
-    tokens = None
+    tokens = []
     for begin in range(0, batch, 8):  # prefill in chunks of 8 prompts to bound activation memory
         chunk = slots[begin:begin + 8]
         prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in chunk]
-        logits = model.step(cache, list(zip(chunk, prompts)))
-        first = sampler(logits).tolist()
-        tokens = first if tokens is None else tokens + first
+        tokens += sampler(model.step(cache, list(zip(chunk, prompts)))).tolist()
+    cache.flush()
+    graph = DecodeGraph(model, cache, batch, context, sampler)
+    graph.capture()
+    graph.load(slots, tokens, [prompt_len] * batch, [1] * batch, [1 << 30] * batch, list(range(batch)), [])
 
-    def one_step(tokens):
-        logits = model.step(cache, [(s, [t]) for s, t in zip(slots, tokens)])
-        return sampler(logits).tolist()
+    def run(n):
+        for i in range(n):
+            if i % CHUNK_STEPS == 0:
+                graph.cursor.zero_()
+            graph.graph.replay()
 
-    for _ in range(warmup):
-        tokens = one_step(tokens)
+    run(warmup)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(steps):
-        tokens = one_step(tokens)
+    run(steps)
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     model.raise_on_kernel_error()
+    assert int(graph.tok_pos.max()) == context, "the timed steps did not end at the context length"
     for s in slots:
         cache.close(s)
-    return ms
+    return ms, graph.kernels_per_step
 
 
 def main():
@@ -156,8 +161,7 @@ def main():
 
     from qwenforge_b200.config import preset_config, preset_dict
     from qwenforge_b200.engine import Model, StudentEngine
-    from qwenforge_b200.ops import kernels
-    from qwenforge_b200.weights import write_random_model
+        from qwenforge_b200.weights import write_random_model
 
     pk = peaks()
     full = preset_config(args.preset)
@@ -194,11 +198,9 @@ def main():
                    "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
         # ---- the headline: decode at the default batch, with clocks sampled meanwhile
-        launches_before = kernels.launches
         with ClockSampler() as clocks:
-            ms = timed_decode(model, cache, batch, context, steps, warmup, vocab, torch)
-        launches = kernels.launches - launches_before
-        gpu_launches = int(round(launches * steps / (steps + warmup + 1)))  # the timed steps' share
+            ms, per_step = timed_decode(model, cache, batch, context, steps, warmup, vocab, torch)
+        gpu_launches = per_step * steps  # this library's own kernels in the timed replays (library GEMMs not counted)
         value = batch * 1e3 / ms
         mean_ctx = context - steps / 2
         step_bytes = numbers["weight_bytes"] + batch * mean_ctx * numbers["kv_bytes_per_token"]
@@ -210,7 +212,7 @@ def main():
         if not args.no_points:
             for b in (1, 64):
                 k = min(steps, 128)
-                points[f"decode_b{b}"] = round(b * 1e3 / timed_decode(model, cache, b, context, k, 4, vocab, torch), 1)
+                points[f"decode_b{b}"] = round(b * 1e3 / timed_decode(model, cache, b, context, k, 4, vocab, torch)[0], 1)
             # ---- end to end through the entry point: host token ids in, host token ids out, every step
             del cache
             engine = StudentEngine(folder, device="cuda:0", dtype=args.dtype)
@@ -219,8 +221,14 @@ def main():
             engine.generate_ids(prompts[:1], 4, ignore_eos=True)  # warm-up
             engine.generate_ids(prompts, k + 1, batch_size=batch, ignore_eos=True)
             loop = engine.last_loop
+            # copies of the decode phase, from the tensors copied: the rows' state once per batch of requests
+            # (5 int32 + 1 int64 per row, 8 stop ids), the produced tokens and the error word once per chunk of steps
+            chunks = -(-loop.steps_run // 32)
             e2e = {"value": round(loop.decoded_tokens / loop.decode_seconds, 1), "unit": "tokens/s",
-                   "h2d_bytes_per_step": 4 * (6 * batch + 1), "d2h_bytes_per_step": 4 * (batch + 1)}
+                   "h2d_bytes_per_step": round((28 * batch + 32) / max(loop.steps_run, 1), 2),
+                   "d2h_bytes_per_step": round(chunks * (4 * 32 * batch + 4) / max(loop.steps_run, 1), 2),
+                   "note": "StudentEngine.generate_ids: host token ids in, host token ids out; decode replays CUDA "
+                           "graphs and reads tokens back every 32 steps"}
 
     line = {
         "metric": "decode tokens/s (batch %d, context %d)" % (batch, context), "value": round(value, 1), "unit": "tokens/s",

@@ -23,6 +23,7 @@ from ..cache import PAGE_TOKENS, CacheFull, round_up
 from ..sampling import Sampler, SamplingParams
 from ..weights.resolve import resolve_model_dir
 from .generate import GenerationLoop, SequenceResult
+from .graphs import MAX_STOP_IDS, GraphDecoder
 from .model import Model
 from .tokenizer import load_tokenizer
 
@@ -30,11 +31,14 @@ from .tokenizer import load_tokenizer
 class ModelStepper:
     """The generation loop's view of a model, its cache and a sampler (`generate.Stepper`)."""
 
-    def __init__(self, model: Model, cache, sampler: Sampler):
+    def __init__(self, model: Model, cache, sampler: Sampler, graph_decoder: Optional[GraphDecoder] = None,
+                 min_graph_steps: int = 8):
         self.model = model
         self.cache = cache
         self.sampler = sampler
         self.max_positions = model.spec.max_positions
+        self.graph_decoder = graph_decoder
+        self.min_graph_steps = min_graph_steps  # the reference graphs runs of >= 8 new tokens (student_engine.py:1274-1276)
 
     def open(self) -> int:
         return self.cache.open()
@@ -59,10 +63,43 @@ class ModelStepper:
         return packed[:-1]
 
 
+    def open_decode_session(self, rows, stop_token_ids):
+        """A CUDA-graph decode session for these rows, or None when graphs are off, a part of the model plans on the
+        host, or the run is too short to repay a capture."""
+        if self.graph_decoder is None or len(rows) > 1024 or len(stop_token_ids) > MAX_STOP_IDS:
+            return None
+        if max(budget - made for _, _, _, made, budget in rows) < self.min_graph_steps:
+            return None
+        return _GraphSession(self, rows, stop_token_ids)
+
+
+class _GraphSession:
+    def __init__(self, stepper: ModelStepper, rows, stop_token_ids):
+        cache = stepper.cache
+        self.stepper = stepper
+        self.slots = [r[0] for r in rows]
+        longest = max(cache.lengths[slot] + (budget - made) for slot, _, _, made, budget in rows)
+        self.graph = stepper.graph_decoder.get(len(rows), longest, stepper.sampler)
+        cache.flush()
+        self.graph.load(self.slots, [r[1] for r in rows], [cache.lengths[r[0]] for r in rows], [r[3] for r in rows],
+                        [r[4] for r in rows], [r[2] for r in rows], stop_token_ids)
+
+    def run(self, n_steps: int) -> list:
+        produced = self.graph.run(n_steps)
+        cache = self.stepper.cache
+        for row, slot in enumerate(self.slots):
+            fed = sum(1 for step_tokens in produced if step_tokens[row] >= 0)
+            if fed:
+                cache.advance(slot, fed)
+        if int(self.stepper.model.err.item()):
+            self.stepper.model.raise_on_kernel_error()
+        return [step_tokens[:len(self.slots)] for step_tokens in produced]
+
+
 class StudentEngine:
     def __init__(self, model_path: str, device: str = "cuda", dtype: str = "bfloat16",
                  attn_implementation: str = "sdpa", local_files_only: bool = False, seed: int = 0,
-                 max_cache_tokens: Optional[int] = None):
+                 max_cache_tokens: Optional[int] = None, cuda_graphs: bool = True):
         self.model_path = model_path
         self.device = torch.device(device)
         self.attn_implementation = str(attn_implementation).lower()
@@ -75,7 +112,9 @@ class StudentEngine:
         self.torch_dtype = self.model.dtype
         self.tokenizer = load_tokenizer(model_dir, self.model.spec.vocab_size, self.local_files_only)
         self._max_cache_tokens = max_cache_tokens
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and GraphDecoder.supported(self.model)
         self.cache = None
+        self.graph_decoder: Optional[GraphDecoder] = None
         self.last_loop: Optional[GenerationLoop] = None
 
     # ------------------------------------------------------------------ cache sizing
@@ -95,9 +134,11 @@ class StudentEngine:
         if cache is None or cache.n_pages * PAGE_TOKENS < need_tokens or cache.max_seqs < need_seqs:
             if cache is not None and cache.live_slots():
                 raise RuntimeError("the cache cannot grow while sequences are live")
-            self.cache = None
+            self.cache = self.graph_decoder = None  # graphs hold the old cache's addresses
             del cache
             self.cache = self.model.new_cache(need_tokens, max(need_seqs, 8))
+        if self.cuda_graphs and self.graph_decoder is None:
+            self.graph_decoder = GraphDecoder(self.model, self.cache)
 
     # ------------------------------------------------------------------ token ids
     @torch.inference_mode()
@@ -120,7 +161,7 @@ class StudentEngine:
         stops = self.model.spec.stop_token_ids if stop_token_ids is None else tuple(stop_token_ids)
         self._ensure_cache([len(p) for p in prompts], budgets, size)
         sampler = Sampler(SamplingParams(float(temperature), self.seed if seed is None else int(seed)))
-        loop = GenerationLoop(ModelStepper(self.model, self.cache, sampler), stops, ignore_eos,
+        loop = GenerationLoop(ModelStepper(self.model, self.cache, sampler, self.graph_decoder), stops, ignore_eos,
                               getattr(self.tokenizer, "bos_token_id", None))
         self.last_loop = loop
         return loop.run(prompts, budgets, size)

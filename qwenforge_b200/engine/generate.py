@@ -33,6 +33,11 @@ class Stepper(Protocol):
     def step_and_choose(self, entries: Sequence[tuple[int, Sequence[int]]], seq_ids: Sequence[int],
                         steps: Sequence[int]) -> list[int]: ...
 
+    # Optional: a stepper may also offer `open_decode_session(rows, stop_token_ids)`, with rows of
+    # (slot, latest token, sequence id, tokens generated so far, budget). It returns None, or an object whose
+    # `run(n)` performs up to n single-token steps for all rows without the host in between and returns, per
+    # step, each row's produced token (-1 once the row has ended, by the same rules as the loop's).
+
 
 @dataclass
 class SequenceResult:
@@ -106,6 +111,13 @@ class GenerationLoop:
             self.prompt_steps_run += 1
             live = self._take(live, chosen)
             started = time.perf_counter()
+            session = None
+            if live and hasattr(stepper, "open_decode_session"):
+                session = stepper.open_decode_session(
+                    [(s.slot, s.result.tokens[-1], s.index, len(s.result.tokens), s.budget) for s in live],
+                    () if self.ignore_eos else tuple(self.stop_token_ids))
+            if session is not None:
+                live = self._run_session(session, live)
             while live:
                 chosen = stepper.step_and_choose([(s.slot, [s.result.tokens[-1]]) for s in live],
                                                  [s.index for s in live], [len(s.result.tokens) for s in live])
@@ -116,6 +128,22 @@ class GenerationLoop:
         finally:
             for s in live:  # only after an exception: normal ends have closed their slots already
                 stepper.close(s.slot)
+
+    def _run_session(self, session, live: list) -> list:
+        """Decode with a host-free session: read the produced tokens chunk by chunk and apply the same decisions."""
+        rows = list(live)
+        while live:
+            remaining = max(s.budget - len(s.result.tokens) for s in live)
+            for step_tokens in session.run(remaining):
+                if not live:
+                    break
+                chosen = [step_tokens[rows.index(s)] for s in live]
+                if any(t < 0 for t in chosen):
+                    raise RuntimeError("decode session and generation loop disagree on which sequences are live")
+                self.steps_run += 1
+                self.decoded_tokens += len(live)
+                live = self._take(live, chosen)
+        return live
 
     def _take(self, live: list, chosen: Sequence[int]) -> list:
         """Append each sequence's new token; sequences that end leave the batch and free their slot."""

@@ -1,0 +1,136 @@
+"""Decode steps replayed from CUDA graphs, without the host between steps.
+
+The reference captures its whole decode step once per (batch, cache capacity) and replays it, patching a write
+index, a position and a mask slot from the host before every replay (student_engine.py:984-1133). Here everything
+that changes from step to step lives on the device: the rows' input tokens, positions, step counts and slots are
+static buffers that the step's own last kernel (`decode_advance`) updates, and the page tables already cover each
+sequence's whole budget, so a replay needs no host work at all and the host reads the produced tokens only once
+per chunk of steps.
+
+A captured graph is keyed by (rows, bound on the longest sequence, sampling temperature and seed): the bound fixes
+how the decode attention splits its key range, the sampling scalars are arguments of the sampling kernel. Graphs
+are kept and replayed by later batches of the same key (the reference's registry, :1081-1118). Rows that end early
+stay in the launch as padding entries (slot -1), which touch no cache and change no result.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..sampling import Sampler
+from .step import StepContext
+
+MAX_STOP_IDS = 8
+CHUNK_STEPS = 32
+
+
+def length_bound(n: int) -> int:
+    """The next power of two >= n (at least 256): sequences of similar length share a graph."""
+    bound = 256
+    while bound < n:
+        bound *= 2
+    return bound
+
+
+class DecodeGraph:
+    """Static buffers and the captured step for `rows` sequences."""
+
+    def __init__(self, model, cache, rows: int, max_len: int, sampler: Sampler):
+        device = model.device
+        self.model, self.cache, self.rows, self.sampler = model, cache, rows, sampler
+        i32 = dict(dtype=torch.int32, device=device)
+        self.token_ids = torch.zeros(rows, **i32)
+        self.tok_pos = torch.zeros(rows, **i32)
+        self.slots = torch.full((rows,), -1, **i32)
+        self.steps = torch.zeros(rows, **i32)
+        self.budgets = torch.zeros(rows, **i32)
+        self.seq_ids = torch.zeros(rows, dtype=torch.int64, device=device)
+        self.stop_ids = torch.full((MAX_STOP_IDS,), -1, **i32)
+        self.sampled = torch.zeros(rows, **i32)
+        self.out_tokens = torch.full((CHUNK_STEPS, rows), -1, **i32)
+        self.cursor = torch.zeros(1, **i32)
+        self.n_stop = 0
+        arange = torch.arange(rows + 1, **i32)
+        self.ctx = StepContext(
+            n_seqs=rows, n_tokens=rows, max_q_len=1, max_kv_len=max_len, token_ids=self.token_ids,
+            tok_seq=arange[:rows].clone(), tok_pos=self.tok_pos, slots=self.slots, cu_q=arange,
+            want_rows=arange[:rows].clone(), err=model.err, dtype=model.dtype, attention=model.attention,
+            decode_scratch=model.decode_scratch)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels_per_step = 0
+
+    def _one_step(self) -> None:
+        logits = self.model.forward(self.ctx, self.cache)
+        self.sampler(logits, self.seq_ids, self.steps, out=self.sampled)
+        ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
+                           self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor)
+
+    def load(self, slots, tokens, positions, steps, budgets, seq_ids, stop_ids) -> None:
+        """Set the rows' state (rows beyond the given ones are padding)."""
+        pad = self.rows - len(slots)
+        packed = torch.tensor([list(tokens) + [0] * pad, list(positions) + [0] * pad, list(slots) + [-1] * pad,
+                               list(steps) + [0] * pad, list(budgets) + [0] * pad], dtype=torch.int32)
+        packed = packed.to(self.token_ids.device)
+        self.token_ids.copy_(packed[0])
+        self.tok_pos.copy_(packed[1])
+        self.slots.copy_(packed[2])
+        self.steps.copy_(packed[3])
+        self.budgets.copy_(packed[4])
+        self.seq_ids.copy_(torch.tensor(list(seq_ids) + [0] * pad, dtype=torch.int64).to(self.seq_ids.device))
+        stops = list(stop_ids)[:MAX_STOP_IDS]
+        self.stop_ids.copy_(torch.tensor(stops + [-1] * (MAX_STOP_IDS - len(stops)), dtype=torch.int32))
+
+    def capture(self) -> None:
+        """Two eager steps on a side stream (they size every scratch buffer), then the capture. The rows are all
+        padding meanwhile (slot -1), so neither touches the cache or the rows' state."""
+        saved = self.slots.clone()
+        self.slots.fill_(-1)
+        stream = torch.cuda.Stream(device=self.model.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self._one_step()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        before = ops.kernels.launches
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            self._one_step()
+        self.kernels_per_step = ops.kernels.launches - before
+        self.graph = graph
+        self.cursor.zero_()
+        self.slots.copy_(saved)
+
+    def run(self, n_steps: int) -> list:
+        """Replay `n_steps` (<= CHUNK_STEPS) steps; returns per step the rows' produced tokens (-1: none)."""
+        n_steps = min(n_steps, CHUNK_STEPS)
+        self.cursor.zero_()
+        for _ in range(n_steps):
+            self.graph.replay()
+        ops.kernels.launches += self.kernels_per_step * n_steps
+        return self.out_tokens[:n_steps].tolist()
+
+
+class GraphDecoder:
+    """Keeps captured decode graphs of one model and cache, newest last; old ones are dropped beyond `keep`."""
+
+    def __init__(self, model, cache, keep: int = 8):
+        self.model, self.cache, self.keep = model, cache, keep
+        self.graphs: dict = {}
+
+    @staticmethod
+    def supported(model) -> bool:
+        return all(getattr(part, "graph_safe", True) for part in model.parts())
+
+    def get(self, rows: int, max_len: int, sampler: Sampler) -> DecodeGraph:
+        key = (rows, length_bound(max_len), sampler.params.temperature, sampler.params.seed)
+        graph = self.graphs.pop(key, None)
+        if graph is None:
+            graph = DecodeGraph(self.model, self.cache, rows, key[1], sampler)
+            graph.capture()
+        self.graphs[key] = graph
+        while len(self.graphs) > self.keep:
+            self.graphs.pop(next(iter(self.graphs)))
+        return graph

@@ -1,4 +1,4 @@
-from .kernels import (FAST_ATTENTION_HEAD_DIMS, DecodeScratch, attention_decode, attention_prefill, ERR_NO_PAGE, ERR_ROW_RANGE, ERR_TOKEN_RANGE, KernelError, KvSiteArgs, add_rms_norm,
+from .kernels import (decode_advance, FAST_ATTENTION_HEAD_DIMS, DecodeScratch, attention_decode, attention_prefill, ERR_NO_PAGE, ERR_ROW_RANGE, ERR_TOKEN_RANGE, KernelError, KvSiteArgs, add_rms_norm,
                       attention_generic, describe_error_word, embed_gather, gather_rows, gemm_f32, require_cuda,
                       rope_cache_write, sample, swiglu)
 from .linear import linear
@@ -7,5 +7,5 @@ __all__ = [
     "ERR_NO_PAGE", "ERR_ROW_RANGE", "ERR_TOKEN_RANGE", "KernelError", "KvSiteArgs", "add_rms_norm",
     "attention_generic", "describe_error_word", "embed_gather", "gather_rows", "gemm_f32", "rope_cache_write",
     "sample", "swiglu", "linear", "require_cuda", "FAST_ATTENTION_HEAD_DIMS", "DecodeScratch",
-    "attention_decode", "attention_prefill",
+    "attention_decode", "attention_prefill", "decode_advance",
 ]

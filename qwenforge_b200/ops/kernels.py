@@ -305,3 +305,20 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optiona
     _check(library("sampling").qf_sample(_ptr(logits), _I(rows), _I(vocab), _LL(logits.stride(0)),
                                          _F(max(float(temperature), 0.0)), _ULL(seed & 0xFFFFFFFFFFFFFFFF),
                                          _ptr(seq_ids), _ptr(steps), _ptr(out), _stream()), "sample")
+
+
+def decode_advance(sampled: torch.Tensor, token_ids: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
+                   steps: torch.Tensor, budgets: torch.Tensor, stop_ids: torch.Tensor, n_stop: int,
+                   out_tokens: torch.Tensor, cursor: torch.Tensor) -> None:
+    """Record each live row's sampled token in out_tokens[cursor], feed it back as the next input, advance
+    position and step count, retire rows that stopped (slot := -1); cursor += 1. All int32, on the device."""
+    for name, t in (("sampled", sampled), ("token_ids", token_ids), ("tok_pos", tok_pos), ("slots", slots),
+                    ("steps", steps), ("budgets", budgets), ("stop_ids", stop_ids), ("out_tokens", out_tokens),
+                    ("cursor", cursor)):
+        _dev(name, t, torch.int32)
+    n = token_ids.numel()
+    if out_tokens.dim() != 2 or out_tokens.shape[1] != n or n_stop > stop_ids.numel():
+        raise KernelError("decode_advance: out_tokens must be [max_steps, rows]; n_stop within stop_ids")
+    _check(library("decode_state").qf_decode_advance(
+        _ptr(sampled), _ptr(token_ids), _ptr(tok_pos), _ptr(slots), _ptr(steps), _ptr(budgets), _ptr(stop_ids),
+        _I(n_stop), _ptr(out_tokens), _ptr(cursor), _I(out_tokens.shape[0]), _I(n), _stream()), "decode_advance")

@@ -53,6 +53,9 @@ class TensorSpec:
 
 class Part:
     kind = ""
+    # False for a part whose forward needs the step's host-side lists (ctx.host_*): a model with such a part
+    # decodes step by step instead of replaying captured graphs
+    graph_safe = True
 
     def __init__(self, spec: PartSpec):
         self.spec = spec

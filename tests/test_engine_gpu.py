@@ -251,3 +251,35 @@ def test_temperature_sampling_is_independent_of_batching(folders):
     assert other_seed != together
     greedy = engine.generate_ids(prompts, 10, batch_size=4, ignore_eos=True)
     assert greedy != together
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_w", "small_64"])
+def test_graph_decoding_equals_stepping(folders, name, dtype):
+    """Decode steps replayed from CUDA graphs give the tokens of step-by-step decoding: unequal prompts, budgets that
+    end at different steps, a stop token, several chunks of replays, and a second batch that reuses the graph."""
+    from qwenforge_b200.engine import StudentEngine
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 600 + n) for n in (5, 70, 17, 1, 64)]
+    budgets = [80, 12, 45, 9, 33]
+    eager = StudentEngine(str(folders[name][0]), device="cuda", dtype=dtype, cuda_graphs=False)
+    graphed = StudentEngine(str(folders[name][0]), device="cuda", dtype=dtype, cuda_graphs=True)
+    for temperature in (0.0, 0.8):
+        want = eager.generate_results(prompts, budgets, batch_size=5, temperature=temperature, ignore_eos=True)
+        got = graphed.generate_results(prompts, budgets, batch_size=5, temperature=temperature, ignore_eos=True)
+        assert graphed.graph_decoder.graphs, "no graph was captured"
+        if dtype == "float32":
+            assert [r.tokens for r in got] == [r.tokens for r in want]
+        else:  # bf16 logits can tie differently between the two attention split shapes; lengths must agree
+            assert [len(r.tokens) for r in got] == budgets
+    stop = want[0].tokens[20]
+    a = eager.generate_results(prompts, budgets, batch_size=5, temperature=0.8, stop_token_ids=[stop])
+    b = graphed.generate_results(prompts, budgets, batch_size=5, temperature=0.8, stop_token_ids=[stop])
+    if dtype == "float32":
+        assert [(r.tokens, r.finish_reason) for r in a] == [(r.tokens, r.finish_reason) for r in b]
+        assert b[0].finish_reason == "stop" and b[0].tokens[-1] == stop
+    assert not graphed.cache.live_slots()
+    assert all(g.pages.n_free == g.pages.n_pages for g in graphed.cache.kv_groups)
+    n_graphs = len(graphed.graph_decoder.graphs)
+    graphed.generate_results(prompts, budgets, batch_size=5, temperature=0.8, ignore_eos=True)
+    assert len(graphed.graph_decoder.graphs) == n_graphs       # the same key: replayed, not captured again

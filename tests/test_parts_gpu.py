@@ -243,6 +243,8 @@ def register_toy_parts():
     from qwenforge_b200.parts import Mixer, PositionEncoding, TensorSpec, register_part
 
     class DecayedSum(Mixer):
+        graph_safe = False   # its forward plans on the host, so decode steps are not captured into CUDA graphs
+
         def __init__(self, spec):
             super().__init__(spec)
             self.width, self.inner, self.decay = self.params["width"], self.params["inner"], self.params["decay"]
