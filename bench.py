@@ -161,7 +161,7 @@ def main():
 
     from qwenforge_b200.config import preset_config, preset_dict
     from qwenforge_b200.engine import Model, StudentEngine
-        from qwenforge_b200.weights import write_random_model
+    from qwenforge_b200.weights import write_random_model
 
     pk = peaks()
     full = preset_config(args.preset)

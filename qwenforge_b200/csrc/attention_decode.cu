@@ -234,17 +234,41 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     // the last block of this (sequence, kv head, chunk): every partial is visible now
     __threadfence();
     if (threadIdx.x == 0) counters[(size_t)seq * gridDim.y + blockIdx.y] = 0;
+    // (max, sum) of every (row, split) into shared memory with independent loads, then one warp per row turns
+    // them into weights exp2(m - M) and the row's denominator
+    float2* ml_s = reinterpret_cast<float2*>(smem_raw);  // [n_g][n_splits]; o_s has been written out above
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_g * n_splits; i += DEC_THREADS)
+        ml_s[i] = __ldcg(reinterpret_cast<const float2*>(part_ml) + part_row0 + i);
+    __syncthreads();
+    for (int r = warp; r < n_g; r += DEC_WARPS) {
+        float m = QF_NEG_BIG;
+        for (int sp = lane; sp < n_splits; sp += 32) m = fmaxf(m, ml_s[r * n_splits + sp].x);
+        m = warp_max(m);
+        float den = 0.f;
+        for (int sp = lane; sp < n_splits; sp += 32) {
+            const float2 v = ml_s[r * n_splits + sp];
+            const float w = exp2f(v.x - m);
+            den += w * v.y;
+            ml_s[r * n_splits + sp].x = w;
+        }
+        den = warp_sum(den);
+        if (lane == 0) l_s[0][r] = den;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
         const int r = i / D, d = i % D;
-        const size_t base = part_row0 + (size_t)r * n_splits;
-        float m = QF_NEG_BIG;
-        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, __ldcg(part_ml + (base + sp) * 2));
-        float num = 0.f, den = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float w = exp2f(__ldcg(part_ml + (base + sp) * 2) - m);
-            den += w * __ldcg(part_ml + (base + sp) * 2 + 1);
-            num += w * __ldcg(part_o + (base + sp) * D + d);
+        const float* po = part_o + (part_row0 + (size_t)r * n_splits) * D + d;
+        float num = 0.f;
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = sp0 + j < n_splits ? __ldcg(po + (size_t)(sp0 + j) * D) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (sp0 + j < n_splits) num += ml_s[r * n_splits + sp0 + j].x * v[j];
         }
+        const float den = l_s[0][r];
         out_row[i] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
 }

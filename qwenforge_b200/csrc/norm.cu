@@ -38,3 +38,19 @@ QF_EXPORT int qf_add_rms_norm(int is_bf16, float* hidden, const void* delta, con
     return is_bf16 ? launch<bf16>(hidden, delta, weight, out, rows, width, eps, stream)
                    : launch<float>(hidden, delta, weight, out, rows, width, eps, stream);
 }
+
+template <typename T> __global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ delta, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        hidden[i] += Num<T>::to_f(delta[i]);
+}
+
+// hidden += delta over n elements (the residual stream catching up with a pending update).
+QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    if (is_bf16)
+        residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(hidden, (const bf16*)delta, n);
+    else
+        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(hidden, (const float*)delta, n);
+    return (int)cudaGetLastError();
+}

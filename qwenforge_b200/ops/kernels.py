@@ -260,8 +260,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok
                           "use attention_generic")
     if q.shape != (n_seqs, n_heads * d) or out.shape != q.shape:
         raise KernelError("attention_decode: wants exactly one token per sequence, q [n_seqs, n_heads * head_dim]")
-    if not 1 <= n_splits <= 256:
-        raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..256")
+    if not 1 <= n_splits <= 128:
+        raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..128")
     group = n_heads // site.kv_heads
     n_counters = n_seqs * site.kv_heads * ((group + 15) // 16)
     if n_splits > 1:
@@ -322,3 +322,99 @@ def decode_advance(sampled: torch.Tensor, token_ids: torch.Tensor, tok_pos: torc
     _check(library("decode_state").qf_decode_advance(
         _ptr(sampled), _ptr(token_ids), _ptr(tok_pos), _ptr(slots), _ptr(steps), _ptr(budgets), _ptr(stop_ids),
         _I(n_stop), _ptr(out_tokens), _ptr(cursor), _I(out_tokens.shape[0]), _I(n), _stream()), "decode_advance")
+
+
+# ---------------------------------------------------------------------------------------------- fused skinny products
+
+SKINNY_MAX_ROWS = 16
+EPI_PLAIN, EPI_RESIDUAL, EPI_SWIGLU, EPI_QKV = 0, 1, 2, 3
+
+
+class _SkinnyArgs(ctypes.Structure):
+    _fields_ = [
+        ("w", _P), ("bias", _P), ("n", _I), ("k", _I), ("ldw", _I), ("m", _I),
+        ("x", _P), ("ldx", _I), ("hidden", _P), ("norm_w", _P), ("eps", _F),
+        ("out", _P), ("ldo", _I), ("out_f32", _I), ("residual", _P), ("inter", _I),
+        ("n_heads", _I), ("kv_heads", _I), ("head_dim", _I), ("rot_dim", _I), ("write_cache", _I),
+        ("inv_freq", _P), ("tok_pos", _P), ("tok_seq", _P), ("slots", _P), ("q_out", _P), ("kv_base", _P),
+        ("table", _P), ("page_elems", _LL), ("table_stride", _I), ("err", _P),
+    ]
+
+
+def skinny_gemm_takes(m: int, weight: torch.Tensor) -> bool:
+    """Whether the fused weight-streaming kernels take `m` token rows against `weight` [N, K] (bf16)."""
+    return (1 <= m <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
+            and weight.stride(0) % 8 == 0 and weight.stride(1) == 1
+            and 8 * (2 if m > 8 else 1) * (weight.shape[1] + 64) * 2 < 200 * 1024)
+
+
+def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,
+                hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None) -> None:
+    """One fused product for up to 16 token rows. Input rows are either `x` [m, K] bf16, or the float32 residual
+    stream `hidden` [m, K] normalised on the fly with `norm_weight`, `eps`. See csrc/skinny_gemm.cu for the epilogues.
+    qkv (EPI_QKV): dict(n_heads, site=KvSiteArgs, inv_freq, rot_dim, tok_pos, tok_seq, slots, q_out, write_cache, err)."""
+    _dev("weight", weight, torch.bfloat16, contiguous=False)
+    a = _SkinnyArgs()
+    a.w, a.n, a.k, a.ldw = weight.data_ptr(), weight.shape[0], weight.shape[1], weight.stride(0)
+    if bias is not None:
+        _dev("bias", bias, torch.bfloat16)
+        a.bias = bias.data_ptr()
+    norm = hidden is not None
+    if norm:
+        _dev("hidden", hidden, torch.float32)
+        _dev("norm_weight", norm_weight, torch.bfloat16)
+        if hidden.shape[1] != a.k or norm_weight.numel() != a.k:
+            raise KernelError("skinny_gemm: hidden/norm_weight widths do not match the weight's K")
+        a.hidden, a.norm_w, a.eps, a.m = hidden.data_ptr(), norm_weight.data_ptr(), eps, hidden.shape[0]
+    else:
+        _dev("x", x, torch.bfloat16, contiguous=False)
+        if x.shape[1] != a.k or x.stride(1) != 1:
+            raise KernelError("skinny_gemm: x width does not match the weight's K")
+        a.x, a.ldx, a.m = x.data_ptr(), x.stride(0), x.shape[0]
+    if epilogue == EPI_PLAIN:
+        _dev("out", out, None, contiguous=False)
+        if out.shape != (a.m, a.n) or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError("skinny_gemm: out must be [m, N] bf16 or float32")
+        a.out, a.ldo, a.out_f32 = out.data_ptr(), out.stride(0), int(out.dtype == torch.float32)
+    elif epilogue == EPI_RESIDUAL:
+        _dev("residual", residual, torch.float32)
+        if residual.shape != (a.m, a.n):
+            raise KernelError("skinny_gemm: residual must be [m, N] float32")
+        a.residual = residual.data_ptr()
+    elif epilogue == EPI_SWIGLU:
+        _dev("out", out, torch.bfloat16)
+        a.inter = a.n // 2
+        if out.shape != (a.m, a.inter):
+            raise KernelError("skinny_gemm: out must be [m, N / 2] bf16")
+        a.out, a.ldo = out.data_ptr(), out.stride(0)
+    elif epilogue == EPI_QKV:
+        site = qkv["site"]
+        _dev("q_out", qkv["q_out"], torch.bfloat16)
+        _dev("cache", site.storage, torch.bfloat16)
+        a.n_heads, a.kv_heads, a.head_dim = qkv["n_heads"], site.kv_heads, site.head_dim
+        a.rot_dim, a.write_cache = qkv["rot_dim"], int(bool(qkv["write_cache"]))
+        a.inv_freq = 0 if qkv["inv_freq"] is None else qkv["inv_freq"].data_ptr()
+        a.tok_pos, a.tok_seq, a.slots = qkv["tok_pos"].data_ptr(), qkv["tok_seq"].data_ptr(), qkv["slots"].data_ptr()
+        a.q_out, a.kv_base, a.table = qkv["q_out"].data_ptr(), site.storage.data_ptr(), site.table.data_ptr()
+        a.page_elems, a.table_stride, a.err = site.page_elems, site.table_stride, qkv["err"].data_ptr()
+        if qkv["q_out"].shape != (a.m, a.n_heads * a.head_dim):
+            raise KernelError("skinny_gemm: q_out must be [m, n_heads * head_dim]")
+    else:
+        raise KernelError(f"skinny_gemm: unknown epilogue {epilogue}")
+    code = library("skinny_gemm").qf_skinny_gemm(_I(epilogue), _I(int(norm)), ctypes.byref(a), _stream())
+    if code == 1:  # cudaErrorInvalidValue: a shape the kernel does not take
+        raise KernelError(f"skinny_gemm: shape m={a.m} n={a.n} k={a.k} (epilogue {epilogue}) is not supported; "
+                          "use the unfused kernels")
+    _check(code, "skinny_gemm")
+
+
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
+    """hidden (float32) += delta, in place."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("delta", delta)
+    if delta.shape != hidden.shape:
+        raise KernelError("residual_add: shapes differ")
+    _check(library("norm").qf_residual_add(_I(_is_bf16(delta.dtype)), _ptr(hidden), _ptr(delta), _LL(hidden.numel()),
+                                           _stream()), "residual_add")

@@ -73,7 +73,7 @@ class GqaAttention(Mixer):
         if dtype == torch.float32:
             libs.add("gemm_f32")
         elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
-            libs |= {"attention_decode", "attention_prefill"}
+            libs |= {"attention_decode", "attention_prefill", "skinny_gemm"}
         return libs
 
     def cache_need(self):
@@ -114,6 +114,30 @@ class GqaAttention(Mixer):
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
                                   ctx.max_q_len, self.scale, self.window, ctx.err)
         return ops.linear(attended, self.o_weight, self.o_bias_t)
+
+    # ---- the fused form for decode steps of a few sequences: three kernels per layer instead of seven
+    def fused_takes(self, ctx) -> bool:
+        if not (ctx.attention == "auto" and ctx.is_decode and ctx.dtype == torch.bfloat16
+                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.out_bias):
+            return False
+        rotary = self.position.fused_rotary() if self.position is not None else None
+        if self.position is not None and (rotary is None or rotary[1] != self.head_dim):
+            return False
+        return (ops.skinny_gemm_takes(ctx.n_tokens, self.qkv_weight) and ops.skinny_gemm_takes(ctx.n_tokens, self.o_weight))
+
+    def fused_forward(self, hidden, rms, ctx, site, writes_cache):
+        n = hidden.shape[0]
+        inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
+        args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
+        q = torch.empty((n, self.q_width), dtype=torch.bfloat16, device=hidden.device)
+        ops.skinny_gemm(ops.EPI_QKV, self.qkv_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1],
+                        bias=self.qkv_bias_t,
+                        qkv=dict(n_heads=self.n_heads, site=args, inv_freq=inv_freq, rot_dim=rot_dim, tok_pos=ctx.tok_pos,
+                                 tok_seq=ctx.tok_seq, slots=ctx.slots, q_out=q, write_cache=writes_cache, err=ctx.err))
+        attended = torch.empty_like(q)
+        ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                             self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
+        ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
 
     def decode_splits(self, ctx) -> int:
         """How many blocks share one (sequence, kv head): enough to fill the GPU about twice, at most one per page

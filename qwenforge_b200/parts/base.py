@@ -25,6 +25,8 @@ Interfaces by role (T = tokens of the step, W = model width):
                  apply(q [T, NH, D], k [T, KVH, D], ctx) -> None    in place, when there is no fused form
   Block          forward(hidden, delta, ctx, site, writes_cache) -> delta
                  arranges norms, mixer and feed-forward around the residual stream `hidden`.
+Mixers and feed-forwards may also offer a fused form for steps of a few tokens (`fused_takes`, `fused_forward`):
+it applies the preceding RMSNorm in its own first kernel and adds its result to `hidden` in place.
 """
 from __future__ import annotations
 
@@ -84,6 +86,10 @@ class Norm(Part):
     def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError
 
+    def fused_rms(self):
+        """(weight, eps) if this norm is a plain RMSNorm that a following kernel may apply in its prologue, else None."""
+        return None
+
 
 class Mixer(Part):
     def cache_need(self):
@@ -92,9 +98,24 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, site, writes_cache: bool) -> torch.Tensor:
         raise NotImplementedError
 
+    # Optional fast form for steps of a few tokens: the part applies the preceding RMSNorm itself and adds its
+    # output to the residual stream in place (hidden += mixer(rmsnorm(hidden))). A block uses it when
+    # `fused_takes(ctx)` is true and its norm has a `fused_rms()` form.
+    def fused_takes(self, ctx) -> bool:
+        return False
+
+    def fused_forward(self, hidden: torch.Tensor, rms, ctx, site, writes_cache: bool) -> None:
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+    def fused_takes(self, ctx) -> bool:
+        return False
+
+    def fused_forward(self, hidden: torch.Tensor, rms, ctx) -> None:
         raise NotImplementedError
 
 

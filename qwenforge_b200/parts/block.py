@@ -5,6 +5,7 @@ The stream `hidden` is float32 and is updated in place; a part's output (`delta`
 the *next* norm's kernel, so a block takes the pending delta of the layer before it and returns its own."""
 from __future__ import annotations
 
+from .. import ops
 from .base import Part
 from .registry import build_part, register_part
 
@@ -24,8 +25,21 @@ class PreNormBlock(Part):
         return self.mixer.cache_need()
 
     def forward(self, hidden, delta, ctx, site, writes_cache):
-        x = self.mixer_norm.forward(hidden, delta)
-        delta = self.mixer.forward(x, ctx, site, writes_cache)
+        rms = self.mixer_norm.fused_rms()
+        if rms is not None and self.mixer.fused_takes(ctx):
+            if delta is not None:
+                ops.residual_add(hidden, delta)
+            self.mixer.fused_forward(hidden, rms, ctx, site, writes_cache)
+            delta = None
+        else:
+            x = self.mixer_norm.forward(hidden, delta)
+            delta = self.mixer.forward(x, ctx, site, writes_cache)
+        rms = self.feed_forward_norm.fused_rms()
+        if rms is not None and self.feed_forward.fused_takes(ctx):
+            if delta is not None:
+                ops.residual_add(hidden, delta)
+            self.feed_forward.fused_forward(hidden, rms, ctx)
+            return None
         x = self.feed_forward_norm.forward(hidden, delta)
         return self.feed_forward.forward(x, ctx)
 

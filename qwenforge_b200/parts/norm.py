@@ -36,5 +36,8 @@ class RmsNorm(Norm):
         ops.add_rms_norm(hidden, delta, self.weight, self.eps, out)
         return out
 
+    def fused_rms(self):
+        return self.weight, self.eps
+
 
 register_part("norm", "rms_norm", RmsNorm)

@@ -26,7 +26,7 @@ class SwiGlu(FeedForward):
         ]
 
     def kernel_libraries(self, dtype):
-        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else set())
+        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm"})
 
     def bind(self, tensors, dtype, device):
         self.gate_up_weight = torch.cat((tensors[self.file_name("gate_weight")], tensors[self.file_name("up_weight")]),
@@ -38,6 +38,17 @@ class SwiGlu(FeedForward):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         ops.swiglu(gate_up, act)
         return ops.linear(act, self.down_weight)
+
+    # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another
+    def fused_takes(self, ctx) -> bool:
+        return (ctx.dtype == torch.bfloat16 and ctx.attention == "auto" and self.inter % 8 == 0
+                and ops.skinny_gemm_takes(ctx.n_tokens, self.gate_up_weight)
+                and ops.skinny_gemm_takes(ctx.n_tokens, self.down_weight))
+
+    def fused_forward(self, hidden, rms, ctx):
+        act = torch.empty((hidden.shape[0], self.inter), dtype=torch.bfloat16, device=hidden.device)
+        ops.skinny_gemm(ops.EPI_SWIGLU, self.gate_up_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1], out=act)
+        ops.skinny_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden)
 
 
 register_part("feed_forward", "swiglu", SwiGlu)

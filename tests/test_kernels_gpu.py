@@ -372,3 +372,105 @@ def test_attention_decode_padding_and_far_key(ops):
                          16, ops.DecodeScratch(DEV), err_word())
     value = site.storage[page, 1, 0, off]
     assert max_err(out[0, :d], value) < 2e-2 and max_err(out[0, d:], value) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------------ fused skinny products
+
+def _rms_rows(hidden, weight, eps):
+    x = hidden.double()
+    return (x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * weight.double()).to(torch.bfloat16).double()
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(896, 896), (50, 72), (1152, 4864), (17, 8)])
+def test_skinny_gemm_plain_and_residual(ops, m, n, k):
+    g = torch.Generator().manual_seed(20)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV)
+    want = x.double() @ w.double().T + b.double()
+    bound = 2e-2 * max(1.0, float(want.abs().max()))
+    for dtype in (torch.bfloat16, torch.float32):
+        out = torch.empty(m, n, dtype=dtype, device=DEV)
+        ops.skinny_gemm(ops.EPI_PLAIN, w, x=x, bias=b, out=out)
+        assert max_err(out, want) <= (bound if dtype == torch.bfloat16 else bound / 20)
+    hidden = torch.randn(m, n, generator=g).to(DEV)
+    before = hidden.clone()
+    ops.skinny_gemm(ops.EPI_RESIDUAL, w, x=x, residual=hidden)
+    assert max_err(hidden, before.double() + x.double() @ w.double().T) <= bound / 20
+    # the norm prologue
+    stream = (torch.randn(m, k, generator=g) * 3).to(DEV)
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).to(DEV)
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.skinny_gemm(ops.EPI_PLAIN, w, hidden=stream, norm_weight=nw, eps=1e-5, out=out)
+    assert max_err(out, _rms_rows(stream, nw, 1e-5) @ w.double().T) <= bound / 10
+    # a row's result does not depend on the other rows of the call
+    if m > 1:
+        one = torch.empty(1, n, dtype=torch.float32, device=DEV)
+        ops.skinny_gemm(ops.EPI_PLAIN, w, hidden=stream[m - 1:], norm_weight=nw, eps=1e-5, out=one)
+        assert torch.equal(one[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,inter,k", [(2, 4864, 896), (8, 200, 120), (13, 24, 64)])
+def test_skinny_gemm_swiglu(ops, m, inter, k):
+    g = torch.Generator().manual_seed(21)
+    stream = torch.randn(m, k, generator=g).to(DEV)
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.skinny_gemm(ops.EPI_SWIGLU, w, hidden=stream, norm_weight=nw, eps=1e-6, out=out)
+    gu = _rms_rows(stream, nw, 1e-6) @ w.double().T
+    want = gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]
+    assert max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("m,nh,kvh,d,rotary", [(8, 14, 2, 64, True), (3, 4, 4, 32, True), (16, 8, 1, 128, False), (1, 6, 3, 96, True)])
+def test_skinny_gemm_qkv(ops, m, nh, kvh, d, rotary):
+    """The fused projection + bias + rotation + cache write against the unfused references."""
+    g = torch.Generator().manual_seed(22)
+    k = 8 * 31
+    stream = torch.randn(m, k, generator=g).to(DEV)
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).to(DEV)
+    n = (nh + 2 * kvh) * d
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV)
+    site_a, site_b = FakeSite(m, 400, kvh, d, torch.bfloat16), FakeSite(m, 400, kvh, d, torch.bfloat16)
+    site_b.table = site_a.table
+    positions = [(37 * i + 63) % 390 for i in range(m)]
+    slots = [(m - 1 - i) if i != 1 else -1 for i in range(m)]
+    tok_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV) if rotary else None
+    q1 = torch.empty(m, nh * d, dtype=torch.bfloat16, device=DEV)
+    e = err_word()
+    ops.skinny_gemm(ops.EPI_QKV, w, hidden=stream, norm_weight=nw, eps=1e-6, bias=b,
+                    qkv=dict(n_heads=nh, site=ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d), inv_freq=inv_freq,
+                             rot_dim=d if rotary else 0, tok_pos=tok_pos, tok_seq=tok_seq, slots=slots_t, q_out=q1,
+                             write_cache=True, err=e))
+    qkv = (_rms_rows(stream, nw, 1e-6) @ w.double().T + b.double()).to(torch.float32)
+    q2 = torch.empty(m, nh * d, dtype=torch.float32, device=DEV)
+    site_b.storage = site_b.storage.float()
+    ref.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, d if rotary else 0, nh, q2, site_b, True, None)
+    assert int(e) == 0
+    assert max_err(q1, q2) <= 3e-2 * max(1.0, float(q2.abs().max()))
+    assert max_err(site_a.storage, site_b.storage) <= 3e-2 * max(1.0, float(site_b.storage.abs().max()))
+    assert float(site_a.storage.float().abs().sum()) > 0
+
+
+def test_skinny_gemm_refuses_what_it_does_not_take(ops):
+    w = torch.zeros(32, 20, dtype=torch.bfloat16, device=DEV)       # K not a multiple of 8
+    x = torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV)
+    assert not ops.skinny_gemm_takes(2, w)
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.skinny_gemm(ops.EPI_PLAIN, w, x=x, out=torch.empty(2, 32, dtype=torch.bfloat16, device=DEV))
+    assert not ops.skinny_gemm_takes(17, torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV))
+
+
+def test_residual_add(ops):
+    g = torch.Generator().manual_seed(23)
+    h = torch.randn(5, 77, generator=g).to(DEV)
+    d = torch.randn(5, 77, generator=g).to(torch.bfloat16).to(DEV)
+    want = h + d.float()
+    ops.residual_add(h, d)
+    assert torch.equal(h, want)
