@@ -131,6 +131,9 @@ def _compile(name: str) -> Path:
         partial.unlink(missing_ok=True)
         raise KernelLibraryError(f"nvcc failed on {source.name} (exit {process.returncode}):\n{output}")
     os.replace(partial, target)
+    for stale in out_dir.glob(f"{name}.*.so"):  # builds of earlier versions of this source
+        if stale != target:
+            stale.unlink(missing_ok=True)
     _say(f"compiled {source.name} in {time.time() - started:.1f} s")
     return target
 

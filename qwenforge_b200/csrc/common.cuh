@@ -17,6 +17,7 @@ typedef __nv_bfloat16 bf16;
 #define QF_ERR_TOKEN_RANGE 1   // a token id outside the embedding table
 #define QF_ERR_NO_PAGE 2       // a position whose cache page is not allocated
 #define QF_ERR_ROW_RANGE 4     // a gathered row index outside the activations
+#define QF_ERR_COPY_TIMEOUT 8  // a bulk copy did not complete within the wait limit
 
 template <typename T> struct Num;
 template <> struct Num<float> {
@@ -29,6 +30,11 @@ template <> struct Num<bf16> {
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ uint32_t warp_sum_u32(uint32_t v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
@@ -76,4 +82,28 @@ __device__ __forceinline__ T* kv_row(const KvSite<T>& s, int slot, int pos, int 
     if (page < 0) return nullptr;
     return s.base + (long long)page * s.page_elems +
            ((long long)(which * s.kv_heads + h) * QF_PAGE + (pos % QF_PAGE)) * s.head_dim;
+}
+
+// Programmatic dependent launch. A kernel launched with `launch_pdl` may start while the kernel before it on the
+// stream is still running; it must call grid_dependency_wait() before it reads anything that kernel wrote or
+// writes anything at all. What it does before that call (fetching weights, which no kernel writes) overlaps the
+// previous kernel's tail. grid_launch_dependents() lets the NEXT kernel start its own preamble early. Both are
+// no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
 }

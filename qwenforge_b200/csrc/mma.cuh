@@ -37,3 +37,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 #define QF_NEG_BIG (-1.0e30f)
+
+// ---- bulk asynchronous copies (the TMA engine in its untiled form) completing on a shared-memory barrier.
+// One thread announces the expected bytes, any threads issue copies of multiples of 16 bytes between 16-byte
+// aligned addresses, and every thread that needs the data waits for the barrier's phase to flip. The wait is
+// bounded: if the phase has not flipped after QF_BULK_WAIT_TRIES polls the caller gets false and reports it.
+#define QF_BULK_WAIT_TRIES 2000000
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (int i = 0; i < QF_BULK_WAIT_TRIES; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
