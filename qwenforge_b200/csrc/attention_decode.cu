@@ -2,34 +2,37 @@
 // cache; the key range of every (sequence, kv head) is cut into `n_splits` runs of whole pages that
 // separate blocks reduce at once, so that a batch of a few sequences still fills the GPU.
 //
-// A block (4 warps) serves one (sequence, kv head, chunk of up to 16 query heads of the group, split).
-// The query heads of the group are the 16 rows of an m16n8k16 tensor-core tile, so keys and values are
-// read once for the whole group. Pages (64 positions: 64 x D keys, 64 x D values) stream through shared
-// memory with double-buffered cp.async; each warp takes 16 keys of a page: S = Q K^T, online softmax in
-// float32 (base-2 exponentials, the scale folded in), O += P V. Warps are merged in shared memory.
-// With one split the block writes the output; otherwise it writes (max, sum, O) partials to scratch and
-// takes a ticket: the block that draws the last ticket of its (sequence, kv head, chunk) merges all
-// partials and resets the ticket counter. No block waits for another.
+// A block serves one (sequence, kv head, chunk of up to 16 query heads of the group, split). The query heads of
+// the group are the 16 rows of an m16n8k16 tensor-core tile, so keys and values are read once for the whole
+// group. Each WARP works alone on whole pages (64 positions: 64 x D keys, 64 x D values): the page arrives in the
+// warp's own shared-memory buffer by 16-byte asynchronous copies into padded rows (bulk copies of single 128-byte
+// rows were measured slower: a page is too many small requests for the copy engine), then S = Q K^T, online
+// softmax in float32 (base-2 exponentials, the scale folded in), O += P V. With eight warps a block has eight
+// pages in flight and no block-wide barrier inside the loop. The warps are merged in shared memory at the end.
+// With one split the block writes the output; otherwise it writes (max, sum, O) partials to scratch and takes a
+// ticket: the block that draws the last ticket of its (sequence, kv head, chunk) merges all partials and resets
+// the ticket counter. No block waits for another. (Merging the splits of a thread-block cluster through
+// distributed shared memory instead was measured slower at these sizes: 19.8 against 14.4 microseconds.)
+// The kernel is launched as a programmatic dependent of the kernel before it.
 #include "mma.cuh"
 
-#define DEC_WARPS 4
-#define DEC_THREADS (DEC_WARPS * 32)
-
-template <int D>
-__global__ void __launch_bounds__(DEC_THREADS)
+template <int D, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                     const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                     int chunks, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
                     float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
+    constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
     constexpr int LD = D + 8;           // padded shared-memory row (bf16 elements): conflict-free ldmatrix
     constexpr int KS = D / 16;          // k-steps of Q K^T
     constexpr int NT = D / 8;           // n-tiles of P V
+    constexpr int PAGE_BYTES = 2 * QF_PAGE * LD * 2;  // one warp's buffer: keys then values of a page
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);             // [2][64][LD]
-    bf16* v_s = k_s + 2 * QF_PAGE * LD;                        // [2][64][LD]
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ int ticket_s;
 
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int split = blockIdx.x, seq = blockIdx.z;
     const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
     const int G = n_heads / site.kv_heads;
@@ -72,113 +75,122 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
+    // ---- every warp works alone on whole pages: page p_begin + warp, then + WARPS, ...
+    bf16* kb = reinterpret_cast<bf16*>(smem_raw + (size_t)warp * PAGE_BYTES);
+    bf16* vb = kb + QF_PAGE * LD;
     const int* table_row = site.table + (long long)slot * site.table_stride;
-    auto load_page = [&](int page_index, int buf) {
-        const int page = table_row[page_index];
-        const bool held = page >= 0;
-        if (!held && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
-        const bf16* kp = site.base + (long long)(held ? page : 0) * site.page_elems + (long long)kvh * QF_PAGE * D;
-        const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
-        constexpr int CH = D / 8;  // 16-byte chunks per row
-        for (int i = threadIdx.x; i < QF_PAGE * CH; i += DEC_THREADS) {
-            const int r = i / CH, c = (i % CH) * 8;
-            cp_async_16(k_s + ((size_t)buf * QF_PAGE + r) * LD + c, kp + r * D + c, held);
-            cp_async_16(v_s + ((size_t)buf * QF_PAGE + r) * LD + c, vp + r * D + c, held);
+    for (int p = p_begin + warp; p < p_end; p += DEC_WARPS) {
+        const int page = table_row[p];
+        if (page < 0) {
+            if (lane == 0) atomicOr(err, QF_ERR_NO_PAGE);
+            continue;
         }
-    };
-
-    if (p_begin < p_end) load_page(p_begin, 0);
-    cp_async_commit();
-    for (int p = p_begin; p < p_end; ++p) {
-        const int buf = (p - p_begin) & 1;
-        if (p + 1 < p_end) load_page(p + 1, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const bf16* kb = k_s + (size_t)buf * QF_PAGE * LD;
-        const bf16* vb = v_s + (size_t)buf * QF_PAGE * LD;
-        const int key0 = p * QF_PAGE + 16 * warp;  // this warp's 16 keys
-        if (key0 < L && key0 + 16 > lo) {
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const bf16* kp = site.base + (long long)page * site.page_elems + (long long)kvh * QF_PAGE * D;
+        const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
+        {   // the page's 2 x 64 rows in 16-byte asynchronous copies, rows padded in shared memory
+            constexpr int CH = D / 8;  // chunks per row
+#pragma unroll 4
+            for (int i = lane; i < QF_PAGE * CH; i += 32) {
+                const int r = i / CH, c = (i % CH) * 8;
+                cp_async_16(kb + (size_t)r * LD + c, kp + (size_t)r * D + c, true);
+                cp_async_16(vb + (size_t)r * LD + c, vp + (size_t)r * D + c, true);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();  // each lane waited for its own copies; together the page is complete
+        }
+        const int key0 = p * QF_PAGE;
+        float s[8][4];
 #pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
+        for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int t2 = 0; t2 < 4; ++t2) {  // 16 keys per ldmatrix.x4
                 uint32_t kf[4];
-                ldmatrix_x4(kf, kb + (size_t)(16 * warp + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
-                mma_bf16_16816(s[0], qa[ks], kf[0], kf[1]);
-                mma_bf16_16816(s[1], qa[ks], kf[2], kf[3]);
+                ldmatrix_x4(kf, kb + (size_t)(16 * t2 + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(s[2 * t2], qa[ks], kf[0], kf[1]);
+                mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
             }
-            float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
-            bool ok[2][2];
+        }
+        const bool full = key0 >= lo && key0 + QF_PAGE <= L;  // every key of the page is visible
+        float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+        for (int t = 0; t < 8; ++t) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
-                    ok[t][e] = kj >= lo && kj < L;
-                    s[t][e] = ok[t][e] ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                    s[t][2 + e] = ok[t][e] ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
-                    mx[0] = fmaxf(mx[0], s[t][e]);
-                    mx[1] = fmaxf(mx[1], s[t][2 + e]);
-                }
+            for (int e = 0; e < 2; ++e) {
+                const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
+                const bool ok = full || (kj >= lo && kj < L);
+                s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
+                s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                mx[0] = fmaxf(mx[0], s[t][e]);
+                mx[1] = fmaxf(mx[1], s[t][2 + e]);
             }
-            float corr[2], sum[2] = {0.f, 0.f};
+        }
+        float corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m_run[r], mx[r]);
-                corr[r] = exp2f(m_run[r] - m_new);
-                m_run[r] = m_new;
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r] = exp2f(m_run[r] - m_new);
+            m_run[r] = m_new;
+        }
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                // a masked score is QF_NEG_BIG: its weight is 0 even while the running maximum is QF_NEG_BIG too
+                s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
+                s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
+                sum[0] += s[t][e];
+                sum[1] += s[t][2 + e];
             }
+        }
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+        for (int r = 0; r < 2; ++r) {
+            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+            l_run[r] = l_run[r] * corr[r] + sum[r];
+        }
+        if (corr[0] != 1.f || corr[1] != 1.f) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    s[t][e] = ok[t][e] ? exp2f(s[t][e] - m_run[0]) : 0.f;
-                    s[t][2 + e] = ok[t][e] ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
-                    sum[0] += s[t][e];
-                    sum[1] += s[t][2 + e];
-                }
+            for (int nt = 0; nt < NT; ++nt) {
+                o[nt][0] *= corr[0];
+                o[nt][1] *= corr[0];
+                o[nt][2] *= corr[1];
+                o[nt][3] *= corr[1];
             }
+        }
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-                l_run[r] = l_run[r] * corr[r] + sum[r];
-            }
-            uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
-                              pack_bf16(s[1][2], s[1][3])};
+        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+            uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                              pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
 #pragma unroll
             for (int nt = 0; nt < NT; nt += 2) {
                 uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vb + (size_t)(16 * warp + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    o[nt + h][0] *= corr[0];
-                    o[nt + h][1] *= corr[0];
-                    o[nt + h][2] *= corr[1];
-                    o[nt + h][3] *= corr[1];
-                }
+                ldmatrix_x4_trans(vf, vb + (size_t)(16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
                 mma_bf16_16816(o[nt], pa, vf[0], vf[1]);
                 mma_bf16_16816(o[nt + 1], pa, vf[2], vf[3]);
             }
         }
-        __syncthreads();  // the buffer may be refilled by the next iteration's prefetch
+        __syncwarp();  // every lane has read the page before the next copies overwrite it
     }
-    cp_async_wait<0>();
 
-    // ---- merge the four warps: common maximum, rescale, add up in shared memory
+    // ---- merge the warps: common maximum, rescale, add up in shared memory in warp order
     if ((lane & 3) == 0) {
         m_s[warp][lane >> 2] = m_run[0];
         m_s[warp][(lane >> 2) + 8] = m_run[1];
     }
     __syncthreads();
-    float* o_s = reinterpret_cast<float*>(smem_raw);  // [16][D] float32, over the key buffers (all reads are done)
+    float* o_s = reinterpret_cast<float*>(smem_raw);  // [16][D] float32, over warp 0's page buffer (all reads are done)
     float m_all[2], f[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
-        m_all[r] = fmaxf(fmaxf(m_s[0][row], m_s[1][row]), fmaxf(m_s[2][row], m_s[3][row]));
+        m_all[r] = m_s[0][row];
+#pragma unroll
+        for (int w = 1; w < DEC_WARPS; ++w) m_all[r] = fmaxf(m_all[r], m_s[w][row]);
         f[r] = exp2f(m_run[r] - m_all[r]);
     }
     if ((lane & 3) == 0) {
@@ -209,7 +221,9 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     if (n_splits == 1) {
         for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
             const int r = i / D;
-            const float l = l_s[0][r] + l_s[1][r] + l_s[2][r] + l_s[3][r];
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
             out_row[i] = __float2bfloat16_rn(l > 0.f ? o_s[i] / l : 0.f);
         }
         return;
@@ -221,8 +235,11 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     }
     if (threadIdx.x < n_g) {
         const int r = threadIdx.x;
-        const float m = fmaxf(fmaxf(m_s[0][r], m_s[1][r]), fmaxf(m_s[2][r], m_s[3][r]));
-        const float l = l_s[0][r] + l_s[1][r] + l_s[2][r] + l_s[3][r];
+        float m = m_s[0][r], l = 0.f;
+#pragma unroll
+        for (int w = 1; w < DEC_WARPS; ++w) m = fmaxf(m, m_s[w][r]);
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
         part_ml[(part_row0 + (size_t)r * n_splits + split) * 2] = m;
         part_ml[(part_row0 + (size_t)r * n_splits + split) * 2 + 1] = l;
     }
@@ -278,16 +295,16 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
                   float scale, int window, int n_splits, float* part_o, float* part_ml, int* counters, int* err,
                   cudaStream_t stream) {
+    constexpr int WARPS = D <= 64 ? 8 : 4;  // one page buffer per warp: 18 KB at D = 64, 35 KB at D = 128
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
-    const size_t smem = (size_t)4 * QF_PAGE * (D + 8) * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = (size_t)WARPS * 2 * QF_PAGE * (D + 8) * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     dim3 grid(n_splits, kv_heads * chunks, n_seqs);
-    decode_split_kernel<D><<<grid, DEC_THREADS, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site,
-                                                                n_heads, chunks, scale * 1.4426950408889634f, window,
-                                                                n_splits, part_o, part_ml, counters, err);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(decode_split_kernel<D, WARPS>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)q, (bf16*)out,
+                           cu_q, tok_pos, slots, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
+                           part_o, part_ml, counters, err);
 }
 
 // Scratch (used when n_splits > 1): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml float32

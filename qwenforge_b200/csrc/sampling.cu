@@ -26,20 +26,27 @@ __device__ __forceinline__ uint32_t row_key(unsigned long long seed, long long s
     return key;
 }
 
-__global__ void __launch_bounds__(1024)
+// One block scans a chunk of one row's vocabulary; with several chunks per row the blocks leave their best
+// (score, id) in scratch and take a ticket, and the block that draws the row's last ticket picks the row's best
+// and resets the ticket counter. Ties go to the lowest id at every level, so the result does not depend on `chunks`.
+__global__ void __launch_bounds__(256)
 sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride, float temperature,
               unsigned long long seed, const long long* __restrict__ seq_ids, const int* __restrict__ steps,
-              int* __restrict__ out) {
-    __shared__ float best_v[32];
-    __shared__ int best_i[32];
-    const int row = blockIdx.x;
+              int* __restrict__ out, int chunks, float* __restrict__ part_v, int* __restrict__ part_i,
+              int* __restrict__ counters) {
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    __shared__ int ticket;
+    const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * row_stride;
     const bool sample = temperature > 0.f;
     const uint32_t key = sample ? row_key(seed, seq_ids[row], steps[row]) : 0u;
     const float inv_t = sample ? 1.0f / temperature : 1.0f;
+    const int per = (vocab + chunks - 1) / chunks;
+    const int begin = chunk * per, end = min(vocab, begin + per);
     float bv = -FLT_MAX;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float s = x[i];
         if (sample) {
             const uint32_t bits = mix32(key ^ mix32((uint32_t)i ^ 0x27D4EB2Fu));
@@ -51,11 +58,12 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
             bi = i;
         }
     }
+    auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) {
+        if (better(ov, oi, bv, bi)) {
             bv = ov;
             bi = oi;
         }
@@ -66,28 +74,64 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
         best_i[warp] = bi;
     }
     __syncthreads();
-    if (warp == 0) {
-        const int nwarps = blockDim.x >> 5;
-        bv = lane < nwarps ? best_v[lane] : -FLT_MAX;
-        bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
+    if (warp != 0) return;
+    const int nwarps = blockDim.x >> 5;
+    bv = lane < nwarps ? best_v[lane] : -FLT_MAX;
+    bi = lane < nwarps ? best_i[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
-            }
+    for (int o = 4; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) {
+            bv = ov;
+            bi = oi;
         }
-        if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
     }
+    if (chunks == 1) {
+        if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+        return;
+    }
+    if (lane == 0) {
+        part_v[(size_t)row * chunks + chunk] = bv;
+        part_i[(size_t)row * chunks + chunk] = bi;
+        __threadfence();
+        ticket = atomicAdd(counters + row, 1);
+    }
+    __syncwarp();
+    if (ticket != chunks - 1) return;
+    __threadfence();
+    if (lane == 0) counters[row] = 0;
+    bv = -FLT_MAX;
+    bi = 0x7fffffff;
+    for (int c = lane; c < chunks; c += 32) {
+        const float v = __ldcg(part_v + (size_t)row * chunks + c);
+        const int i = __ldcg(part_i + (size_t)row * chunks + c);
+        if (better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
 }
 
 // logits: [rows][row_stride >= vocab] float32; seq_ids [rows] int64 and steps [rows] int32 are read only when sampling.
+// chunks > 1 needs scratch: part_v float32 [rows * chunks], part_i int32 [rows * chunks], counters int32 [rows], zero
+// before the first call (the kernel leaves them zero).
 QF_EXPORT int qf_sample(const float* logits, int rows, int vocab, long long row_stride, float temperature,
-                        unsigned long long seed, const long long* seq_ids, const int* steps, int* out,
-                        cudaStream_t stream) {
+                        unsigned long long seed, const long long* seq_ids, const int* steps, int* out, int chunks,
+                        float* part_v, int* part_i, int* counters, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, 1024, 0, stream>>>(logits, vocab, row_stride, temperature, seed, seq_ids, steps, out);
+    if (chunks < 1 || (chunks > 1 && (!part_v || !part_i || !counters))) return (int)cudaErrorInvalidValue;
+    sample_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, row_stride, temperature, seed, seq_ids, steps, out,
+                                                          chunks, part_v, part_i, counters);
     return (int)cudaGetLastError();
 }

@@ -7,12 +7,17 @@
 //             QKV      + bias, rotate q and k heads by position (float32 angles), q -> q_out, k and v -> cache pages
 //
 // The product runs on the tensor cores as out^T = W x^T: 16 weight rows are the M side of an m16n8k16 tile and
-// 8 token rows its N side, so no weight is touched twice and no shared-memory bandwidth is spent on it. A block
-// owns 16 weight rows; its warps split K in interleaved blocks of 32 and are summed in a fixed order. Each lane
-// loads 16 contiguous bytes of a weight row straight into the A fragments of two MMAs (the k order inside a
-// block of 32 is permuted, identically for the x fragments, which does not change the sum's terms).
-// The 16 rows of a block are chosen so that the two rows a lane holds (g and g + 8) are the pair its epilogue
+// 8 token rows its N side. The kernel is a weight streamer: a block puts ALL the weight bytes it will need in
+// flight at once (one bulk asynchronous copy per weight row, completing on a shared-memory barrier with a bounded
+// wait), prepares its token rows while they fly, and only then multiplies. How many 16-row tiles a block takes,
+// and over how many blocks of a thread-block cluster a tile's K is split, is planned on the host so that every SM
+// streams and all blocks are resident in one wave. Partial sums are added in a fixed order: first the warps of a
+// block, then the blocks of a cluster through distributed shared memory, so results do not change from run to run.
+// It is launched as a programmatic dependent: the weight copies start while the previous kernel still runs.
+// The 16 rows of a tile are chosen so that the two rows a lane holds (g and g + 8) are the pair its epilogue
 // needs: component j and j + D/2 of a head for the rotation, gate row i and up row i for SwiGLU.
+#include <cooperative_groups.h>
+
 #include "mma.cuh"
 
 enum { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
@@ -55,6 +60,7 @@ template <int EPI> __device__ __forceinline__ void tile_rows(const SkinnyArgs& a
         const int per_head = a.head_dim / 16, head = tile / per_head, j = (tile % per_head) * 8 + g;
         ra = head * a.head_dim + j;
         rb = ra + a.head_dim / 2;
+        if (head >= a.n_heads + 2 * a.kv_heads) ra = rb = -1;
     } else {
         ra = tile * 16 + g;
         rb = ra + 8;
@@ -63,104 +69,203 @@ template <int EPI> __device__ __forceinline__ void tile_rows(const SkinnyArgs& a
     }
 }
 
-template <int NT, int EPI, bool NORM, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) skinny_gemm_kernel(const SkinnyArgs a) {
+// Shared-memory geometry of one launch, computed on the host.
+struct SkinnyPlan {
+    int tpb;       // 16-row weight tiles per block
+    int ksplit;    // blocks of a cluster that share a tile, each taking a slice of K
+    int per;       // k-blocks (of 32) per slice
+    int stride_w;  // bytes between weight rows in shared memory (16 modulo 128: conflict-free ldmatrix)
+    int stride_x;  // bytes between token rows in shared memory (16 modulo 128: conflict-free fragment loads)
+};
+
+static inline int pad_to_16_mod_128(int bytes) { return bytes + ((16 - bytes % 128) + 128) % 128; }
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+
+template <int NT, int EPI, bool NORM>
+__global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const SkinnyArgs a, const SkinnyPlan plan) {
+    namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int MP = 8 * NT;  // token rows, padded
-    const int kp = (a.k + 31) / 32 * 32;
-    // row stride of x in shared memory: congruent to 64 bytes modulo 128, so that the eight (row, quarter) pairs
-    // of a quarter-warp's 16-byte loads fall on distinct banks
-    const int ldxs = kp + ((kp * 2) % 128 == 64 ? 0 : ((64 - (kp * 2) % 128 + 128) % 128) / 2);
-    bf16* x_s = reinterpret_cast<bf16*>(smem_raw);                       // [MP][ldxs]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)MP * ldxs * 2);  // [WARPS][NT * 4][32]
+    __shared__ __align__(8) uint64_t w_bar;
+    constexpr int MP = 8 * NT;
+    const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per;
+    unsigned char* w_s = smem_raw;                                           // [tpb * 16][stride_w]
+    const size_t w_bytes = max((size_t)tpb * 16 * plan.stride_w, (size_t)SK_WARPS * NT * 4 * 32 * 4);
+    unsigned char* x_s = w_s + w_bytes;                                      // [MP][stride_x]
+    // after the products, the weights' space holds the partial sums: red [SK_WARPS][NT * 4][32] floats
+    float* red = reinterpret_cast<float*>(w_s);
+    float* part = reinterpret_cast<float*>(x_s + (size_t)MP * plan.stride_x);  // [ksplit - 1][tpb][NT * 4][32]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    int ra, rb;
-    tile_rows<EPI>(a, blockIdx.x, g, ra, rb);
-    const bf16* wa = a.w + (size_t)max(ra, 0) * a.ldw;
-    const bf16* wb = a.w + (size_t)max(rb, 0) * a.ldw;
-    const int n_kb = kp / 32;
+    const int rank = ksplit > 1 ? (int)(blockIdx.x % ksplit) : 0;
+    const int block = blockIdx.x / ksplit;
+    const int n_kb = (a.k + 31) / 32;
+    const int kb_begin = rank * per, kb_count = max(0, min(per, n_kb - kb_begin));
+    const int k_begin = kb_begin * 32;
+    const int kslice = per * 32;
 
-    // ---- start the first weight loads, then prepare x while they fly
-    constexpr int UNROLL = 4;
-    uint4 fa[UNROLL], fb[UNROLL];
-    auto load_w = [&](int kb0) {
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int kb = kb0 + u * WARPS, kk = kb * 32 + t * 8;
-            const bool ok = kb < n_kb && kk < a.k;
-            fa[u] = (ok && ra >= 0) ? __ldcs(reinterpret_cast<const uint4*>(wa + kk)) : make_uint4(0, 0, 0, 0);
-            fb[u] = (ok && rb >= 0) ? __ldcs(reinterpret_cast<const uint4*>(wb + kk)) : make_uint4(0, 0, 0, 0);
+    // ---- all of this block's weights go in flight at once: one bulk asynchronous copy per weight row slice,
+    // issued by the lanes of warp 0 and completing on one shared-memory barrier
+    const int slice_bytes = max(0, min(per * 64, (a.k - k_begin) * 2));  // valid bytes of a row slice (multiple of 16)
+    if (warp == 0) {
+        if (lane == 0) mbar_init(&w_bar, 1);
+        __syncwarp();
+        uint32_t mine = 0;
+        for (int row = lane; row < tpb * 16; row += 32) {
+            int ra, rb;
+            tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
+            if (((row & 15) < 8 ? ra : rb) >= 0) mine += slice_bytes;
         }
-    };
-    load_w(warp);
+        const uint32_t total = warp_sum_u32(mine);
+        if (lane == 0) mbar_expect_tx(&w_bar, total);
+        __syncwarp();
+        if (slice_bytes > 0)
+            for (int row = lane; row < tpb * 16; row += 32) {
+                int ra, rb;
+                tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
+                const int grow = (row & 15) < 8 ? ra : rb;
+                if (grow >= 0)
+                    bulk_copy_g2s(w_s + (size_t)row * plan.stride_w, a.w + (size_t)grow * a.ldw + k_begin, slice_bytes, &w_bar);
+            }
+    } else {
+        // rows that do not exist, and the tail of a slice beyond K, must be zero: they meet zero token values
+        const int tail16 = (per * 64 - slice_bytes) / 16;
+        for (int row = warp - 1; row < tpb * 16; row += SK_WARPS - 1) {
+            int ra, rb;
+            tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
+            const bool exists = ((row & 15) < 8 ? ra : rb) >= 0;
+            const int first = exists ? slice_bytes / 16 : 0, count = exists ? tail16 : per * 4;
+            for (int c = lane; c < count; c += 32)
+                *reinterpret_cast<uint4*>(w_s + (size_t)row * plan.stride_w + (size_t)(first + c) * 16) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    grid_launch_dependents();
+    grid_dependency_wait();  // weights are nobody's output; everything below reads what earlier kernels wrote
 
+    // ---- this block's slice of the token rows, normalised on the way if asked
     if (NORM) {
-        for (int m = warp; m < MP; m += WARPS) {
-            bf16* dst = x_s + (size_t)m * ldxs;
+        for (int m = warp; m < MP; m += SK_WARPS) {
+            bf16* dst = reinterpret_cast<bf16*>(x_s + (size_t)m * plan.stride_x);
             if (m < a.m) {
-                const float* h = a.hidden + (size_t)m * a.k;
+                // the row is read in batches of independent 16-byte loads (a.k is a multiple of 8), so that the sum of
+                // squares costs a few memory round trips, not one per element
+                const float4* h4 = reinterpret_cast<const float4*>(a.hidden + (size_t)m * a.k);
+                const int n4 = a.k / 4;
                 float ss = 0.f;
-                for (int c = lane; c < a.k; c += 32) ss += h[c] * h[c];
+                float4 v[8];  // the first 1024 columns stay in registers for the second pass
+                for (int base = 0; base < n4; base += 32 * 8) {
+                    float4 u8[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int i = base + u * 32 + lane;
+                        u8[u] = i < n4 ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        ss += u8[u].x * u8[u].x + u8[u].y * u8[u].y + u8[u].z * u8[u].z + u8[u].w * u8[u].w;
+                        if (base == 0) v[u] = u8[u];
+                    }
+                }
                 ss = warp_sum(ss);
                 const float inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
-                for (int c = lane; c < kp; c += 32)
-                    dst[c] = c < a.k ? __float2bfloat16_rn(h[c] * inv * __bfloat162float(a.norm_w[c])) : __float2bfloat16_rn(0.f);
+                const float* h = a.hidden + (size_t)m * a.k;
+                // column c of the slice is column k_begin + c of the row; the lane handles float4 groups u * 32 + lane
+                for (int base = 0; base < kslice; base += 32 * 4 * 8) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int c = base + (u * 32 + lane) * 4, kk = k_begin + c;
+                        if (c >= kslice) continue;
+                        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                        uint2 wv = make_uint2(0u, 0u);
+                        if (kk < a.k) {
+                            x = (k_begin == 0 && base == 0) ? v[u] : *reinterpret_cast<const float4*>(h + kk);
+                            wv = *reinterpret_cast<const uint2*>(a.norm_w + kk);
+                        }
+                        const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv.x);
+                        const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
+                        uint2 o;
+                        o.x = pack_bf16(x.x * inv * __low2float(w01), x.y * inv * __high2float(w01));
+                        o.y = pack_bf16(x.z * inv * __low2float(w23), x.w * inv * __high2float(w23));
+                        *reinterpret_cast<uint2*>(dst + c) = o;
+                    }
+                }
             } else {
-                for (int c = lane; c < kp; c += 32) dst[c] = __float2bfloat16_rn(0.f);
+                for (int c = lane; c < kslice; c += 32) dst[c] = __float2bfloat16_rn(0.f);
             }
         }
     } else {
-        const int chunks = kp / 8;
-        for (int i = threadIdx.x; i < MP * chunks; i += WARPS * 32) {
+        const int chunks = kslice / 8;
+        for (int i = threadIdx.x; i < MP * chunks; i += SK_THREADS) {
             const int m = i / chunks, c = (i % chunks) * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < a.m && c < a.k) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + c);
-            *reinterpret_cast<uint4*>(x_s + (size_t)m * ldxs + c) = v;
+            if (m < a.m && k_begin + c < a.k) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + k_begin + c);
+            *reinterpret_cast<uint4*>(x_s + (size_t)m * plan.stride_x + c * 2) = v;
         }
     }
-    __syncthreads();
+    __syncthreads();  // the token rows are staged, and the barrier's initialisation is visible to every warp
+    if (!mbar_wait(&w_bar, 0) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
 
+    // ---- products: the warps of a tile take its k-blocks in turn
+    const int wpt = SK_WARPS / tpb, tile_local = warp / wpt, sub = warp % wpt;
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    for (int kb0 = warp; kb0 < n_kb; kb0 += UNROLL * WARPS) {
-        uint4 ca[UNROLL], cb[UNROLL];
+    const unsigned char* w_tile = w_s + (size_t)tile_local * 16 * plan.stride_w;
+    const unsigned char* a_addr = w_tile + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * plan.stride_w + (lane >> 4) * 16;
+    for (int kb = sub; kb < kb_count; kb += wpt) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            ca[u] = fa[u];
-            cb[u] = fb[u];
-        }
-        if (kb0 + UNROLL * WARPS < n_kb) load_w(kb0 + UNROLL * WARPS);
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int kb = kb0 + u * WARPS;
-            if (kb >= n_kb) break;
-            // A fragments: rows g / g + 8; k slots (2t, 2t+1) and (2t+8, 2t+9) take this lane's 8 values in two MMAs
-            const uint32_t a1[4] = {ca[u].x, cb[u].x, ca[u].y, cb[u].y};
-            const uint32_t a2[4] = {ca[u].z, cb[u].z, ca[u].w, cb[u].w};
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t af[4];
+            ldmatrix_x4(af, a_addr + (kb * 32 + ks * 16) * 2);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint4 xv = *reinterpret_cast<const uint4*>(x_s + (size_t)(8 * nt + g) * ldxs + kb * 32 + t * 8);
-                mma_bf16_16816(acc[nt], a1, xv.x, xv.y);
-                mma_bf16_16816(acc[nt], a2, xv.z, xv.w);
+                const unsigned char* xr = x_s + (size_t)(8 * nt + g) * plan.stride_x + (kb * 32 + ks * 16 + 2 * t) * 2;
+                mma_bf16_16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(xr), *reinterpret_cast<const uint32_t*>(xr + 16));
             }
         }
     }
-    // ---- sum the warps in a fixed order
+    // ---- sum the warps of each tile in a fixed order, then the blocks of the cluster in rank order
+    __syncthreads();  // every warp is done with the weights: their space becomes `red`
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) red[((size_t)warp * NT * 4 + nt * 4 + e) * 32 + lane] = acc[nt][e];
     __syncthreads();
-    if (warp != 0) return;
+    const bool tile_leader = sub == 0;
+    if (tile_leader) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float s = 0.f;
-            for (int w = 0; w < WARPS; ++w) s += red[((size_t)w * NT * 4 + nt * 4 + e) * 32 + lane];
-            acc[nt][e] = s;
+            for (int e = 0; e < 4; ++e) {
+                float s = 0.f;
+                for (int w = 0; w < wpt; ++w) s += red[((size_t)(warp + w) * NT * 4 + nt * 4 + e) * 32 + lane];
+                acc[nt][e] = s;
+            }
+    }
+    if (ksplit > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (rank > 0 && tile_leader) {
+            float* remote = cluster.map_shared_rank(part, 0) + ((size_t)(rank - 1) * tpb + tile_local) * NT * 4 * 32;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) remote[(nt * 4 + e) * 32 + lane] = acc[nt][e];
         }
+        cluster.sync();
+        if (rank > 0) return;
+        if (tile_leader) {
+            for (int r = 1; r < ksplit; ++r) {
+                const float* p = part + ((size_t)(r - 1) * tpb + tile_local) * NT * 4 * 32;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[nt][e] += p[(nt * 4 + e) * 32 + lane];
+            }
+        }
+    }
+    if (!tile_leader) return;
+    int ra, rb;
+    tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
     // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
     const float bias_a = (a.bias && ra >= 0) ? __bfloat162float(a.bias[ra]) : 0.f;
     const float bias_b = (a.bias && rb >= 0) ? __bfloat162float(a.bias[rb]) : 0.f;
@@ -188,7 +293,7 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_gemm_kernel(const SkinnyArg
             } else if (EPI == EPI_SWIGLU) {
                 if (ra >= 0)
                     reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(va / (1.0f + expf(-va)) * vb);
-            } else {  // EPI_QKV
+            } else if (ra >= 0) {  // EPI_QKV
                 const int D = a.head_dim, head = ra / D, j = ra % D;  // rb is component j + D/2 of the same head
                 float oa = va, ob = vb;
                 const int pos = a.tok_pos[m];
@@ -224,23 +329,75 @@ __global__ void __launch_bounds__(WARPS * 32) skinny_gemm_kernel(const SkinnyArg
     }
 }
 
-template <int NT, int EPI, bool NORM, int WARPS> static int launch_one(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
-    const int kp = (a.k + 31) / 32 * 32;
-    const int ldxs = kp + ((kp * 2) % 128 == 64 ? 0 : ((64 - (kp * 2) % 128 + 128) % 128) / 2);
-    const size_t smem = (size_t)8 * NT * ldxs * 2 + (size_t)WARPS * NT * 4 * 32 * 4;
-    if (smem > 220 * 1024) return (int)cudaErrorInvalidValue;
-    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM, WARPS>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static size_t plan_smem(const SkinnyPlan& p, int nt) {
+    size_t w = (size_t)p.tpb * 16 * p.stride_w;
+    const size_t red = (size_t)SK_WARPS * nt * 4 * 32 * 4;
+    if (w < red) w = red;  // the partial sums reuse the weights' space
+    return w + (size_t)8 * nt * p.stride_x + (size_t)(p.ksplit - 1) * p.tpb * nt * 4 * 32 * 4;
+}
+
+// How a product is cut into blocks: few tiles share their K among the blocks of a cluster so that every SM streams
+// weights; many tiles are grouped so that all blocks are resident at once (one wave) and the norm prologue is not
+// repeated more often than needed.
+static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
+    const int sms = 148, n_kb = (a.k + 31) / 32;
+    const size_t budget = 200 * 1024;
+    auto fill = [&](int tpb, int ksplit) {
+        p.tpb = tpb;
+        p.ksplit = ksplit;
+        p.per = (n_kb + ksplit - 1) / ksplit;
+        p.stride_w = pad_to_16_mod_128(p.per * 64);
+        p.stride_x = pad_to_16_mod_128(p.per * 64);
+        return plan_smem(p, nt);
+    };
+    if (tiles <= sms) {
+        int ksplit = 2 * sms / tiles;
+        if (ksplit > 4) ksplit = 4;
+        while (ksplit > 1 && (n_kb + ksplit - 1) / ksplit < 4) --ksplit;
+        if (ksplit == 3) ksplit = 2;
+        for (; ksplit <= 8; ksplit *= 2)
+            if (fill(1, ksplit) <= budget) return true;
+        return false;
+    }
+    for (int tpb = 1; tpb <= 8; tpb *= 2) {
+        const size_t smem = fill(tpb, 1);
+        if (smem > budget) break;
+        const int resident = (int)((227 * 1024) / (smem + 1024));
+        const int blocks = (tiles + tpb - 1) / tpb;
+        if (blocks <= sms * (resident > 3 ? 3 : resident)) return true;  // the launch bounds allow three blocks of 256 threads
+    }
+    for (int ksplit = 1; ksplit <= 8; ksplit *= 2)
+        if (fill(1, ksplit) <= budget) return true;
+    return false;
+}
+
+template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
+    SkinnyPlan p;
+    if (!make_plan(a, tiles, NT, p)) return (int)cudaErrorInvalidValue;
+    const size_t smem = plan_smem(p, NT);
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    skinny_gemm_kernel<NT, EPI, NORM, WARPS><<<tiles, WARPS * 32, smem, stream>>>(a);
-    return (int)cudaGetLastError();
+    const int blocks = (tiles + p.tpb - 1) / p.tpb;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(blocks * p.ksplit);
+    config.blockDim = dim3(SK_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = p.ksplit;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = p.ksplit > 1 ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&config, skinny_gemm_kernel<NT, EPI, NORM>, a, p);
 }
 
 template <int EPI, bool NORM> static int launch_epi(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
-    // few tiles: more warps per block share one tile's K; many tiles: fewer warps, more blocks per SM
-    const bool wide = tiles < 400;
-    if (a.m <= 8) return wide ? launch_one<1, EPI, NORM, 8>(a, tiles, stream) : launch_one<1, EPI, NORM, 4>(a, tiles, stream);
-    return wide ? launch_one<2, EPI, NORM, 8>(a, tiles, stream) : launch_one<2, EPI, NORM, 4>(a, tiles, stream);
+    if (a.m <= 8) return launch_one<1, EPI, NORM>(a, tiles, stream);
+    return launch_one<2, EPI, NORM>(a, tiles, stream);
 }
 
 // One entry for all variants. Shapes that the kernel does not take return cudaErrorInvalidValue; the caller

@@ -57,13 +57,14 @@ class DecodeGraph:
             n_seqs=rows, n_tokens=rows, max_q_len=1, max_kv_len=max_len, token_ids=self.token_ids,
             tok_seq=arange[:rows].clone(), tok_pos=self.tok_pos, slots=self.slots, cu_q=arange,
             want_rows=arange[:rows].clone(), err=model.err, dtype=model.dtype, attention=model.attention,
-            decode_scratch=model.decode_scratch)
+            decode_scratch=ops.DecodeScratch(device))  # the graph's own: its addresses are baked into the capture
+        self.sample_scratch = ops.SampleScratch()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
 
     def _one_step(self) -> None:
         logits = self.model.forward(self.ctx, self.cache)
-        self.sampler(logits, self.seq_ids, self.steps, out=self.sampled)
+        self.sampler(logits, self.seq_ids, self.steps, out=self.sampled, scratch=self.sample_scratch)
         ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
                            self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor)
 

@@ -23,11 +23,13 @@ _F = ctypes.c_float
 ERR_TOKEN_RANGE = 1
 ERR_NO_PAGE = 2
 ERR_ROW_RANGE = 4
+ERR_COPY_TIMEOUT = 8
 
 _ERROR_TEXT = {
     ERR_TOKEN_RANGE: "a token id lies outside the embedding table",
     ERR_NO_PAGE: "a position was read or written whose cache page is not held by its sequence",
     ERR_ROW_RANGE: "a wanted row lies outside the step's tokens",
+    ERR_COPY_TIMEOUT: "a bulk copy into shared memory did not complete within its wait limit",
 }
 
 
@@ -285,9 +287,29 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
                                            _I(two_i // 2), _stream()), "swiglu")
 
 
+class SampleScratch:
+    """Scratch of the sampling kernel when several blocks share a row: each block's best (score, id) and the
+    rows' ticket counters (kept zero between calls by the kernel itself)."""
+
+    def __init__(self):
+        self.part_v = self.part_i = self.counters = None
+
+    def ensure(self, rows: int, chunks: int, device) -> None:
+        if self.part_v is None or self.part_v.numel() < rows * chunks or self.part_v.device != device:
+            self.part_v = torch.empty(rows * chunks, dtype=torch.float32, device=device)
+            self.part_i = torch.empty(rows * chunks, dtype=torch.int32, device=device)
+        if self.counters is None or self.counters.numel() < rows or self.counters.device != device:
+            self.counters = torch.zeros(rows, dtype=torch.int32, device=device)
+
+
+_sample_scratch = SampleScratch()
+
+
 def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optional[torch.Tensor],
-           steps: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out[r] = argmax (temperature <= 0) or a Gumbel-max draw keyed by (seed, seq_ids[r], steps[r])."""
+           steps: Optional[torch.Tensor], out: torch.Tensor, scratch: Optional[SampleScratch] = None) -> None:
+    """out[r] = argmax (temperature <= 0) or a Gumbel-max draw keyed by (seed, seq_ids[r], steps[r]).
+    `scratch`: whoever captures the call into a CUDA graph passes a scratch of its own, which then lives as long
+    as the graph; other callers share one that grows as needed."""
     _dev("logits", logits, torch.float32, contiguous=False)
     _dev("out", out, torch.int32)
     if logits.dim() != 2 or logits.stride(1) != 1:
@@ -302,9 +324,17 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optiona
         _dev("steps", steps, torch.int32)
         if seq_ids.numel() != rows or steps.numel() != rows:
             raise KernelError("sample: seq_ids and steps must have one element per row")
+    # enough blocks to fill the GPU when there are few rows, at least 2048 tokens of the vocabulary each
+    chunks = max(1, min(-(-vocab // 2048), -(-296 // rows), 64))
+    scratch = scratch or _sample_scratch
+    if chunks > 1:
+        scratch.ensure(rows, chunks, logits.device)
     _check(library("sampling").qf_sample(_ptr(logits), _I(rows), _I(vocab), _LL(logits.stride(0)),
                                          _F(max(float(temperature), 0.0)), _ULL(seed & 0xFFFFFFFFFFFFFFFF),
-                                         _ptr(seq_ids), _ptr(steps), _ptr(out), _stream()), "sample")
+                                         _ptr(seq_ids), _ptr(steps), _ptr(out), _I(chunks),
+                                         _ptr(scratch.part_v if chunks > 1 else None),
+                                         _ptr(scratch.part_i if chunks > 1 else None),
+                                         _ptr(scratch.counters if chunks > 1 else None), _stream()), "sample")
 
 
 def decode_advance(sampled: torch.Tensor, token_ids: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
@@ -341,17 +371,29 @@ class _SkinnyArgs(ctypes.Structure):
     ]
 
 
+_own_err_words = {}
+
+
+def _err_word_for(device) -> torch.Tensor:
+    """A device error word for calls that bring none of their own (kernel tests)."""
+    key = str(device)
+    if key not in _own_err_words:
+        _own_err_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _own_err_words[key]
+
+
 def skinny_gemm_takes(m: int, weight: torch.Tensor) -> bool:
     """Whether the fused weight-streaming kernels take `m` token rows against `weight` [N, K] (bf16)."""
     return (1 <= m <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
             and weight.stride(0) % 8 == 0 and weight.stride(1) == 1
-            and 8 * (2 if m > 8 else 1) * (weight.shape[1] + 64) * 2 < 200 * 1024)
+            and (16 + 8 * (2 if m > 8 else 1)) * (weight.shape[1] // 8 + 128) * 2 + 16384 < 200 * 1024)
 
 
 def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,
                 hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                 bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None) -> None:
+                residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None,
+                err: Optional[torch.Tensor] = None) -> None:
     """One fused product for up to 16 token rows. Input rows are either `x` [m, K] bf16, or the float32 residual
     stream `hidden` [m, K] normalised on the fly with `norm_weight`, `eps`. See csrc/skinny_gemm.cu for the epilogues.
     qkv (EPI_QKV): dict(n_heads, site=KvSiteArgs, inv_freq, rot_dim, tok_pos, tok_seq, slots, q_out, write_cache, err)."""
@@ -403,6 +445,8 @@ def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor
             raise KernelError("skinny_gemm: q_out must be [m, n_heads * head_dim]")
     else:
         raise KernelError(f"skinny_gemm: unknown epilogue {epilogue}")
+    if not a.err:
+        a.err = (err if err is not None else _err_word_for(weight.device)).data_ptr()
     code = library("skinny_gemm").qf_skinny_gemm(_I(epilogue), _I(int(norm)), ctypes.byref(a), _stream())
     if code == 1:  # cudaErrorInvalidValue: a shape the kernel does not take
         raise KernelError(f"skinny_gemm: shape m={a.m} n={a.n} k={a.k} (epilogue {epilogue}) is not supported; "

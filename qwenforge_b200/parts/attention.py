@@ -140,12 +140,15 @@ class GqaAttention(Mixer):
         ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
 
     def decode_splits(self, ctx) -> int:
-        """How many blocks share one (sequence, kv head): enough to fill the GPU about twice, at most one per page
-        of the longest key range. Depends on the batch's shape only (it is fixed inside a captured graph)."""
+        """How many blocks share one (sequence, kv head): a block's warps take one page each (8 warps up to head size
+        64, else 4), so at most one split per that many pages, and no more splits than leave one block per SM: every
+        split costs a round of partial results. Depends on the batch's shape only (fixed inside a captured graph)."""
         span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + PAGE_TOKENS)
         pages = max(1, -(-span // PAGE_TOKENS))
+        warps = 8 if self.head_dim <= 64 else 4
         blocks = ctx.n_seqs * self.n_kv * (-(-(self.n_heads // self.n_kv) // 16))
-        return max(1, min(pages, 64, -(-2 * SM_COUNT // blocks)))
+        # measured on B200 (context 4096): batch 64 is fastest unsplit, batch 8 with 8 splits, batch 1 with 8 to 16
+        return max(1, min(-(-pages // warps), SM_COUNT // blocks, 64))
 
 
 register_part("mixer", "gqa_attention", GqaAttention)

@@ -33,9 +33,9 @@ class Sampler:
         return self.params.temperature <= 0.0
 
     def __call__(self, logits: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
-                 steps: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 steps: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, scratch=None) -> torch.Tensor:
         """logits float32 [rows, vocab] -> int32 [rows]; seq_ids int64 [rows] and steps int32 [rows] when sampling."""
         if out is None:
             out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        ops.sample(logits, self.params.temperature, self.params.seed, seq_ids, steps, out)
+        ops.sample(logits, self.params.temperature, self.params.seed, seq_ids, steps, out, scratch)
         return out

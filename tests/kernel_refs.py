@@ -128,7 +128,7 @@ def swiglu(gate_up, out):
     out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
 
-def sample(logits, temperature, seed, seq_ids, steps, out):
+def sample(logits, temperature, seed, seq_ids, steps, out, scratch=None):
     for r in range(logits.shape[0]):
         token, _ = plain.sample_token(logits[r].cpu(), temperature, seed,
                                       int(seq_ids[r]) if seq_ids is not None else 0,
