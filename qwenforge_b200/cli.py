@@ -1,0 +1,149 @@
+"""Command line of qwenforge_b200, in the manner of the reference's scripts/run_inference_benchmark.py:88-153.
+
+    python -m qwenforge_b200.cli --model DIR [--dtype bfloat16] [--suites decode_throughput,ttft_prefill] ...
+    python -m qwenforge_b200.cli --random-weights qwen2.5-0.5b --suites decode_throughput --decode-batch-sizes 1,8
+    python -m qwenforge_b200.cli --model DIR --prompt "some text" --max-new-tokens-decode 32
+
+Options that the reference has keep its names and meanings: --model, --device, --dtype, --attn-implementation,
+--local-files-only, --seed, --suites, --output-dir, --limit, --decode-batch-sizes, --ttft-batch-sizes,
+--max-new-tokens-decode, --max-new-tokens-ttft, --warmup-iters (global warm-up generate calls), --batch-warmup-iters
+(untimed calls per batch), --timed-repeats (timed calls per batch; the median is kept), --verbose-batches.
+The reference's text workloads and its scoring against a saved baseline are not part of this library: the suites
+here run on seeded random token ids of the lengths given by --decode-prompt-lens / --ttft-prompt-lens (defaults are
+the lengths of the reference's published runs). Added: --random-weights PRESET (writes a seeded random model to a
+temporary folder), --temperature, --stop-token-ids, --ignore-eos, --no-graphs, --prompt.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ALL_SUITES = ("decode_throughput", "ttft_prefill")
+
+
+def parse_args(argv=None) -> argparse.Namespace:
+    p = argparse.ArgumentParser(prog="qwenforge_b200", description=__doc__.split("\n\n")[0])
+    p.add_argument("--model", default=os.environ.get("HF_MODEL_NAME"), help="model folder (or hub id found in the local cache)")
+    p.add_argument("--random-weights", metavar="PRESET", default=None,
+                   help="use a seeded random model of a named size instead of --model (see config/presets)")
+    p.add_argument("--device", default=os.environ.get("HF_DEVICE", "cuda"))
+    p.add_argument("--dtype", choices=["auto", "bfloat16", "float32"], default="bfloat16")
+    p.add_argument("--attn-implementation", default="sdpa",
+                   help="'sdpa': the fastest attention kernels that take the shapes; anything else: the plain SIMT kernel")
+    p.add_argument("--local-files-only", action="store_true")
+    p.add_argument("--seed", type=int, default=0, help="weights (random mode), token ids and sampling")
+    p.add_argument("--suites", default=",".join(ALL_SUITES))
+    p.add_argument("--output-dir", default=None)
+    p.add_argument("--limit", type=int, default=None, help="first N cases of each suite")
+    p.add_argument("--decode-batch-sizes", default="1,2,4")
+    p.add_argument("--ttft-batch-sizes", default="1")
+    p.add_argument("--max-new-tokens-decode", type=int, default=128)
+    p.add_argument("--max-new-tokens-ttft", type=int, default=1)
+    p.add_argument("--decode-prompt-lens", default="183,212,245,275", help="prompt lengths of the decode suite")
+    p.add_argument("--ttft-prompt-lens", default="171,246,1000,1031,2175,3152,4719,7069")
+    p.add_argument("--warmup-iters", type=int, default=1)
+    p.add_argument("--batch-warmup-iters", type=int, default=0)
+    p.add_argument("--timed-repeats", type=int, default=1)
+    p.add_argument("--verbose-batches", action="store_true")
+    p.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
+    p.add_argument("--stop-token-ids", default="", help="comma list; default: the model's eos token")
+    p.add_argument("--ignore-eos", action="store_true", help="always generate the full budget, as the reference does")
+    p.add_argument("--no-graphs", action="store_true", help="decode step by step instead of replaying CUDA graphs")
+    p.add_argument("--prompt", action="append", default=None, help="generate text for this prompt (repeatable) and exit")
+    args = p.parse_args(argv)
+    if not args.model and not args.random_weights:
+        p.error("give --model DIR or --random-weights PRESET")
+    return args
+
+
+def _ints(text: str) -> list:
+    return [int(x) for x in str(text).split(",") if x.strip()]
+
+
+def run_suite(engine, name, prompt_lens, batch_sizes, max_new, args, vocab) -> list:
+    import torch
+    rows = []
+    g = torch.Generator().manual_seed(args.seed + 1)
+    lens = prompt_lens[:args.limit] if args.limit else prompt_lens
+    stops = _ints(args.stop_token_ids) or None
+    for batch in batch_sizes:
+        prompts = [torch.randint(0, vocab, (lens[i % len(lens)],), generator=g).tolist() for i in range(max(batch, len(lens)))]
+        kw = dict(batch_size=batch, temperature=args.temperature, seed=args.seed, stop_token_ids=stops,
+                  ignore_eos=args.ignore_eos or stops is None)
+        for _ in range(args.batch_warmup_iters):
+            engine.generate_ids(prompts, max_new, **kw)
+        times, tokens = [], 0
+        for _ in range(max(args.timed_repeats, 1)):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            out = engine.generate_ids(prompts, max_new, **kw)
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+            tokens = sum(len(t) for t in out)
+        latency = statistics.median(times)
+        row = dict(suite=name, batch_size=batch, requests=len(prompts), prompt_tokens=sum(len(p) for p in prompts),
+                   new_tokens=tokens, latency_s=round(latency, 6), tokens_per_s=round(tokens / latency, 2),
+                   decode_tokens_per_s=round(engine.last_loop.decoded_tokens / engine.last_loop.decode_seconds, 2)
+                   if engine.last_loop.decode_seconds > 0 else None)
+        rows.append(row)
+        if args.verbose_batches or not args.output_dir:
+            print(json.dumps(row), flush=True)
+    return rows
+
+
+def main(argv=None) -> int:
+    args = parse_args(argv)
+    import torch
+
+    from .config import preset_config
+    from .engine import StudentEngine
+    from .weights import write_random_model
+
+    holder = None
+    model_path = args.model
+    if args.random_weights:
+        holder = tempfile.TemporaryDirectory(prefix="qf_random_")
+        model_path = holder.name
+        store = torch.float32 if args.dtype == "float32" else torch.bfloat16
+        write_random_model(preset_config(args.random_weights), args.seed, model_path, store)
+    try:
+        engine = StudentEngine(model_path, device=args.device, dtype=args.dtype,
+                               attn_implementation=args.attn_implementation, local_files_only=args.local_files_only,
+                               seed=args.seed, cuda_graphs=not args.no_graphs)
+        if args.prompt:
+            for text in engine.generate(list(args.prompt), args.max_new_tokens_decode, batch_size=len(args.prompt)):
+                print(text)
+            return 0
+        vocab = engine.model.spec.vocab_size
+        for _ in range(args.warmup_iters):
+            engine.generate_ids([[1, 2, 3]], 8, ignore_eos=True)
+        results = []
+        suites = [s for s in args.suites.split(",") if s.strip()]
+        for suite in suites:
+            if suite == "decode_throughput":
+                results += run_suite(engine, suite, _ints(args.decode_prompt_lens), _ints(args.decode_batch_sizes),
+                                     args.max_new_tokens_decode, args, vocab)
+            elif suite == "ttft_prefill":
+                results += run_suite(engine, suite, _ints(args.ttft_prompt_lens), _ints(args.ttft_batch_sizes),
+                                     args.max_new_tokens_ttft, args, vocab)
+            else:
+                raise SystemExit(f"unknown suite {suite!r}; known: {', '.join(ALL_SUITES)}")
+        if args.output_dir:
+            out = Path(args.output_dir)
+            out.mkdir(parents=True, exist_ok=True)
+            (out / "summary.json").write_text(json.dumps(dict(model=str(args.model or args.random_weights),
+                                                              dtype=args.dtype, seed=args.seed, results=results), indent=1))
+        return 0
+    finally:
+        if holder is not None:
+            holder.cleanup()
+
+
+if __name__ == "__main__":
+    sys.exit(main())
