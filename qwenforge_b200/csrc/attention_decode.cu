@@ -330,3 +330,80 @@ QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, con
     }
 #undef QF_CASE
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same split-K decode attention for callers that must not allocate (declared in attention_decode_noalloc.h).
+// The partial results and the ticket counters live in ONE file-scope device array instead of caller-provided
+// scratch. Every GPU that loads this library holds the array (QF_NOALLOC_BYTES, about 4.1 MB) until the process ends.
+#include <stdio.h>
+
+#include "attention_decode_noalloc.h"
+
+#define QF_NOALLOC_PART_ML_FLOATS (QF_NOALLOC_MAX_ROWS * 2)
+#define QF_NOALLOC_PART_O_FLOATS (QF_NOALLOC_MAX_ROWS * QF_NOALLOC_MAX_HEAD_DIM)
+#define QF_NOALLOC_BYTES ((QF_NOALLOC_PART_O_FLOATS + QF_NOALLOC_PART_ML_FLOATS + QF_NOALLOC_MAX_COUNTERS) * 4)
+
+// layout: [part_o floats][part_ml floats][counters ints]
+static __device__ __align__(256) unsigned char qf_noalloc_scratch[QF_NOALLOC_BYTES];
+
+#define QF_NOALLOC_MAX_DEVICES 64
+static unsigned char* qf_noalloc_ptr[QF_NOALLOC_MAX_DEVICES];  // device address of the array, per device
+static thread_local char qf_noalloc_message[256];
+
+QF_EXPORT const char* qf_attention_decode_noalloc_error(void) { return qf_noalloc_message; }
+
+QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* cu_q, const int* tok_pos,
+                                          const int* slots, void* base, const int* table, long long page_elems,
+                                          int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                                          float scale, int window, int n_splits, int* err, cudaStream_t stream) {
+    qf_noalloc_message[0] = 0;
+    if (n_seqs <= 0) return 0;
+    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || n_splits > 128) {
+        snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
+                 "qf_attention_decode_noalloc: bad shape (n_heads %d, kv_heads %d, n_splits %d)", n_heads, kv_heads, n_splits);
+        return (int)cudaErrorInvalidValue;
+    }
+    const long long rows = (long long)n_seqs * n_heads * n_splits;
+    const long long n_counters = (long long)n_seqs * kv_heads * ((n_heads / kv_heads + 15) / 16);
+    if (n_splits > 1 && (rows > QF_NOALLOC_MAX_ROWS || head_dim > QF_NOALLOC_MAX_HEAD_DIM || n_counters > QF_NOALLOC_MAX_COUNTERS)) {
+        snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
+                 "qf_attention_decode_noalloc: n_seqs * n_heads * n_splits = %lld (limit %d), head_dim %d (limit %d), "
+                 "counters %lld (limit %d): beyond the built-in scratch; use fewer splits or qf_attention_decode",
+                 rows, QF_NOALLOC_MAX_ROWS, head_dim, QF_NOALLOC_MAX_HEAD_DIM, n_counters, QF_NOALLOC_MAX_COUNTERS);
+        return QF_NOALLOC_TOO_LARGE;
+    }
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= QF_NOALLOC_MAX_DEVICES) {
+        snprintf(qf_noalloc_message, sizeof qf_noalloc_message, "qf_attention_decode_noalloc: device index %d not supported", device);
+        return (int)cudaErrorInvalidDevice;
+    }
+    if (!qf_noalloc_ptr[device]) {
+        // Set-up, once per device, with that device current: in host code the array's NAME is only a host-side
+        // stand-in, not something a kernel may be given; its device address has to be asked for.
+        unsigned char* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, qf_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
+                     "qf_attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol;
+        }
+        qf_noalloc_ptr[device] = p;
+    }
+    float* part_o = reinterpret_cast<float*>(qf_noalloc_ptr[device]);
+    float* part_ml = part_o + QF_NOALLOC_PART_O_FLOATS;
+    int* counters = reinterpret_cast<int*>(part_ml + QF_NOALLOC_PART_ML_FLOATS);
+    if (n_splits > 1) {
+        // the array keeps whatever the last call left: the ticket counters must start at zero
+        e = cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int code = qf_attention_decode(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
+                                         head_dim, n_heads, n_seqs, scale, window, n_splits, part_o, part_ml, counters,
+                                         err, stream);
+    if (code == (int)cudaErrorInvalidValue)
+        snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
+                 "qf_attention_decode_noalloc: head_dim %d has no kernel (32, 64, 96, 128)", head_dim);
+    return code;
+}

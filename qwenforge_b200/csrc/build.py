@@ -86,7 +86,7 @@ def _build_dir() -> Path:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(_NVCC_FLAGS).encode())
-    for path in sorted(_SRC.glob("*.cuh")) + [_SRC / f"{name}.cu"]:
+    for path in sorted(_SRC.glob("*.cuh")) + sorted(_SRC.glob("*.h")) + [_SRC / f"{name}.cu"]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     return h.hexdigest()[:16]
