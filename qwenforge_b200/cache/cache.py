@@ -18,9 +18,9 @@ pages, page table and page allocator). A group with a window gives pages back as
 every position on them has left the window, so in steady state a sequence holds about
 window / PAGE_TOKENS + 1 pages there.
 
-Beside the groups lies the per-slot *sequence state*: a fixed number of 32-bit words per
-slot on the device (length, last token, finished flag, sampling counters), used by steps that
-run without the host (CUDA-graph decoding).
+The state that decoding itself keeps per sequence (latest token, position, step count, budget)
+lives in the decode graph's own device buffers (`engine/graphs.py`); this cache holds only what
+the model's mixers declare.
 """
 from __future__ import annotations
 
@@ -32,17 +32,6 @@ import torch
 from .allocators import CacheFull, CacheMisuse, PageAllocator, SlotAllocator
 
 PAGE_TOKENS = 64
-
-# words of the per-slot sequence state
-STATE_LENGTH = 0      # tokens in the cache
-STATE_TOKEN = 1       # the sequence's latest token (input of the next decode step)
-STATE_FINISHED = 2    # 1 once a stop token was produced or the budget is spent
-STATE_STEP = 3        # tokens generated so far (the sampling counter)
-STATE_SEQ_LO = 4      # sequence id, low and high word (the sampling key)
-STATE_SEQ_HI = 5
-STATE_BUDGET = 6      # tokens still allowed
-STATE_WORDS = 8
-
 
 def round_up(n: int, multiple: int) -> int:
     return (n + multiple - 1) // multiple * multiple
@@ -168,7 +157,7 @@ class StateSite:
 
 
 class SequenceCache:
-    """Slots, groups and the per-slot sequence state of one model on one device.
+    """Slots and groups of one model on one device.
 
     needs        one entry per schedule entry: KvNeed, StateNeed or None (that entry keeps nothing,
                  or reads another entry's cache)
@@ -210,7 +199,6 @@ class SequenceCache:
                     self._sites[entry] = StateSite(group, i)
             else:
                 raise TypeError(f"unknown cache need {need!r}")
-        self.seq_state = torch.zeros((self.max_seqs, STATE_WORDS), dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ sites
     def site(self, entry: int):
@@ -224,7 +212,6 @@ class SequenceCache:
         self.lengths[slot] = 0
         for group in self.state_groups:
             group.reset(slot)
-        self.seq_state[slot].zero_()
         return slot
 
     def _check_held(self, slot: int) -> None:

@@ -12,11 +12,35 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// Eight bf16 elements per thread (16-byte loads and stores); needs inter % 8 == 0 and 16-byte aligned rows.
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter, size_t total8) {
+    const int per_row = inter / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / per_row, c = (i % per_row) * 8;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + c);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * inter + inter + c);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            o2[j] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * inter + c) = o4;
+    }
+}
+
 QF_EXPORT int qf_swiglu(int is_bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
     const size_t total = (size_t)rows * inter;
     if (total == 0) return 0;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (is_bf16)
+    if (is_bf16 && inter % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
+        const size_t total8 = total / 8;
+        const int b8 = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        swiglu_bf16x8_kernel<<<b8, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total8);
+    } else if (is_bf16)
         swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total);
     else
         swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inter, total);

@@ -15,7 +15,7 @@
 #define PF_BM 64
 
 template <int D>
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, D <= 64 ? 4 : 2)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                      float scale_log2, int window, int* err) {

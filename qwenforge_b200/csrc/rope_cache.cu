@@ -26,12 +26,15 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, int qkv_stride, con
         if (site.table[(long long)slot * site.table_stride + pos / QF_PAGE] < 0) atomicOr(err, QF_ERR_NO_PAGE);
     }
 
+    // the token's sines and cosines once for all heads
+    __shared__ float sin_s[128], cos_s[128];  // rot_dim <= head_dim <= 256
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sin_s[j], &cos_s[j]);
+    __syncthreads();
     // work items: (head, j) rotation pairs of q and k heads, then pass-through and value elements
     const int rot_items = (n_heads + KVH) * half;
     for (int i = threadIdx.x; i < rot_items; i += blockDim.x) {
         const int head = i / half, j = i % half;
-        float s, c;
-        sincosf((float)pos * inv_freq[j], &s, &c);
+        const float s = sin_s[j], c = cos_s[j];
         const bool is_q = head < n_heads;
         const int src = is_q ? head * D : q_width + (head - n_heads) * D;
         const float x1 = Num<T>::to_f(row[src + j]), x2 = Num<T>::to_f(row[src + j + half]);
@@ -87,7 +90,7 @@ QF_EXPORT int qf_rope_cache_write(int is_bf16, const void* qkv, int qkv_stride, 
                                   const int* slots, const float* inv_freq, int rot_dim, int n_heads, void* q_out,
                                   void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
                                   int head_dim, int write_cache, int n_tokens, int* err, cudaStream_t stream) {
-    if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1)) return (int)cudaErrorInvalidValue;
+    if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1) || rot_dim > 256) return (int)cudaErrorInvalidValue;
     return is_bf16 ? launch<bf16>(qkv, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, base,
                                   table, page_elems, table_stride, kv_heads, head_dim, write_cache, n_tokens, err,
                                   stream)

@@ -62,6 +62,8 @@ class Model:
     # ------------------------------------------------------------------ weights
     def bind(self, tensors) -> "Model":
         ops.require_cuda(self.device, "the model")
+        if self.device.type == "cuda" and self.device.index is not None:
+            torch.cuda.set_device(self.device)  # the kernels launch on the current device's current stream
         libraries = {"embed", "norm"}
         for part in self.parts():
             libraries |= part.kernel_libraries(self.dtype)

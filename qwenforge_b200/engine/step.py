@@ -57,7 +57,7 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
         if q == 0:
             raise ValueError(f"step: entry {s} brings no tokens")
         base = cu_q[-1]
-        ids.extend(int(t) for t in tokens)
+        ids.extend(tokens)
         tok_seq.extend([s] * q)
         tok_pos.extend(range(start, start + q))
         slots.append(slot)
@@ -71,10 +71,8 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
                     raise ValueError(f"step: entry {s} wants place {place} of {q} tokens")
                 rows.append(base + place)
     total = cu_q[-1]
-    packed = torch.tensor(ids + tok_seq + tok_pos + slots + cu_q + rows, dtype=torch.int32)
-    if torch.device(device).type == "cuda":
-        packed = packed.pin_memory()
-    dev = packed.to(device, non_blocking=True)
+    # one host-to-device copy; from pageable memory it is complete when the call returns, so the host lists may go
+    dev = torch.tensor(ids + tok_seq + tok_pos + slots + cu_q + rows, dtype=torch.int32).to(device)
     o = 0
 
     def take(count):

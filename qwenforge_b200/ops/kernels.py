@@ -61,7 +61,8 @@ def _check(code: int, what: str) -> None:
 
 
 def _stream() -> _P:
-    return _P(torch.cuda.current_stream().cuda_stream)
+    """The current stream's raw handle on the current device (the short way: this runs once per kernel launch)."""
+    return _P(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _ptr(t: Optional[torch.Tensor]) -> _P:

@@ -283,3 +283,43 @@ def test_graph_decoding_equals_stepping(folders, name, dtype):
     n_graphs = len(graphed.graph_decoder.graphs)
     graphed.generate_results(prompts, budgets, batch_size=5, temperature=0.8, ignore_eos=True)
     assert len(graphed.graph_decoder.graphs) == n_graphs       # the same key: replayed, not captured again
+
+
+@pytest.mark.parametrize("preset,layers", [("qwen2.5-0.5b", 2), ("qwen2.5-3b", 1), ("qwen2.5-7b", 1)])
+def test_real_layer_sizes(preset, layers, tmp_path):
+    """The layer sizes of the three Qwen2.5 models (head size 64 and 128, groups of 7, 8 and 7, widths 896/2048/3584,
+    intermediate 4864/11008/18944) with few layers and a small vocabulary, in float32 and bfloat16, against the plain
+    implementation: a whole prompt, a batch of unequal prompts, and tokens decoded one by one."""
+    import json
+
+    from qwenforge_b200.config import preset_dict
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.weights import save_safetensors
+    config = dict(preset_dict(preset), num_hidden_layers=layers, vocab_size=1000, max_position_embeddings=512)
+    weights = plain.random_weights(config, 9)
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    save_safetensors(tmp_path / "model.safetensors", weights)
+    seqs = [random_tokens(1000, n, 700 + n) for n in (70, 9)]
+    refs = [plain.forward_logits(config, weights, s, dtype=torch.float32) for s in seqs]
+    for dtype in DTYPES:
+        model = Model.from_dir(tmp_path, dtype, "cuda")
+        cache = model.new_cache(512, 4)
+        slots = [cache.open() for _ in seqs]
+        heads = [len(s) - 6 for s in seqs]
+        got = [[] for _ in seqs]
+        logits = model.step(cache, [(slot, s[:h]) for slot, s, h in zip(slots, seqs, heads)],
+                            want=[list(range(h)) for h in heads])
+        got[0].append(logits[:heads[0]])
+        got[1].append(logits[heads[0]:])
+        for t in range(6):
+            logits = model.step(cache, [(slot, [s[h + t]]) for slot, s, h in zip(slots, seqs, heads)])
+            got[0].append(logits[0:1])
+            got[1].append(logits[1:2])
+        model.raise_on_kernel_error()
+        for pieces, ref in zip(got, refs):
+            rel, abs_ = (1e-4, 1e-5) if dtype == torch.float32 else (4e-2, 2e-2)   # the oracle is float32 here
+            bound = abs_ + rel * float(ref.abs().max())
+            err = float((torch.cat(pieces).double().cpu() - ref.double()).abs().max())
+            assert err <= bound, f"{preset} {dtype}: {err:.3e} > {bound:.3e}"
+        del model, cache
+        torch.cuda.empty_cache()
