@@ -4,8 +4,8 @@
 //
 // A block serves one (sequence, kv head, chunk of up to 16 query heads of the group, split). The query heads of
 // the group are the 16 rows of an m16n8k16 tensor-core tile, so keys and values are read once for the whole
-// group. Each WARP works alone on whole pages (64 positions: 64 x D keys, 64 x D values): the page arrives in the
-// warp's own shared-memory buffer by 16-byte asynchronous copies into padded rows (bulk copies of single 128-byte
+// group. Each WARP works alone on whole pages (64 positions: 64 x D keys, 64 x D values): the page arrives in two
+// halves through the warp's own two shared-memory buffers, by 16-byte asynchronous copies into padded rows (bulk copies of single 128-byte
 // rows were measured slower: a page is too many small requests for the copy engine), then S = Q K^T, online
 // softmax in float32 (base-2 exponentials, the scale folded in), O += P V. With eight warps a block has eight
 // pages in flight and no block-wide barrier inside the loop. The warps are merged in shared memory at the end.
@@ -75,107 +75,125 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
-    // ---- every warp works alone on whole pages: page p_begin + warp, then + WARPS, ...
-    bf16* kb = reinterpret_cast<bf16*>(smem_raw + (size_t)warp * PAGE_BYTES);
-    bf16* vb = kb + QF_PAGE * LD;
+    // ---- every warp works alone on whole pages: page p_begin + warp, then + WARPS, ... It takes a page in two halves
+    // of 32 positions through two buffers, so that the second half (or the next page's first) is on its way while
+    // the first is multiplied.
+    constexpr int HALF = QF_PAGE / 2;
+    constexpr int STAGE_ELEMS = 2 * HALF * LD;  // keys then values of half a page
+    bf16* stage0 = reinterpret_cast<bf16*>(smem_raw + (size_t)warp * PAGE_BYTES);
     const int* table_row = site.table + (long long)slot * site.table_stride;
-    for (int p = p_begin + warp; p < p_end; p += DEC_WARPS) {
-        const int page = table_row[p];
-        if (page < 0) {
-            if (lane == 0) atomicOr(err, QF_ERR_NO_PAGE);
-            continue;
-        }
-        const bf16* kp = site.base + (long long)page * site.page_elems + (long long)kvh * QF_PAGE * D;
-        const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
-        {   // the page's 2 x 64 rows in 16-byte asynchronous copies, rows padded in shared memory
-            constexpr int CH = D / 8;  // chunks per row
+    const int my_pages = p_begin + warp < p_end ? (p_end - p_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
+    const int n_halves = 2 * my_pages;
+    // half i of this warp: page p_begin + warp + (i / 2) * WARPS, positions key0 .. key0 + 31
+    auto issue = [&](int i) {
+        if (i < n_halves) {
+            const int p = p_begin + warp + (i >> 1) * DEC_WARPS, key0 = p * QF_PAGE + (i & 1) * HALF;
+            const int page = table_row[p];
+            if (page < 0) {
+                if (lane == 0 && (i & 1) == 0) atomicOr(err, QF_ERR_NO_PAGE);
+            } else if (key0 < L && key0 + HALF > lo) {
+                const bf16* kp = site.base + (long long)page * site.page_elems + ((long long)kvh * QF_PAGE + (i & 1) * HALF) * D;
+                const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
+                bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
+                bf16* vb = kb + HALF * LD;
+                constexpr int CH = D / 8;  // 16-byte chunks per row
 #pragma unroll 4
-            for (int i = lane; i < QF_PAGE * CH; i += 32) {
-                const int r = i / CH, c = (i % CH) * 8;
-                cp_async_16(kb + (size_t)r * LD + c, kp + (size_t)r * D + c, true);
-                cp_async_16(vb + (size_t)r * LD + c, vp + (size_t)r * D + c, true);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            __syncwarp();  // each lane waited for its own copies; together the page is complete
-        }
-        const int key0 = p * QF_PAGE;
-        float s[8][4];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-            for (int t2 = 0; t2 < 4; ++t2) {  // 16 keys per ldmatrix.x4
-                uint32_t kf[4];
-                ldmatrix_x4(kf, kb + (size_t)(16 * t2 + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
-                mma_bf16_16816(s[2 * t2], qa[ks], kf[0], kf[1]);
-                mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
+                for (int j = lane; j < HALF * CH; j += 32) {
+                    const int r = j / CH, c = (j % CH) * 8;
+                    cp_async_16(kb + (size_t)r * LD + c, kp + (size_t)r * D + c, true);
+                    cp_async_16(vb + (size_t)r * LD + c, vp + (size_t)r * D + c, true);
+                }
             }
         }
-        const bool full = key0 >= lo && key0 + QF_PAGE <= L;  // every key of the page is visible
-        float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
+        cp_async_commit();  // one group per half, empty when there is nothing to fetch
+    };
+    issue(0);
+    for (int i = 0; i < n_halves; ++i) {
+        issue(i + 1);
+        cp_async_wait<1>();
+        __syncwarp();  // each lane waited for its own copies; together the half page is complete
+        const int p = p_begin + warp + (i >> 1) * DEC_WARPS, key0 = p * QF_PAGE + (i & 1) * HALF;
+        if (table_row[p] >= 0 && key0 < L && key0 + HALF > lo) {
+            const bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
+            const bf16* vb = kb + HALF * LD;
+            float s[4][4];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
+            for (int t = 0; t < 4; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
-                const bool ok = full || (kj >= lo && kj < L);
-                s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
-                mx[0] = fmaxf(mx[0], s[t][e]);
-                mx[1] = fmaxf(mx[1], s[t][2 + e]);
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int t2 = 0; t2 < 2; ++t2) {  // 16 keys per ldmatrix.x4
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, kb + (size_t)(16 * t2 + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
+                    mma_bf16_16816(s[2 * t2], qa[ks], kf[0], kf[1]);
+                    mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
+                }
+            }
+            const bool full = key0 >= lo && key0 + HALF <= L;  // every key of the half is visible
+            float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
+                    const bool ok = full || (kj >= lo && kj < L);
+                    s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
+                    s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                    mx[0] = fmaxf(mx[0], s[t][e]);
+                    mx[1] = fmaxf(mx[1], s[t][2 + e]);
+                }
+            }
+            float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                corr[r] = exp2f(m_run[r] - m_new);
+                m_run[r] = m_new;
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    // a masked score is QF_NEG_BIG: its weight is 0 even while the running maximum is QF_NEG_BIG too
+                    s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
+                    s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
+                    sum[0] += s[t][e];
+                    sum[1] += s[t][2 + e];
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+                sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+                l_run[r] = l_run[r] * corr[r] + sum[r];
+            }
+            if (corr[0] != 1.f || corr[1] != 1.f) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    o[nt][0] *= corr[0];
+                    o[nt][1] *= corr[0];
+                    o[nt][2] *= corr[1];
+                    o[nt][3] *= corr[1];
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {  // 16 keys per step
+                uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                                  pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+                for (int nt = 0; nt < NT; nt += 2) {
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, vb + (size_t)(16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
+                    mma_bf16_16816(o[nt], pa, vf[0], vf[1]);
+                    mma_bf16_16816(o[nt + 1], pa, vf[2], vf[3]);
+                }
             }
         }
-        float corr[2], sum[2] = {0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            corr[r] = exp2f(m_run[r] - m_new);
-            m_run[r] = m_new;
-        }
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                // a masked score is QF_NEG_BIG: its weight is 0 even while the running maximum is QF_NEG_BIG too
-                s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
-                s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
-                sum[0] += s[t][e];
-                sum[1] += s[t][2 + e];
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-            sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-            l_run[r] = l_run[r] * corr[r] + sum[r];
-        }
-        if (corr[0] != 1.f || corr[1] != 1.f) {
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                o[nt][0] *= corr[0];
-                o[nt][1] *= corr[0];
-                o[nt][2] *= corr[1];
-                o[nt][3] *= corr[1];
-            }
-        }
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
-            uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
-                              pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
-#pragma unroll
-            for (int nt = 0; nt < NT; nt += 2) {
-                uint32_t vf[4];
-                ldmatrix_x4_trans(vf, vb + (size_t)(16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
-                mma_bf16_16816(o[nt], pa, vf[0], vf[1]);
-                mma_bf16_16816(o[nt + 1], pa, vf[2], vf[3]);
-            }
-        }
-        __syncwarp();  // every lane has read the page before the next copies overwrite it
+        __syncwarp();  // every lane has read this buffer before the copies of half i + 2 overwrite it
     }
+    cp_async_wait<0>();
 
     // ---- merge the warps: common maximum, rescale, add up in shared memory in warp order
     if ((lane & 3) == 0) {

@@ -326,7 +326,7 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optiona
         if seq_ids.numel() != rows or steps.numel() != rows:
             raise KernelError("sample: seq_ids and steps must have one element per row")
     # enough blocks to fill the GPU when there are few rows, at least 2048 tokens of the vocabulary each
-    chunks = max(1, min(-(-vocab // 2048), -(-296 // rows), 64))
+    chunks = max(1, min(-(-vocab // 2048), -(-1184 // rows), 64))
     scratch = scratch or _sample_scratch
     if chunks > 1:
         scratch.ensure(rows, chunks, logits.device)
