@@ -117,39 +117,70 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
             }
             // a page that every row of the warp sees whole needs no mask
             const bool full = key0 + QF_PAGE - 1 <= warp_first && key0 >= (window > 0 ? max(0, warp_last - window + 1) : 0);
-            float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
-                    const bool ok0 = full || (kj <= row_pos[0] && kj >= row_lo[0]);
-                    const bool ok1 = full || (kj <= row_pos[1] && kj >= row_lo[1]);
-                    s[t][e] = ok0 ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                    s[t][2 + e] = ok1 ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
-                    mx[0] = fmaxf(mx[0], s[t][e]);
-                    mx[1] = fmaxf(mx[1], s[t][2 + e]);
-                }
-            }
             float corr[2], sum[2] = {0.f, 0.f};
+            if (full) {
+                // the common case (every page left of the diagonal): no comparisons, one fused multiply-add and one
+                // hardware exponential per score
+                float mx[2] = {s[0][0], s[0][2]};
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-                const float m_new = fmaxf(m_run[i], mx[i]);
-                corr[i] = exp2f(m_run[i] - m_new);
-                m_run[i] = m_new;
-            }
+                for (int t = 0; t < 8; ++t) {
+                    mx[0] = fmaxf(mx[0], fmaxf(s[t][0], s[t][1]));
+                    mx[1] = fmaxf(mx[1], fmaxf(s[t][2], s[t][3]));
+                }
+                float neg_m[2];
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
+                for (int i = 0; i < 2; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    const float m_new = fmaxf(m_run[i], mx[i] * scale_log2);
+                    corr[i] = fast_exp2(m_run[i] - m_new);
+                    m_run[i] = m_new;
+                    neg_m[i] = -m_new;
+                }
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    // a masked score is QF_NEG_BIG: its exponential is 0 unless the whole row is masked so far,
-                    // in which case the maximum is QF_NEG_BIG too and the difference would be 0
-                    s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
-                    s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
-                    sum[0] += s[t][e];
-                    sum[1] += s[t][2 + e];
+                for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        s[t][e] = fast_exp2(fmaf(s[t][e], scale_log2, neg_m[0]));
+                        s[t][2 + e] = fast_exp2(fmaf(s[t][2 + e], scale_log2, neg_m[1]));
+                        sum[0] += s[t][e];
+                        sum[1] += s[t][2 + e];
+                    }
+                }
+            } else {
+                float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
+                        const bool ok0 = kj <= row_pos[0] && kj >= row_lo[0];
+                        const bool ok1 = kj <= row_pos[1] && kj >= row_lo[1];
+                        s[t][e] = ok0 ? s[t][e] * scale_log2 : QF_NEG_BIG;
+                        s[t][2 + e] = ok1 ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                        mx[0] = fmaxf(mx[0], s[t][e]);
+                        mx[1] = fmaxf(mx[1], s[t][2 + e]);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    const float m_new = fmaxf(m_run[i], mx[i]);
+                    corr[i] = fast_exp2(m_run[i] - m_new);
+                    m_run[i] = m_new;
+                }
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        // a masked score is QF_NEG_BIG: its exponential is 0 unless the whole row is masked so far,
+                        // in which case the maximum is QF_NEG_BIG too and the difference would be 0
+                        s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? fast_exp2(s[t][e] - m_run[0]) : 0.f;
+                        s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? fast_exp2(s[t][2 + e] - m_run[1]) : 0.f;
+                        sum[0] += s[t][e];
+                        sum[1] += s[t][2 + e];
+                    }
                 }
             }
 #pragma unroll

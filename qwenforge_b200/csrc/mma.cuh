@@ -38,6 +38,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 #define QF_NEG_BIG (-1.0e30f)
 
+// 2^x by the hardware approximation (about 2 ulp; flushes denormals): enough for bf16 attention weights.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // ---- bulk asynchronous copies (the TMA engine in its untiled form) completing on a shared-memory barrier.
 // One thread announces the expected bytes, any threads issue copies of multiples of 16 bytes between 16-byte
 // aligned addresses, and every thread that needs the data waits for the barrier's phase to flip. The wait is

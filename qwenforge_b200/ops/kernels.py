@@ -168,7 +168,7 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
 
 def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
                      inv_freq: Optional[torch.Tensor], rot_dim: int, n_heads: int, q_out: torch.Tensor,
-                     site: KvSiteArgs, write_cache: bool, err: torch.Tensor) -> None:
+                     site: KvSiteArgs, write_cache: bool, err: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
     """Rotate q and k heads of qkv [T, (NH + 2 KVH) D] by position, write q to q_out [T, NH D] and k, v into the cache."""
     _dev("qkv", qkv)
     _dev("q_out", q_out, qkv.dtype)
@@ -180,12 +180,16 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
     d, kvh = site.head_dim, site.kv_heads
     if qkv.shape[1] != (n_heads + 2 * kvh) * d or q_out.shape != (n, n_heads * d):
         raise KernelError("rope_cache_write: qkv/q_out widths do not match the head counts")
+    if bias is not None:
+        _dev("bias", bias, qkv.dtype)
+        if bias.numel() != qkv.shape[1]:
+            raise KernelError("rope_cache_write: bias must have one element per projection column")
     if inv_freq is not None:
         _dev("inv_freq", inv_freq, torch.float32)
         if inv_freq.numel() * 2 != rot_dim:
             raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 frequencies")
     _check(library("rope_cache").qf_rope_cache_write(
-        _I(_is_bf16(qkv.dtype)), _ptr(qkv), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
+        _I(_is_bf16(qkv.dtype)), _ptr(qkv), _ptr(bias), _I(qkv.stride(0)), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots),
         _ptr(inv_freq), _I(rot_dim), _I(n_heads), _ptr(q_out), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(kvh), _I(d), _I(1 if write_cache else 0), _I(n), _ptr(err),
         _stream()), "rope_cache_write")

@@ -90,8 +90,9 @@ class GqaAttention(Mixer):
 
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
-        qkv = ops.linear(x, self.qkv_weight, self.qkv_bias_t)
         rotary = self.position.fused_rotary() if self.position is not None else None
+        late_bias = self.position is None or rotary is not None  # the kernel that rotates and stores adds the bias
+        qkv = ops.linear(x, self.qkv_weight, None if late_bias else self.qkv_bias_t)
         if self.position is not None and rotary is None:
             q_view = qkv[:, :self.q_width].view(n, self.n_heads, self.head_dim)
             k_view = qkv[:, self.q_width:self.q_width + self.kv_width].view(n, self.n_kv, self.head_dim)
@@ -100,7 +101,7 @@ class GqaAttention(Mixer):
         q = torch.empty((n, self.q_width), dtype=x.dtype, device=x.device)
         args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
         ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args,
-                             writes_cache, ctx.err)
+                             writes_cache, ctx.err, bias=self.qkv_bias_t if late_bias else None)
         attended = torch.empty_like(q)
         fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16
                 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS)

@@ -62,10 +62,12 @@ def _kv_rows(site, slot, positions, head, which):
     return pages, offs
 
 
-def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, site, write_cache, err):
+def rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, q_out, site, write_cache, err, bias=None):
     n = qkv.shape[0]
     d, kvh = site.head_dim, site.kv_heads
     x = _f(qkv)
+    if bias is not None:
+        x = x + _f(bias)
     q = x[:, :n_heads * d].reshape(n, n_heads, d).clone()
     k = x[:, n_heads * d:(n_heads + kvh) * d].reshape(n, kvh, d).clone()
     v = x[:, (n_heads + kvh) * d:].reshape(n, kvh, d)

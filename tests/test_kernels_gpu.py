@@ -474,3 +474,39 @@ def test_residual_add(ops):
     want = h + d.float()
     ops.residual_add(h, d)
     assert torch.equal(h, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rope_cache_write_adds_the_bias_first(ops, dtype):
+    g = torch.Generator().manual_seed(30)
+    nh, kvh, d, n = 3, 1, 32, 5
+    site_a, site_b = FakeSite(1, 64, kvh, d, dtype), FakeSite(1, 64, kvh, d, dtype)
+    site_b.table = site_a.table
+    qkv = torch.randn(n, (nh + 2 * kvh) * d, generator=g).to(dtype).to(DEV)
+    bias = torch.randn((nh + 2 * kvh) * d, generator=g).to(dtype).to(DEV)
+    tok_seq = torch.zeros(n, dtype=torch.int32, device=DEV)
+    tok_pos = torch.arange(7, 7 + n, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(1, dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))).to(DEV)   # half of the head rotates
+    q1 = torch.empty(n, nh * d, dtype=dtype, device=DEV)
+    q2 = torch.empty_like(q1)
+    e = err_word()
+    ops.rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, 16, nh, q1, ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d),
+                         True, e, bias=bias)
+    ref.rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, 16, nh, q2, site_b, True, None, bias=bias)
+    assert int(e) == 0 and max_err(q1, q2) <= tol(dtype) * 8 and max_err(site_a.storage, site_b.storage) <= tol(dtype) * 8
+
+
+def test_linear_bf16_matches_a_plain_product(ops):
+    g = torch.Generator().manual_seed(31)
+    for m, n, k in ((1, 8, 16), (70, 200, 120), (2048, 1152, 896)):
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+        b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV)
+        want = x.double() @ w.double().T
+        assert max_err(ops.linear(x, w), want) <= 2e-2 * max(1.0, float(want.abs().max()))
+        assert max_err(ops.linear(x, w, out_dtype=torch.float32), want) <= 2e-3 * max(1.0, float(want.abs().max()))
+        assert ops.linear(x, w, out_dtype=torch.float32).dtype == torch.float32
+        assert max_err(ops.linear(x, w, b), want + b.double()) <= 3e-2 * max(1.0, float(want.abs().max()))
+        wide = torch.randn(m, k + 8, generator=g).to(torch.bfloat16).to(DEV)   # strided rows
+        assert max_err(ops.linear(wide[:, :k], w), wide[:, :k].double() @ w.double().T) <= 2e-2 * max(1.0, float(want.abs().max()))
