@@ -1,0 +1,259 @@
+// Matrix products for many token rows on the fifth-generation tensor cores (tcgen05), bf16 in, float32
+// accumulation in tensor memory:   C[M][N] = A[M][K] * W[N][K]^T
+// with the feed-forward's gate fused in:  EPI_SWIGLU writes silu(gate) * up for W = [gate rows | up rows].
+//
+// One block computes one 128 x 128 tile of C. Operand tiles of 128 rows x 64 columns (128 bytes per row) are
+// brought into shared memory by the tensor memory accelerator (2-D tiled copies with the 128-byte swizzle that
+// the tensor cores read) through a ring of stages. Thread 0 of warp 0 issues the copies, thread 0 of warp 1 issues
+// the tcgen05.mma instructions (four of K = 16 per stage) whose accumulator is 128 lanes x 128 columns of tensor
+// memory; `tcgen05.commit` hands a stage back when its products have been read, and signals the epilogue at the
+// end. All four warps then read their 32 accumulator lanes with tcgen05.ld, apply the epilogue and store.
+// Two blocks fit an SM, so one block's epilogue overlaps the other's products. Every wait on a barrier is bounded;
+// a wait that runs out sets QF_ERR_COPY_TIMEOUT, and the block still frees its tensor memory and returns.
+// Copies use no cluster multicast; every block loads its own tiles.
+#include <cuda.h>
+
+#include "mma.cuh"
+
+enum { TC_PLAIN = 0, TC_SWIGLU = 1 };
+
+#define TC_BM 128
+#define TC_BN 128
+#define TC_BK 64
+#define TC_STAGES 3
+#define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
+#define TC_THREADS 128
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte swizzle:
+// start address / 16; leading byte offset 1 (unused for swizzled K-major); stride between 8-row groups 1024 bytes;
+// descriptor version 1 (sm_100); layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* p) {
+    return (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: float32 accumulator, bf16 A and B, both K-major, N = 128, M = 128.
+#define TC_IDESC ((1u << 4) | (1u << 7) | (1u << 10) | ((TC_BN >> 3) << 17) | ((TC_BM >> 4) << 24))
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p; \n\t"
+        "}\n" ::"r"(tmem_c),
+        "l"(desc_a), "l"(desc_b), "r"(TC_IDESC), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, bf16* __restrict__ out,
+               int M, int n_out, int K, int inter, int ldo, int* err) {
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], acc_bar;
+    __shared__ uint32_t tmem_base_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+    const int n_k = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+    }
+    if (warp == 0) {  // one warp allocates the accumulator: 128 columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TC_BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = tmem_base_s;
+    bool timed_out = false;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: fill the ring with operand tiles
+        for (int kb = 0; kb < n_k && !timed_out; ++kb) {
+            const int s = kb % TC_STAGES;
+            if (kb >= TC_STAGES && !mbar_wait(&empty_bar[s], ((kb / TC_STAGES) - 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            unsigned char* a_s = smem + (size_t)s * TC_STAGE_BYTES;
+            unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
+            mbar_expect_tx(&full_bar[s], TC_STAGE_BYTES);
+            tma_load_2d(a_s, &map_a, kb * TC_BK, tile_m * TC_BM, &full_bar[s]);
+            if (EPI == TC_SWIGLU) {  // 64 gate rows, then the 64 matching up rows
+                tma_load_2d(b_s, &map_b, kb * TC_BK, tile_n * 64, &full_bar[s]);
+                tma_load_2d(b_s + 64 * TC_BK * 2, &map_b, kb * TC_BK, inter + tile_n * 64, &full_bar[s]);
+            } else {
+                tma_load_2d(b_s, &map_b, kb * TC_BK, tile_n * TC_BN, &full_bar[s]);
+                tma_load_2d(b_s + 64 * TC_BK * 2, &map_b, kb * TC_BK, tile_n * TC_BN + 64, &full_bar[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- one thread issues the products
+        for (int kb = 0; kb < n_k && !timed_out; ++kb) {
+            const int s = kb % TC_STAGES;
+            if (!mbar_wait(&full_bar[s], (kb / TC_STAGES) & 1)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const unsigned char* a_s = smem + (size_t)s * TC_STAGE_BYTES;
+            const unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
+            const uint64_t da = smem_desc_sw128(a_s), db = smem_desc_sw128(b_s);
+#pragma unroll
+            for (int k4 = 0; k4 < TC_BK / 16; ++k4)  // 16 columns = 32 bytes = 2 units of the address field
+                umma_bf16(tmem_acc, da + 2 * k4, db + 2 * k4, (kb > 0 || k4 > 0) ? 1u : 0u);
+            umma_commit(&empty_bar[s]);  // arrives when these products have finished reading the stage
+        }
+        umma_commit(&acc_bar);           // arrives when every product has finished
+    }
+    if (timed_out) atomicOr(err, QF_ERR_COPY_TIMEOUT);
+    __syncwarp();
+
+    // ---- epilogue: warp w owns accumulator lanes (= tile rows) 32 w .. 32 w + 31
+    if (!mbar_wait(&acc_bar, 0) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
+    tc_fence_after();
+    const int row = tile_m * TC_BM + warp * 32 + lane;
+    const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
+    if (EPI == TC_SWIGLU) {
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t g[32], u[32];
+            tmem_load_32(lane_base + c0, g);
+            tmem_load_32(lane_base + 64 + c0, u);
+            const int col = tile_n * 64 + c0;
+            if (row < M && col < n_out) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+                    packed[j] = pack_bf16(g0 / (1.0f + expf(-g0)) * __uint_as_float(u[2 * j]),
+                                          g1 / (1.0f + expf(-g1)) * __uint_as_float(u[2 * j + 1]));
+                }
+                bf16* dst = out + (size_t)row * ldo + col;
+                if (col + 32 <= n_out) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                } else {
+                    for (int j = 0; j < n_out - col; ++j) dst[j] = reinterpret_cast<const bf16*>(packed)[j];
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_load_32(lane_base + c0, v);
+            const int col = tile_n * TC_BN + c0;
+            if (row < M && col < n_out) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) packed[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                bf16* dst = out + (size_t)row * ldo + col;
+                if (col + 32 <= n_out) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                } else {
+                    for (int j = 0; j < n_out - col; ++j) dst[j] = reinterpret_cast<const bf16*>(packed)[j];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem_acc), "r"(TC_BN));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A 2-D map over a row-major bf16 matrix [rows][ld], boxes of `box_rows` rows x 64 columns, 128-byte swizzle,
+// zeros outside the matrix.
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// a [m][lda], w [n][ldw] (for TC_SWIGLU: n = 2 * inter, gate rows then up rows), out [m][ldo] with n columns
+// (TC_SWIGLU: inter columns). Needs k, lda, ldw, ldo multiples of 8 and 16-byte aligned bases; for TC_SWIGLU
+// inter a multiple of 8. Returns cudaErrorInvalidValue for what it does not take, cudaErrorNotSupported when
+// the driver has no tensor-map encoder.
+QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, int ldw, void* out, int ldo, int m, int n, int k,
+                         int* err, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8 || ldo % 8) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, a, m, k, lda, TC_BM) || !make_map(&map_b, w, n, k, ldw, 64)) return (int)cudaErrorNotSupported;
+    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;
+    dim3 grid;
+    if (epilogue == TC_SWIGLU) {
+        if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
+        const int inter = n / 2;
+        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        grid = dim3((inter + 63) / 64, (m + TC_BM - 1) / TC_BM);
+        tc_gemm_kernel<TC_SWIGLU><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, inter, k, inter, ldo, err);
+    } else if (epilogue == TC_PLAIN) {
+        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        grid = dim3((n + TC_BN - 1) / TC_BN, (m + TC_BM - 1) / TC_BM);
+        tc_gemm_kernel<TC_PLAIN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n, k, 0, ldo, err);
+    } else {
+        return (int)cudaErrorInvalidValue;
+    }
+    return (int)cudaGetLastError();
+}

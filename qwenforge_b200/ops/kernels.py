@@ -467,3 +467,36 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
         raise KernelError("residual_add: shapes differ")
     _check(library("norm").qf_residual_add(_I(_is_bf16(delta.dtype)), _ptr(hidden), _ptr(delta), _LL(hidden.numel()),
                                            _stream()), "residual_add")
+
+
+# ---------------------------------------------------------------------------------------------- tcgen05 products
+
+TC_PLAIN, TC_SWIGLU = 0, 1
+
+
+def tc_gemm_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes x [M, K] against weight [N, K]: bf16, K and the row strides multiples of 8."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def tc_gemm(epilogue: int, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
+    """out = x @ weight.T on the tcgen05 tensor cores (bf16 in, float32 accumulate in tensor memory, bf16 out).
+    TC_SWIGLU: weight = [gate rows | up rows], out [M, N / 2] = silu(x gate^T) * (x up^T)."""
+    _dev("x", x, torch.bfloat16, contiguous=False)
+    _dev("weight", weight, torch.bfloat16, contiguous=False)
+    _dev("out", out, torch.bfloat16, contiguous=False)
+    m, k = x.shape
+    n = weight.shape[0]
+    cols = n // 2 if epilogue == TC_SWIGLU else n
+    if weight.shape[1] != k or out.shape != (m, cols) or out.stride(1) != 1:
+        raise KernelError(f"tc_gemm: shapes {tuple(x.shape)} x {tuple(weight.shape)}^T -> {tuple(out.shape)} do not agree")
+    if not tc_gemm_takes(x, weight) or out.stride(0) % 8 or out.data_ptr() % 16:
+        raise KernelError("tc_gemm: operands must be bf16 with K and row strides multiples of 8 and 16-byte aligned")
+    err = err if err is not None else _err_word_for(x.device)
+    code = library("tc_gemm").qf_tc_gemm(_I(epilogue), _ptr(x), _I(x.stride(0)), _ptr(weight), _I(weight.stride(0)), _ptr(out),
+                                         _I(out.stride(0)), _I(m), _I(n), _I(k), _ptr(err), _stream())
+    if code == 801:
+        raise KernelError("tc_gemm: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
+    _check(code, "tc_gemm")

@@ -510,3 +510,38 @@ def test_linear_bf16_matches_a_plain_product(ops):
         assert max_err(ops.linear(x, w, b), want + b.double()) <= 3e-2 * max(1.0, float(want.abs().max()))
         wide = torch.randn(m, k + 8, generator=g).to(torch.bfloat16).to(DEV)   # strided rows
         assert max_err(ops.linear(wide[:, :k], w), wide[:, :k].double() @ w.double().T) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+# ------------------------------------------------------------------------------------------------ tcgen05 products
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 1152, 896), (2048, 896, 4864), (130, 136, 72), (1, 8, 8)])
+def test_tc_gemm_plain(ops, m, n, k):
+    g = torch.Generator().manual_seed(40)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    e = err_word()
+    ops.tc_gemm(ops.TC_PLAIN, x, w, out, e)
+    want = x.double() @ w.double().T
+    assert int(e) == 0 and max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 64, 64), (300, 200, 896), (2048, 4864, 896), (70, 72, 120)])
+def test_tc_gemm_swiglu(ops, m, inter, k):
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.full((m, inter), 7.0, dtype=torch.bfloat16, device=DEV)
+    e = err_word()
+    ops.tc_gemm(ops.TC_SWIGLU, x, w, out, e)
+    gu = x.double() @ w.double().T
+    want = gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]
+    assert int(e) == 0 and max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+def test_tc_gemm_refuses_misaligned_shapes(ops):
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    assert not ops.tc_gemm_takes(x, w)
+    with pytest.raises(ops.KernelError):
+        ops.tc_gemm(ops.TC_PLAIN, x, w, torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV))
