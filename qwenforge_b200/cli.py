@@ -55,6 +55,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     p.add_argument("--stop-token-ids", default="", help="comma list; default: the model's eos token")
     p.add_argument("--ignore-eos", action="store_true", help="always generate the full budget, as the reference does")
     p.add_argument("--no-graphs", action="store_true", help="decode step by step instead of replaying CUDA graphs")
+    p.add_argument("--own-gemm", action="store_true",
+                   help="run the projections of steps with 128 or more tokens on the library's own tcgen05 kernel "
+                        "instead of cuBLAS (slower at present; see ops/linear.py)")
     p.add_argument("--prompt", action="append", default=None, help="generate text for this prompt (repeatable) and exit")
     args = p.parse_args(argv)
     if not args.model and not args.random_weights:
@@ -105,6 +108,9 @@ def main(argv=None) -> int:
     from .engine import StudentEngine
     from .weights import write_random_model
 
+    if args.own_gemm:
+        from .ops import use_own_tensor_core_products
+        use_own_tensor_core_products(True)
     holder = None
     model_path = args.model
     if args.random_weights:

@@ -2,11 +2,11 @@
 // accumulation in tensor memory:   C[M][N] = A[M][K] * W[N][K]^T
 // with the feed-forward's gate fused in:  EPI_SWIGLU writes silu(gate) * up for W = [gate rows | up rows].
 //
-// One block computes one 128 x 128 tile of C. Operand tiles of 128 rows x 64 columns (128 bytes per row) are
+// One block computes one 128 x 128 or 128 x 256 tile of C. Operand tiles of 128 rows x 64 columns (128 bytes per row) are
 // brought into shared memory by the tensor memory accelerator (2-D tiled copies with the 128-byte swizzle that
 // the tensor cores read) through a ring of stages. Thread 0 of warp 0 issues the copies, thread 0 of warp 1 issues
-// the tcgen05.mma instructions (four of K = 16 per stage) whose accumulator is 128 lanes x 128 columns of tensor
-// memory; `tcgen05.commit` hands a stage back when its products have been read, and signals the epilogue at the
+// the tcgen05.mma instructions (four of K = 16 per stage) whose accumulator is 128 lanes x 128 or 256 columns of
+// tensor memory; `tcgen05.commit` hands a stage back when its products have been read, and signals the epilogue at the
 // end. All four warps then read their 32 accumulator lanes with tcgen05.ld, apply the epilogue and store.
 // Two blocks fit an SM, so one block's epilogue overlaps the other's products. Every wait on a barrier is bounded;
 // a wait that runs out sets QF_ERR_COPY_TIMEOUT, and the block still frees its tensor memory and returns.
@@ -18,11 +18,14 @@
 enum { TC_PLAIN = 0, TC_SWIGLU = 1 };
 
 #define TC_BM 128
-#define TC_BN 128
 #define TC_BK 64
-#define TC_STAGES 3
-#define TC_STAGE_BYTES ((TC_BM + TC_BN) * TC_BK * 2)
 #define TC_THREADS 128
+// tile width BN: 128 (three stages of 32 KB, two blocks per SM) or 256 (four stages of 48 KB, one block per SM)
+template <int BN> struct TcGeometry {
+    static constexpr int stages = BN == 128 ? 3 : 4;
+    static constexpr int stage_bytes = (TC_BM + BN) * TC_BK * 2;
+    static constexpr size_t smem = (size_t)stages * stage_bytes + 1024;
+};
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -38,17 +41,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* p) {
     return (uint64_t)((smem_addr(p) & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Instruction descriptor: float32 accumulator, bf16 A and B, both K-major, N = 128, M = 128.
-#define TC_IDESC ((1u << 4) | (1u << 7) | (1u << 10) | ((TC_BN >> 3) << 17) | ((TC_BM >> 4) << 24))
+// Instruction descriptor: float32 accumulator, bf16 A and B, both K-major, N = BN, M = 128.
+template <int BN> __device__ __forceinline__ constexpr uint32_t tc_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p; \n\t"
         "}\n" ::"r"(tmem_c),
-        "l"(desc_a), "l"(desc_b), "r"(TC_IDESC), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -69,12 +74,14 @@ __device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, bf16* __restrict__ out,
                int M, int n_out, int K, int inter, int ldo, int* err) {
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    constexpr int TC_STAGES = TcGeometry<BN>::stages, TC_STAGE_BYTES = TcGeometry<BN>::stage_bytes;
+    constexpr int HALF = BN / 2;  // TC_SWIGLU: gate columns [0, HALF), up columns [HALF, BN)
     __shared__ __align__(8) uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], acc_bar;
     __shared__ uint32_t tmem_base_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,7 +96,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(&acc_bar, 1);
     }
     if (warp == 0) {  // one warp allocates the accumulator: 128 columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TC_BN));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(BN));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     tc_fence_before();
@@ -110,12 +117,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
             mbar_expect_tx(&full_bar[s], TC_STAGE_BYTES);
             tma_load_2d(a_s, &map_a, kb * TC_BK, tile_m * TC_BM, &full_bar[s]);
-            if (EPI == TC_SWIGLU) {  // 64 gate rows, then the 64 matching up rows
-                tma_load_2d(b_s, &map_b, kb * TC_BK, tile_n * 64, &full_bar[s]);
-                tma_load_2d(b_s + 64 * TC_BK * 2, &map_b, kb * TC_BK, inter + tile_n * 64, &full_bar[s]);
-            } else {
-                tma_load_2d(b_s, &map_b, kb * TC_BK, tile_n * TC_BN, &full_bar[s]);
-                tma_load_2d(b_s + 64 * TC_BK * 2, &map_b, kb * TC_BK, tile_n * TC_BN + 64, &full_bar[s]);
+#pragma unroll
+            for (int box = 0; box < BN / 64; ++box) {  // boxes of 64 weight rows
+                int w_row = tile_n * BN + 64 * box;
+                if (EPI == TC_SWIGLU)  // HALF gate rows, then the HALF matching up rows
+                    w_row = 64 * box < HALF ? tile_n * HALF + 64 * box : inter + tile_n * HALF + (64 * box - HALF);
+                tma_load_2d(b_s + (size_t)box * 64 * TC_BK * 2, &map_b, kb * TC_BK, w_row, &full_bar[s]);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -132,7 +139,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint64_t da = smem_desc_sw128(a_s), db = smem_desc_sw128(b_s);
 #pragma unroll
             for (int k4 = 0; k4 < TC_BK / 16; ++k4)  // 16 columns = 32 bytes = 2 units of the address field
-                umma_bf16(tmem_acc, da + 2 * k4, db + 2 * k4, (kb > 0 || k4 > 0) ? 1u : 0u);
+                umma_bf16(tmem_acc, da + 2 * k4, db + 2 * k4, tc_idesc<BN>(), (kb > 0 || k4 > 0) ? 1u : 0u);
             umma_commit(&empty_bar[s]);  // arrives when these products have finished reading the stage
         }
         umma_commit(&acc_bar);           // arrives when every product has finished
@@ -147,11 +154,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
     if (EPI == TC_SWIGLU) {
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
             uint32_t g[32], u[32];
             tmem_load_32(lane_base + c0, g);
-            tmem_load_32(lane_base + 64 + c0, u);
-            const int col = tile_n * 64 + c0;
+            tmem_load_32(lane_base + HALF + c0, u);
+            const int col = tile_n * HALF + c0;
             if (row < M && col < n_out) {
                 uint32_t packed[16];
 #pragma unroll
@@ -172,10 +179,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
 #pragma unroll
-        for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t v[32];
             tmem_load_32(lane_base + c0, v);
-            const int col = tile_n * TC_BN + c0;
+            const int col = tile_n * BN + c0;
             if (row < M && col < n_out) {
                 uint32_t packed[16];
 #pragma unroll
@@ -194,7 +201,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem_acc), "r"(TC_BN));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem_acc), "r"(BN));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -227,6 +234,16 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int EPI, int BN>
+static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n_out, int k, int inter, int ldo,
+                     int* err, dim3 grid, cudaStream_t stream) {
+    const size_t smem = TcGeometry<BN>::smem;
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, err);
+    return (int)cudaGetLastError();
+}
+
 // a [m][lda], w [n][ldw] (for TC_SWIGLU: n = 2 * inter, gate rows then up rows), out [m][ldo] with n columns
 // (TC_SWIGLU: inter columns). Needs k, lda, ldw, ldo multiples of 8 and 16-byte aligned bases; for TC_SWIGLU
 // inter a multiple of 8. Returns cudaErrorInvalidValue for what it does not take, cudaErrorNotSupported when
@@ -238,22 +255,19 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
     if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_b;
     if (!make_map(&map_a, a, m, k, lda, TC_BM) || !make_map(&map_b, w, n, k, ldw, 64)) return (int)cudaErrorNotSupported;
-    const size_t smem = (size_t)TC_STAGES * TC_STAGE_BYTES + 1024;
-    dim3 grid;
+    // wide tiles when there are enough of them to fill the SMs; narrow ones otherwise
+    const int out_cols = epilogue == TC_SWIGLU ? n / 2 : n;
+    const int m_tiles = (m + TC_BM - 1) / TC_BM;
     if (epilogue == TC_SWIGLU) {
         if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
         const int inter = n / 2;
-        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        grid = dim3((inter + 63) / 64, (m + TC_BM - 1) / TC_BM);
-        tc_gemm_kernel<TC_SWIGLU><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, inter, k, inter, ldo, err);
-    } else if (epilogue == TC_PLAIN) {
-        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        grid = dim3((n + TC_BN - 1) / TC_BN, (m + TC_BM - 1) / TC_BM);
-        tc_gemm_kernel<TC_PLAIN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n, k, 0, ldo, err);
-    } else {
-        return (int)cudaErrorInvalidValue;
+        const bool wide = (long long)m_tiles * ((inter + 127) / 128) >= 148;
+        return wide ? launch_tc<TC_SWIGLU, 256>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 127) / 128, m_tiles), stream)
+                    : launch_tc<TC_SWIGLU, 128>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 63) / 64, m_tiles), stream);
     }
-    return (int)cudaGetLastError();
+    if (epilogue != TC_PLAIN) return (int)cudaErrorInvalidValue;
+    const bool wide = (long long)m_tiles * ((out_cols + 255) / 256) >= 148;
+    return wide ? launch_tc<TC_PLAIN, 256>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 255) / 256, m_tiles), stream)
+                : launch_tc<TC_PLAIN, 128>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, m_tiles), stream);
 }
+

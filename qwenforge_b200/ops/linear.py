@@ -13,6 +13,23 @@ import torch
 
 from . import kernels
 
+# Products of 128 or more token rows can run on this library's own tcgen05 kernel (`csrc/tc_gemm.cu`) instead of the
+# cuBLAS call. Off by default: measured on a B200 at 2048 x 9728 x 896 it reaches 665 TFLOP/s where cuBLAS reaches
+# 1,150, and fused with the SwiGLU gate 60 microseconds where cuBLAS plus the gate kernel need 46.
+_own_tensor_core_products = False
+OWN_PRODUCT_MIN_ROWS = 128
+
+
+def use_own_tensor_core_products(on: bool) -> None:
+    global _own_tensor_core_products
+    _own_tensor_core_products = bool(on)
+
+
+def own_tensor_core_products(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether x @ weight.T is to run on the library's own tcgen05 kernel."""
+    return (_own_tensor_core_products and x.dtype == torch.bfloat16 and x.shape[0] >= OWN_PRODUCT_MIN_ROWS
+            and weight.shape[0] % 8 == 0 and kernels.tc_gemm_takes(x, weight))
+
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -28,6 +45,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return out
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise kernels.KernelError(f"linear: dtypes {x.dtype} x {weight.dtype} are not supported")
+    if out_dtype != torch.float32 and bias is None and own_tensor_core_products(x, weight):
+        if out is None:
+            out = torch.empty((m, n), device=x.device, dtype=torch.bfloat16)
+        kernels.tc_gemm(kernels.TC_PLAIN, x, weight, out)
+        return out
     if out_dtype == torch.float32:
         result = torch.mm(x, weight.t(), out_dtype=torch.float32)
         if bias is not None:

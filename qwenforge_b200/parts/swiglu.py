@@ -26,7 +26,7 @@ class SwiGlu(FeedForward):
         ]
 
     def kernel_libraries(self, dtype):
-        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm"})
+        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm", "tc_gemm"})
 
     def bind(self, tensors, dtype, device):
         self.gate_up_weight = torch.cat((tensors[self.file_name("gate_weight")], tensors[self.file_name("up_weight")]),
@@ -34,8 +34,11 @@ class SwiGlu(FeedForward):
         self.down_weight = tensors[self.file_name("down_weight")]
 
     def forward(self, x, ctx):
-        gate_up = ops.linear(x, self.gate_up_weight)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        if self.inter % 8 == 0 and ops.own_tensor_core_products(x, self.gate_up_weight):
+            ops.tc_gemm(ops.TC_SWIGLU, x, self.gate_up_weight, act, ctx.err if ctx is not None else None)
+            return ops.linear(act, self.down_weight)
+        gate_up = ops.linear(x, self.gate_up_weight)
         ops.swiglu(gate_up, act)
         return ops.linear(act, self.down_weight)
 

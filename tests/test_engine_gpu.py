@@ -323,3 +323,21 @@ def test_real_layer_sizes(preset, layers, tmp_path):
             assert err <= bound, f"{preset} {dtype}: {err:.3e} > {bound:.3e}"
         del model, cache
         torch.cuda.empty_cache()
+
+
+def test_own_tensor_core_products_in_the_model(folders):
+    """With the library's own tcgen05 products switched on, a 200-token prompt gives the plain implementation's logits."""
+    from qwenforge_b200 import ops
+    model = get_model(folders, "small_64", torch.bfloat16)
+    tokens = random_tokens(ALL_CONFIGS["small_64"]["vocab_size"], 200, 900)
+    ref = plain_logits(folders, "small_64", tokens)
+    ops.use_own_tensor_core_products(True)
+    try:
+        cache = model.new_cache(512, 2)
+        slot = cache.open()
+        before = ops.kernels.launches
+        logits = model.step(cache, [(slot, tokens)], want=[list(range(200))])
+        model.raise_on_kernel_error()
+    finally:
+        ops.use_own_tensor_core_products(False)
+    assert_logits_close(logits, ref, torch.bfloat16, "own tcgen05 products")
