@@ -100,3 +100,16 @@ def test_too_small_a_cache_fails_loudly(tmp_path):
                            "--out", str(tmp_path / "o"), "--max-tokens", "64"], input=text, capture_output=True,
                           text=True, timeout=600)
     assert done.returncode != 0 and "CacheFull" in done.stderr
+
+
+def test_command_line_runs_a_small_suite(tmp_path):
+    done = subprocess.run([sys.executable, "-m", "qwenforge_b200.cli", "--random-weights", "tiny-b", "--dtype", "bfloat16",
+                           "--suites", "decode_throughput,ttft_prefill", "--decode-batch-sizes", "1,3",
+                           "--decode-prompt-lens", "5,9,17", "--ttft-prompt-lens", "33,64", "--max-new-tokens-decode", "12",
+                           "--timed-repeats", "2", "--output-dir", str(tmp_path / "out")],
+                          capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert done.returncode == 0, done.stderr[-2000:]
+    summary = json.loads((tmp_path / "out" / "summary.json").read_text())
+    rows = summary["results"]
+    assert [r["suite"] for r in rows] == ["decode_throughput", "decode_throughput", "ttft_prefill"]
+    assert rows[1]["batch_size"] == 3 and rows[1]["new_tokens"] == 3 * 12 and all(r["tokens_per_s"] > 0 for r in rows)
