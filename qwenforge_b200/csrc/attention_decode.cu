@@ -14,22 +14,28 @@
 // the ticket counter. No block waits for another. (Merging the splits of a thread-block cluster through
 // distributed shared memory instead was measured slower at these sizes: 19.8 against 14.4 microseconds.)
 // The kernel is launched as a programmatic dependent of the kernel before it.
-#include "mma.cuh"
+#include "tma.cuh"
 
-template <int D, int WARPS>
+// TMA: head sizes whose rows are a multiple of 128 bytes (64, 128) take the half pages by tiled copies of the tensor
+// memory accelerator (128-byte swizzle; one copy per 64 columns for the keys and as many for the values, completing
+// on the warp's own barrier with a bounded wait); other head sizes use 16-byte asynchronous copies into padded rows.
+template <int D, int WARPS, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
-decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
-                    const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
-                    int chunks, float scale_log2, int window, int n_splits, float* __restrict__ part_o,
-                    float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
+decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
+                    const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots,
+                    KvSite<bf16> site, int n_heads, int chunks, float scale_log2, int window, int n_splits,
+                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
-    constexpr int LD = D + 8;           // padded shared-memory row (bf16 elements): conflict-free ldmatrix
+    constexpr int LD = TMA ? D : D + 8;  // shared-memory row (bf16 elements): padded, or swizzled blocks of 64 columns
     constexpr int KS = D / 16;          // k-steps of Q K^T
     constexpr int NT = D / 8;           // n-tiles of P V
     constexpr int PAGE_BYTES = 2 * QF_PAGE * LD * 2;  // one warp's buffer: keys then values of a page
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ unsigned char smem_unaligned[];
+    // the swizzle of the tiled copies is a function of the shared-memory address: buffers start on 1024 bytes
+    unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     __shared__ float m_s[DEC_WARPS][16], l_s[DEC_WARPS][16];
     __shared__ int ticket_s;
+    __shared__ __align__(8) uint64_t bars[DEC_WARPS][2];
 
     grid_launch_dependents();
     grid_dependency_wait();
@@ -85,17 +91,49 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
     const int my_pages = p_begin + warp < p_end ? (p_end - p_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
     const int n_halves = 2 * my_pages;
     // half i of this warp: page p_begin + warp + (i / 2) * WARPS, positions key0 .. key0 + 31
+    // Element (row r, column c) of a staged half page: padded rows, or (TMA) blocks of 32 rows x 64 columns in which the
+    // 16-byte chunk index is XORed with the row (the 128-byte swizzle the tiled copy writes).
+    auto at = [&](const bf16* base, int r, int c) -> const bf16* {
+        if (TMA) return base + (size_t)(c >> 6) * (HALF * 64) + (size_t)r * 64 + ((((c >> 3) & 7) ^ (r & 7)) << 3) + (c & 7);
+        return base + (size_t)r * LD + c;
+    };
+    if (TMA && lane == 0) {
+        mbar_init(&bars[warp][0], 1);
+        mbar_init(&bars[warp][1], 1);
+    }
+    __syncwarp();
+    auto half_live = [&](int i, int& page, int& key0) {
+        if (i >= n_halves) return false;
+        const int p = p_begin + warp + (i >> 1) * DEC_WARPS;
+        key0 = p * QF_PAGE + (i & 1) * HALF;
+        page = table_row[p];
+        if (page < 0) {
+            if (lane == 0 && (i & 1) == 0) atomicOr(err, QF_ERR_NO_PAGE);
+            return false;
+        }
+        return key0 < L && key0 + HALF > lo;
+    };
     auto issue = [&](int i) {
-        if (i < n_halves) {
-            const int p = p_begin + warp + (i >> 1) * DEC_WARPS, key0 = p * QF_PAGE + (i & 1) * HALF;
-            const int page = table_row[p];
-            if (page < 0) {
-                if (lane == 0 && (i & 1) == 0) atomicOr(err, QF_ERR_NO_PAGE);
-            } else if (key0 < L && key0 + HALF > lo) {
+        int page, key0;
+        if (half_live(i, page, key0)) {
+            bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
+            bf16* vb = kb + HALF * LD;
+            if (TMA) {
+                if (lane == 0) {
+                    // row of the cache seen as one matrix [pages * 2 * kv_heads * 64][D]
+                    const long long k_row = ((long long)page * 2 * site.kv_heads + kvh) * QF_PAGE + (i & 1) * HALF;
+                    const long long v_row = k_row + (long long)site.kv_heads * QF_PAGE;
+                    uint64_t* bar = &bars[warp][i & 1];
+                    mbar_expect_tx(bar, 2 * HALF * D * 2);
+#pragma unroll
+                    for (int cb = 0; cb < D / 64; ++cb) {
+                        tma_load_2d(kb + (size_t)cb * HALF * 64, &kv_map, cb * 64, (int)k_row, bar);
+                        tma_load_2d(vb + (size_t)cb * HALF * 64, &kv_map, cb * 64, (int)v_row, bar);
+                    }
+                }
+            } else {
                 const bf16* kp = site.base + (long long)page * site.page_elems + ((long long)kvh * QF_PAGE + (i & 1) * HALF) * D;
                 const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
-                bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
-                bf16* vb = kb + HALF * LD;
                 constexpr int CH = D / 8;  // 16-byte chunks per row
 #pragma unroll 4
                 for (int j = lane; j < HALF * CH; j += 32) {
@@ -105,15 +143,23 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
                 }
             }
         }
-        cp_async_commit();  // one group per half, empty when there is nothing to fetch
+        if (!TMA) cp_async_commit();  // one group per half, empty when there is nothing to fetch
     };
+    uint32_t tma_uses[2] = {0, 0};  // completed fetches into each buffer (the parity the next wait looks for)
     issue(0);
     for (int i = 0; i < n_halves; ++i) {
         issue(i + 1);
-        cp_async_wait<1>();
-        __syncwarp();  // each lane waited for its own copies; together the half page is complete
-        const int p = p_begin + warp + (i >> 1) * DEC_WARPS, key0 = p * QF_PAGE + (i & 1) * HALF;
-        if (table_row[p] >= 0 && key0 < L && key0 + HALF > lo) {
+        int page_i, key0;
+        const bool live = half_live(i, page_i, key0);
+        if (TMA) {
+            // the barrier of this buffer is on its (i / 2)-th use; only halves that were fetched are waited for
+            if (live && !mbar_wait(&bars[warp][i & 1], tma_uses[i & 1] & 1) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
+            if (live) ++tma_uses[i & 1];
+        } else {
+            cp_async_wait<1>();
+            __syncwarp();  // each lane waited for its own copies; together the half page is complete
+        }
+        if (live) {
             const bf16* kb = stage0 + (size_t)(i & 1) * STAGE_ELEMS;
             const bf16* vb = kb + HALF * LD;
             float s[4][4];
@@ -124,7 +170,7 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
 #pragma unroll
                 for (int t2 = 0; t2 < 2; ++t2) {  // 16 keys per ldmatrix.x4
                     uint32_t kf[4];
-                    ldmatrix_x4(kf, kb + (size_t)(16 * t2 + (lane >> 4) * 8 + (lane & 7)) * LD + 16 * ks + ((lane >> 3) & 1) * 8);
+                    ldmatrix_x4(kf, at(kb, 16 * t2 + (lane >> 4) * 8 + (lane & 7), 16 * ks + ((lane >> 3) & 1) * 8));
                     mma_bf16_16816(s[2 * t2], qa[ks], kf[0], kf[1]);
                     mma_bf16_16816(s[2 * t2 + 1], qa[ks], kf[2], kf[3]);
                 }
@@ -185,7 +231,7 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
 #pragma unroll
                 for (int nt = 0; nt < NT; nt += 2) {
                     uint32_t vf[4];
-                    ldmatrix_x4_trans(vf, vb + (size_t)(16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + 8 * nt + (lane >> 4) * 8);
+                    ldmatrix_x4_trans(vf, at(vb, 16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7), 8 * nt + (lane >> 4) * 8));
                     mma_bf16_16816(o[nt], pa, vf[0], vf[1]);
                     mma_bf16_16816(o[nt + 1], pa, vf[2], vf[3]);
                 }
@@ -193,7 +239,7 @@ decode_split_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const in
         }
         __syncwarp();  // every lane has read this buffer before the copies of half i + 2 overwrite it
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
 
     // ---- merge the warps: common maximum, rescale, add up in shared memory in warp order
     if ((lane & 3) == 0) {
@@ -313,16 +359,23 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
                   float scale, int window, int n_splits, float* part_o, float* part_ml, int* counters, int* err,
                   cudaStream_t stream) {
-    constexpr int WARPS = D <= 64 ? 8 : 4;  // one page buffer per warp: 18 KB at D = 64, 35 KB at D = 128
+    constexpr int WARPS = D <= 64 ? 8 : 4;  // two half-page buffers per warp: 16 to 18 KB at D = 64, 33 to 35 KB at D = 128
+    constexpr bool TMA = D % 64 == 0;
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
-    const size_t smem = (size_t)WARPS * 2 * QF_PAGE * (D + 8) * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = (size_t)WARPS * 2 * QF_PAGE * (TMA ? D : D + 8) * sizeof(bf16) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D, WARPS, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
+    CUtensorMap kv_map = {};
+    if (TMA) {
+        // The cache of this entry as one matrix of rows of D elements. The map is given more rows than any cache has
+        // (its extent only bounds what a copy may address; copies address rows of held pages only).
+        if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE / 2)) return (int)cudaErrorNotSupported;
+    }
     dim3 grid(n_splits, kv_heads * chunks, n_seqs);
-    return (int)launch_pdl(decode_split_kernel<D, WARPS>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)q, (bf16*)out,
-                           cu_q, tok_pos, slots, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
-                           part_o, part_ml, counters, err);
+    return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
+                           (bf16*)out, cu_q, tok_pos, slots, site, n_heads, chunks, scale * 1.4426950408889634f, window,
+                           n_splits, part_o, part_ml, counters, err);
 }
 
 // Scratch (used when n_splits > 1): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml float32

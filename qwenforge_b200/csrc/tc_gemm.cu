@@ -11,9 +11,7 @@
 // Two blocks fit an SM, so one block's epilogue overlaps the other's products. Every wait on a barrier is bounded;
 // a wait that runs out sets QF_ERR_COPY_TIMEOUT, and the block still frees its tensor memory and returns.
 // Copies use no cluster multicast; every block loads its own tiles.
-#include <cuda.h>
-
-#include "mma.cuh"
+#include "tma.cuh"
 
 enum { TC_PLAIN = 0, TC_SWIGLU = 1 };
 
@@ -26,13 +24,6 @@ template <int BN> struct TcGeometry {
     static constexpr int stage_bytes = (TC_BM + BN) * TC_BK * 2;
     static constexpr size_t smem = (size_t)stages * stage_bytes + 1024;
 };
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-                     smem_addr(dst)),
-                 "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
-                 : "memory");
-}
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte swizzle:
 // start address / 16; leading byte offset 1 (unused for swizzled K-major); stride between 8-row groups 1024 bytes;
@@ -204,36 +195,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem_acc), "r"(BN));
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess &&
-            status == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A 2-D map over a row-major bf16 matrix [rows][ld], boxes of `box_rows` rows x 64 columns, 128-byte swizzle,
-// zeros outside the matrix.
-static bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int EPI, int BN>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n_out, int k, int inter, int ldo,
                      int* err, dim3 grid, cudaStream_t stream) {
@@ -254,7 +215,7 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8 || ldo % 8) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)out) % 16) return (int)cudaErrorInvalidValue;
     CUtensorMap map_a, map_b;
-    if (!make_map(&map_a, a, m, k, lda, TC_BM) || !make_map(&map_b, w, n, k, ldw, 64)) return (int)cudaErrorNotSupported;
+    if (!qf_make_map_bf16(&map_a, a, m, k, lda, TC_BM) || !qf_make_map_bf16(&map_b, w, n, k, ldw, 64)) return (int)cudaErrorNotSupported;
     // wide tiles when there are enough of them to fill the SMs; narrow ones otherwise
     const int out_cols = epilogue == TC_SWIGLU ? n / 2 : n;
     const int m_tiles = (m + TC_BM - 1) / TC_BM;
