@@ -76,6 +76,8 @@ struct SkinnyPlan {
     int per;       // k-blocks (of 32) per slice
     int stride_w;  // bytes between weight rows in shared memory (16 modulo 128: conflict-free ldmatrix)
     int stride_x;  // bytes between token rows in shared memory (16 modulo 128: conflict-free fragment loads)
+    int rounds;    // tile batches a block works through, one after another, two weight buffers in turn (1: all at once)
+    int nblk;      // blocks (clusters) launched; in round r a block takes tile batch  its index + r * nblk
 };
 
 static inline int pad_to_16_mod_128(int bytes) { return bytes + ((16 - bytes % 128) + 128) % 128; }
@@ -83,62 +85,79 @@ static inline int pad_to_16_mod_128(int bytes) { return bytes + ((16 - bytes % 1
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 
-template <int NT, int EPI, bool NORM>
+// STREAM: the block works through several tile batches (plan.rounds > 1); without it the loop and the second
+// buffer compile away.
+template <int NT, int EPI, bool NORM, bool STREAM>
 __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const SkinnyArgs a, const SkinnyPlan plan) {
     namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t w_bar;
+    __shared__ __align__(8) uint64_t w_bar[2];
     constexpr int MP = 8 * NT;
-    const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per;
-    unsigned char* w_s = smem_raw;                                           // [tpb * 16][stride_w]
-    const size_t w_bytes = max((size_t)tpb * 16 * plan.stride_w, (size_t)SK_WARPS * NT * 4 * 32 * 4);
-    unsigned char* x_s = w_s + w_bytes;                                      // [MP][stride_x]
-    // after the products, the weights' space holds the partial sums: red [SK_WARPS][NT * 4][32] floats
-    float* red = reinterpret_cast<float*>(w_s);
+    const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per, rounds = STREAM ? plan.rounds : 1;
+    // weights [tpb * 16][stride_w], one buffer, or two when the block works through several tile batches
+    const size_t w_bytes = rounds > 1 ? (size_t)tpb * 16 * plan.stride_w
+                                      : max((size_t)tpb * 16 * plan.stride_w, (size_t)SK_WARPS * NT * 4 * 32 * 4);
+    unsigned char* w_base = smem_raw;
+    unsigned char* x_s = w_base + (rounds > 1 ? 2 : 1) * w_bytes;            // [MP][stride_x]
     float* part = reinterpret_cast<float*>(x_s + (size_t)MP * plan.stride_x);  // [ksplit - 1][tpb][NT * 4][32]
+    // partial sums of the warps, red [SK_WARPS][NT * 4][32] floats: a single tile batch lends them the weights'
+    // space once its products are done; with several batches the weights stay in use and red has its own space
+    float* red = rounds > 1 ? part + (size_t)(ksplit - 1) * tpb * NT * 4 * 32 : reinterpret_cast<float*>(w_base);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int rank = ksplit > 1 ? (int)(blockIdx.x % ksplit) : 0;
-    const int block = blockIdx.x / ksplit;
+    const int block0 = blockIdx.x / ksplit;
     const int n_kb = (a.k + 31) / 32;
     const int kb_begin = rank * per, kb_count = max(0, min(per, n_kb - kb_begin));
     const int k_begin = kb_begin * 32;
     const int kslice = per * 32;
 
-    // ---- all of this block's weights go in flight at once: one bulk asynchronous copy per weight row slice,
-    // issued by the lanes of warp 0 and completing on one shared-memory barrier
+    // ---- the weights of a tile batch go in flight at once: one bulk asynchronous copy per weight row slice, issued by
+    // the lanes of warp 0 and completing on the buffer's shared-memory barrier; the other warps zero what no copy fills
     const int slice_bytes = max(0, min(per * 64, (a.k - k_begin) * 2));  // valid bytes of a row slice (multiple of 16)
-    if (warp == 0) {
-        if (lane == 0) mbar_init(&w_bar, 1);
-        __syncwarp();
-        uint32_t mine = 0;
-        for (int row = lane; row < tpb * 16; row += 32) {
-            int ra, rb;
-            tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
-            if (((row & 15) < 8 ? ra : rb) >= 0) mine += slice_bytes;
+    if (warp == 0) {  // warp 0 alone touches the barriers until the block-wide barrier after the token rows are staged
+        if (lane == 0) {
+            mbar_init(&w_bar[0], 1);
+            mbar_init(&w_bar[1], 1);
         }
-        const uint32_t total = warp_sum_u32(mine);
-        if (lane == 0) mbar_expect_tx(&w_bar, total);
         __syncwarp();
-        if (slice_bytes > 0)
+    }
+    auto fetch = [&](int round) {
+        unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
+        const int block = block0 + round * plan.nblk;
+        if (warp == 0) {
+            uint32_t mine = 0;
             for (int row = lane; row < tpb * 16; row += 32) {
                 int ra, rb;
                 tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
-                const int grow = (row & 15) < 8 ? ra : rb;
-                if (grow >= 0)
-                    bulk_copy_g2s(w_s + (size_t)row * plan.stride_w, a.w + (size_t)grow * a.ldw + k_begin, slice_bytes, &w_bar);
+                if (((row & 15) < 8 ? ra : rb) >= 0) mine += slice_bytes;
             }
-    } else {
-        // rows that do not exist, and the tail of a slice beyond K, must be zero: they meet zero token values
-        const int tail16 = (per * 64 - slice_bytes) / 16;
-        for (int row = warp - 1; row < tpb * 16; row += SK_WARPS - 1) {
-            int ra, rb;
-            tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
-            const bool exists = ((row & 15) < 8 ? ra : rb) >= 0;
-            const int first = exists ? slice_bytes / 16 : 0, count = exists ? tail16 : per * 4;
-            for (int c = lane; c < count; c += 32)
-                *reinterpret_cast<uint4*>(w_s + (size_t)row * plan.stride_w + (size_t)(first + c) * 16) = make_uint4(0, 0, 0, 0);
+            const uint32_t total = warp_sum_u32(mine);
+            if (lane == 0) mbar_expect_tx(&w_bar[round & 1], total);
+            __syncwarp();
+            if (slice_bytes > 0)
+                for (int row = lane; row < tpb * 16; row += 32) {
+                    int ra, rb;
+                    tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
+                    const int grow = (row & 15) < 8 ? ra : rb;
+                    if (grow >= 0)
+                        bulk_copy_g2s(w_s + (size_t)row * plan.stride_w, a.w + (size_t)grow * a.ldw + k_begin, slice_bytes,
+                                      &w_bar[round & 1]);
+                }
+        } else {
+            // rows that do not exist, and the tail of a slice beyond K, must be zero: they meet zero token values
+            const int tail16 = (per * 64 - slice_bytes) / 16;
+            for (int row = warp - 1; row < tpb * 16; row += SK_WARPS - 1) {
+                int ra, rb;
+                tile_rows<EPI>(a, block * tpb + (row >> 4), row & 7, ra, rb);
+                const bool exists = ((row & 15) < 8 ? ra : rb) >= 0;
+                const int first = exists ? slice_bytes / 16 : 0, count = exists ? tail16 : per * 4;
+                for (int c = lane; c < count; c += 32)
+                    *reinterpret_cast<uint4*>(w_s + (size_t)row * plan.stride_w + (size_t)(first + c) * 16) = make_uint4(0, 0, 0, 0);
+            }
         }
-    }
+    };
+    fetch(0);
+    if (rounds > 1) fetch(1);
     grid_launch_dependents();
     grid_dependency_wait();  // weights are nobody's output; everything below reads what earlier kernels wrote
 
@@ -202,11 +221,15 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
             *reinterpret_cast<uint4*>(x_s + (size_t)m * plan.stride_x + c * 2) = v;
         }
     }
-    __syncthreads();  // the token rows are staged, and the barrier's initialisation is visible to every warp
-    if (!mbar_wait(&w_bar, 0) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
+    __syncthreads();  // the token rows are staged
+    const int wpt = SK_WARPS / tpb, tile_local = warp / wpt, sub = warp % wpt;
+    const bool tile_leader = sub == 0;
+    for (int round = 0; round < rounds; ++round) {
+    const unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
+    const int block = block0 + round * plan.nblk;
+    if (!mbar_wait(&w_bar[round & 1], (round >> 1) & 1) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
 
     // ---- products: the warps of a tile take its k-blocks in turn
-    const int wpt = SK_WARPS / tpb, tile_local = warp / wpt, sub = warp % wpt;
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -225,13 +248,13 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
         }
     }
     // ---- sum the warps of each tile in a fixed order, then the blocks of the cluster in rank order
-    __syncthreads();  // every warp is done with the weights: their space becomes `red`
+    __syncthreads();  // every warp is done with this buffer's weights
+    if (round + 2 < rounds) fetch(round + 2);  // the batch after next goes into the buffer that has just been read
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) red[((size_t)warp * NT * 4 + nt * 4 + e) * 32 + lane] = acc[nt][e];
     __syncthreads();
-    const bool tile_leader = sub == 0;
     if (tile_leader) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -252,8 +275,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                 for (int e = 0; e < 4; ++e) remote[(nt * 4 + e) * 32 + lane] = acc[nt][e];
         }
         cluster.sync();
-        if (rank > 0) return;
-        if (tile_leader) {
+        if (rank == 0 && tile_leader) {
             for (int r = 1; r < ksplit; ++r) {
                 const float* p = part + ((size_t)(r - 1) * tpb + tile_local) * NT * 4 * 32;
 #pragma unroll
@@ -262,8 +284,9 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                     for (int e = 0; e < 4; ++e) acc[nt][e] += p[(nt * 4 + e) * 32 + lane];
             }
         }
+        if (rounds > 1) cluster.sync();  // the first block has read the partial sums before the next batch overwrites them
     }
-    if (!tile_leader) return;
+    if (tile_leader && rank == 0) {
     int ra, rb;
     tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
     // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
@@ -327,13 +350,15 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
             }
         }
     }
+    }  // the lanes that own outputs
+    }  // tile batches
 }
 
 static size_t plan_smem(const SkinnyPlan& p, int nt) {
     size_t w = (size_t)p.tpb * 16 * p.stride_w;
     const size_t red = (size_t)SK_WARPS * nt * 4 * 32 * 4;
-    if (w < red) w = red;  // the partial sums reuse the weights' space
-    return w + (size_t)8 * nt * p.stride_x + (size_t)(p.ksplit - 1) * p.tpb * nt * 4 * 32 * 4;
+    if (p.rounds == 1 && w < red) w = red;  // a single batch lends the partial sums the weights' space
+    return (p.rounds > 1 ? 2 * w + red : w) + (size_t)8 * nt * p.stride_x + (size_t)(p.ksplit - 1) * p.tpb * nt * 4 * 32 * 4;
 }
 
 // How a product is cut into blocks: few tiles share their K among the blocks of a cluster so that every SM streams
@@ -341,13 +366,15 @@ static size_t plan_smem(const SkinnyPlan& p, int nt) {
 // repeated more often than needed.
 static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
     const int sms = 148, n_kb = (a.k + 31) / 32;
-    const size_t budget = 200 * 1024;
-    auto fill = [&](int tpb, int ksplit) {
+    const size_t budget = 200 * 1024, most = 224 * 1024;
+    auto fill = [&](int tpb, int ksplit, int rounds) {
         p.tpb = tpb;
         p.ksplit = ksplit;
         p.per = (n_kb + ksplit - 1) / ksplit;
         p.stride_w = pad_to_16_mod_128(p.per * 64);
         p.stride_x = pad_to_16_mod_128(p.per * 64);
+        p.rounds = rounds;
+        p.nblk = (tiles + tpb - 1) / tpb;
         return plan_smem(p, nt);
     };
     if (tiles <= sms) {
@@ -356,18 +383,29 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
         while (ksplit > 1 && (n_kb + ksplit - 1) / ksplit < 4) --ksplit;
         if (ksplit == 3) ksplit = 2;
         for (; ksplit <= 8; ksplit *= 2)
-            if (fill(1, ksplit) <= budget) return true;
+            if (fill(1, ksplit, 1) <= budget) return true;
         return false;
     }
+    // every block resident at once, in one wave
     for (int tpb = 1; tpb <= 8; tpb *= 2) {
-        const size_t smem = fill(tpb, 1);
+        const size_t smem = fill(tpb, 1, 1);
         if (smem > budget) break;
         const int resident = (int)((227 * 1024) / (smem + 1024));
         const int blocks = (tiles + tpb - 1) / tpb;
         if (blocks <= sms * (resident > 3 ? 3 : resident)) return true;  // the launch bounds allow three blocks of 256 threads
     }
-    for (int ksplit = 1; ksplit <= 8; ksplit *= 2)
-        if (fill(1, ksplit) <= budget) return true;
+    // too many tiles for one wave: one block per SM (or cluster) streams its share of the tile batches through two
+    // weight buffers, the token rows staged once; K is split over a cluster where two buffers of whole rows do not fit
+    for (int ksplit = 1; ksplit <= 8; ksplit *= 2) {
+        for (int tpb = 2; tpb >= 1; --tpb) {
+            if (fill(tpb, ksplit, 2) > most) continue;
+            const int batches = (tiles + tpb - 1) / tpb, nblk = sms / ksplit;
+            p.nblk = batches < nblk ? batches : nblk;
+            p.rounds = (batches + p.nblk - 1) / p.nblk;
+            if (p.rounds == 1) fill(tpb, ksplit, 1), p.nblk = batches;
+            return true;
+        }
+    }
     return false;
 }
 
@@ -375,11 +413,11 @@ template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a,
     SkinnyPlan p;
     if (!make_plan(a, tiles, NT, p)) return (int)cudaErrorInvalidValue;
     const size_t smem = plan_smem(p, NT);
-    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    auto kernel = p.rounds > 1 ? skinny_gemm_kernel<NT, EPI, NORM, true> : skinny_gemm_kernel<NT, EPI, NORM, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const int blocks = (tiles + p.tpb - 1) / p.tpb;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(blocks * p.ksplit);
+    config.gridDim = dim3(p.nblk * p.ksplit);
     config.blockDim = dim3(SK_THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
@@ -392,7 +430,7 @@ template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a,
     attr[1].val.clusterDim.z = 1;
     config.attrs = attr;
     config.numAttrs = p.ksplit > 1 ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&config, skinny_gemm_kernel<NT, EPI, NORM>, a, p);
+    return (int)cudaLaunchKernelEx(&config, kernel, a, p);
 }
 
 template <int EPI, bool NORM> static int launch_epi(const SkinnyArgs& a, int tiles, cudaStream_t stream) {

@@ -411,7 +411,8 @@ def test_skinny_gemm_plain_and_residual(ops, m, n, k):
         assert torch.equal(one[0], out[m - 1])
 
 
-@pytest.mark.parametrize("m,inter,k", [(2, 4864, 896), (8, 200, 120), (13, 24, 64)])
+@pytest.mark.parametrize("m,inter,k", [(2, 4864, 896), (8, 200, 120), (13, 24, 64),
+                                       (16, 11008, 2048), (5, 18944, 3584)])   # streamed in several rounds
 def test_skinny_gemm_swiglu(ops, m, inter, k):
     g = torch.Generator().manual_seed(21)
     stream = torch.randn(m, k, generator=g).to(DEV)
@@ -456,6 +457,23 @@ def test_skinny_gemm_qkv(ops, m, nh, kvh, d, rotary):
     assert max_err(q1, q2) <= 3e-2 * max(1.0, float(q2.abs().max()))
     assert max_err(site_a.storage, site_b.storage) <= 3e-2 * max(1.0, float(site_b.storage.abs().max()))
     assert float(site_a.storage.float().abs().sum()) > 0
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 6400, 2048), (3, 5000, 3584), (9, 2400, 8192)])
+def test_skinny_gemm_streams_many_tiles_in_rounds(ops, m, n, k):
+    """More weight tiles than fit the SMs at once: blocks work through several batches with two weight buffers."""
+    g = torch.Generator().manual_seed(24)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.03).to(torch.bfloat16).to(DEV)
+    want = x.double() @ w.double().T
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    e = err_word()
+    ops.skinny_gemm(ops.EPI_PLAIN, w, x=x, out=out, err=e)
+    assert int(e) == 0 and max_err(out, want) <= 2e-3 * max(1.0, float(want.abs().max()))
+    hidden = torch.randn(m, n, generator=g).to(DEV)
+    before = hidden.clone()
+    ops.skinny_gemm(ops.EPI_RESIDUAL, w, x=x, residual=hidden, err=e)
+    assert int(e) == 0 and max_err(hidden, before.double() + want) <= 2e-3 * max(1.0, float(want.abs().max()))
 
 
 def test_skinny_gemm_refuses_what_it_does_not_take(ops):
