@@ -38,7 +38,6 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     __shared__ __align__(8) uint64_t bars[DEC_WARPS][2];
 
     grid_launch_dependents();
-    grid_dependency_wait();
     const int split = blockIdx.x, seq = blockIdx.z;
     const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
     const int G = n_heads / site.kv_heads;
@@ -51,6 +50,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     bf16* out_row = out + (size_t)tok * q_width + (size_t)head0 * D;
 
     if (slot < 0) {  // padding entry: defined output, no cache access, no ticket
+        grid_dependency_wait();
         if (split == 0)
             for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) out_row[i] = __float2bfloat16_rn(0.f);
         return;
@@ -60,26 +60,6 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     const int first_page = lo / QF_PAGE, last_page = (L - 1) / QF_PAGE;
     const int pps = (last_page - first_page + n_splits) / n_splits;  // ceil(pages / splits)
     const int p_begin = first_page + split * pps, p_end = min(p_begin + pps, last_page + 1);
-
-    // Q fragments: row r = lane / 4 (and r + 8) is query head head0 + r; rows beyond the group are zero
-    uint32_t qa[KS][4];
-    {
-        const int r0 = lane >> 2, r1 = r0 + 8, c = 2 * (lane & 3);
-        const bf16* q0 = q + (size_t)tok * q_width + (size_t)(head0 + r0) * D;
-        const bf16* q1 = q + (size_t)tok * q_width + (size_t)(head0 + r1) * D;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qa[ks][0] = r0 < n_g ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + c) : 0u;
-            qa[ks][1] = r1 < n_g ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + c) : 0u;
-            qa[ks][2] = r0 < n_g ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + 8 + c) : 0u;
-            qa[ks][3] = r1 < n_g ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + 8 + c) : 0u;
-        }
-    }
-
-    float o[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
     // ---- every warp works alone on whole pages: page p_begin + warp, then + WARPS, ... It takes a page in two halves
     // of 32 positions through two buffers, so that the second half (or the next page's first) is on its way while
@@ -146,7 +126,33 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         if (!TMA) cp_async_commit();  // one group per half, empty when there is nothing to fetch
     };
     uint32_t tma_uses[2] = {0, 0};  // completed fetches into each buffer (the parity the next wait looks for)
-    issue(0);
+    // Positions before the new token lie in the cache since earlier steps: a first half page that holds only such
+    // positions is fetched before this kernel waits for the one that wrote the new token's query, key and value.
+    const bool early = n_halves > 0 && (p_begin + warp) * QF_PAGE + HALF <= L - 1;
+    if (early) issue(0);
+    grid_dependency_wait();
+
+    // Q fragments: row r = lane / 4 (and r + 8) is query head head0 + r; rows beyond the group are zero
+    uint32_t qa[KS][4];
+    {
+        const int r0 = lane >> 2, r1 = r0 + 8, c = 2 * (lane & 3);
+        const bf16* q0 = q + (size_t)tok * q_width + (size_t)(head0 + r0) * D;
+        const bf16* q1 = q + (size_t)tok * q_width + (size_t)(head0 + r1) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qa[ks][0] = r0 < n_g ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + c) : 0u;
+            qa[ks][1] = r1 < n_g ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + c) : 0u;
+            qa[ks][2] = r0 < n_g ? *reinterpret_cast<const uint32_t*>(q0 + 16 * ks + 8 + c) : 0u;
+            qa[ks][3] = r1 < n_g ? *reinterpret_cast<const uint32_t*>(q1 + 16 * ks + 8 + c) : 0u;
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
+
+    if (!early) issue(0);
     for (int i = 0; i < n_halves; ++i) {
         issue(i + 1);
         int page_i, key0;
