@@ -126,10 +126,12 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         if (!TMA) cp_async_commit();  // one group per half, empty when there is nothing to fetch
     };
     uint32_t tma_uses[2] = {0, 0};  // completed fetches into each buffer (the parity the next wait looks for)
-    // Positions before the new token lie in the cache since earlier steps: a first half page that holds only such
-    // positions is fetched before this kernel waits for the one that wrote the new token's query, key and value.
-    const bool early = n_halves > 0 && (p_begin + warp) * QF_PAGE + HALF <= L - 1;
-    if (early) issue(0);
+    // Positions before the new token lie in the cache since earlier steps: the halves of the warp's first page that
+    // hold only such positions are fetched before this kernel waits for the one that wrote the new token's query,
+    // key and value.
+    const int page0_end = (p_begin + warp + 1) * QF_PAGE;
+    const int n_early = n_halves == 0 ? 0 : page0_end <= L - 1 ? 2 : page0_end - HALF <= L - 1 ? 1 : 0;
+    for (int i = 0; i < n_early; ++i) issue(i);
     grid_dependency_wait();
 
     // Q fragments: row r = lane / 4 (and r + 8) is query head head0 + r; rows beyond the group are zero
@@ -152,9 +154,9 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
-    if (!early) issue(0);
+    if (n_early == 0) issue(0);
     for (int i = 0; i < n_halves; ++i) {
-        issue(i + 1);
+        if (i + 1 >= n_early) issue(i + 1);
         int page_i, key0;
         const bool live = half_live(i, page_i, key0);
         if (TMA) {
@@ -247,62 +249,52 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     }
     if (!TMA) cp_async_wait<0>();
 
-    // ---- merge the warps: common maximum, rescale, add up in shared memory in warp order
+    // ---- merge the warps: every warp leaves its numerators, rescaled to the block's maximum, in its own page buffer
+    // (its copies are complete and nobody else read it); then all threads add the warps up, in warp order
     if ((lane & 3) == 0) {
         m_s[warp][lane >> 2] = m_run[0];
         m_s[warp][(lane >> 2) + 8] = m_run[1];
     }
     __syncthreads();
-    float* o_s = reinterpret_cast<float*>(smem_raw);  // [16][D] float32, over warp 0's page buffer (all reads are done)
-    float m_all[2], f[2];
+    constexpr int OLD = D + 8;  // float32 row stride (8 modulo 32): the 8-byte stores of a half warp meet no bank twice
+    float* o_w = reinterpret_cast<float*>(smem_raw + (size_t)warp * PAGE_BYTES);  // [16][OLD]
+    float f[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
-        m_all[r] = m_s[0][row];
+        float m_all = m_s[0][row];
 #pragma unroll
-        for (int w = 1; w < DEC_WARPS; ++w) m_all[r] = fmaxf(m_all[r], m_s[w][row]);
-        f[r] = exp2f(m_run[r] - m_all[r]);
+        for (int w = 1; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, m_s[w][row]);
+        f[r] = exp2f(m_run[r] - m_all);
     }
     if ((lane & 3) == 0) {
         l_s[warp][lane >> 2] = l_run[0] * f[0];
         l_s[warp][(lane >> 2) + 8] = l_run[1] * f[1];
     }
-    for (int w = 0; w < DEC_WARPS; ++w) {
-        if (warp == w) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int c = 8 * nt + 2 * (lane & 3), r0 = lane >> 2, r1 = r0 + 8;
-                if (w == 0) {
-                    o_s[r0 * D + c] = o[nt][0] * f[0];
-                    o_s[r0 * D + c + 1] = o[nt][1] * f[0];
-                    o_s[r1 * D + c] = o[nt][2] * f[1];
-                    o_s[r1 * D + c + 1] = o[nt][3] * f[1];
-                } else {
-                    o_s[r0 * D + c] += o[nt][0] * f[0];
-                    o_s[r0 * D + c + 1] += o[nt][1] * f[0];
-                    o_s[r1 * D + c] += o[nt][2] * f[1];
-                    o_s[r1 * D + c + 1] += o[nt][3] * f[1];
-                }
-            }
-        }
-        __syncthreads();
+    for (int nt = 0; nt < NT; ++nt) {
+        const int c = 8 * nt + 2 * (lane & 3), r0 = lane >> 2, r1 = r0 + 8;
+        *reinterpret_cast<float2*>(o_w + r0 * OLD + c) = make_float2(o[nt][0] * f[0], o[nt][1] * f[0]);
+        *reinterpret_cast<float2*>(o_w + r1 * OLD + c) = make_float2(o[nt][2] * f[1], o[nt][3] * f[1]);
     }
-    // block result: row r: maximum max_w m_s[w][r], sum sum_w l_s[w][r], numerator o_s[r][:]
-    if (n_splits == 1) {
-        for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
-            const int r = i / D;
-            float l = 0.f;
-#pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
-            out_row[i] = __float2bfloat16_rn(l > 0.f ? o_s[i] / l : 0.f);
-        }
-        return;
-    }
+    __syncthreads();
+    // block result: row r: maximum max_w m_s[w][r], sum sum_w l_s[w][r], numerator sum_w (warp w's buffer)[r][:]
     const size_t part_row0 = ((size_t)seq * n_heads + head0) * n_splits;  // partial index of (row 0, split 0)
     for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
         const int r = i / D, d = i % D;
-        part_o[(part_row0 + (size_t)r * n_splits + split) * D + d] = o_s[i];
+        float num = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) num += reinterpret_cast<const float*>(smem_raw + (size_t)w * PAGE_BYTES)[r * OLD + d];
+        if (n_splits == 1) {
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
+            out_row[i] = __float2bfloat16_rn(l > 0.f ? num / l : 0.f);
+        } else {
+            part_o[(part_row0 + (size_t)r * n_splits + split) * D + d] = num;
+        }
     }
+    if (n_splits == 1) return;
     if (threadIdx.x < n_g) {
         const int r = threadIdx.x;
         float m = m_s[0][r], l = 0.f;
@@ -315,47 +307,49 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     }
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) ticket_s = atomicAdd(counters + (size_t)seq * gridDim.y + blockIdx.y, 1);
-    __syncthreads();
-    if (ticket_s != n_splits - 1) return;
-    // the last block of this (sequence, kv head, chunk): every partial is visible now
-    __threadfence();
-    if (threadIdx.x == 0) counters[(size_t)seq * gridDim.y + blockIdx.y] = 0;
-    // (max, sum) of every (row, split) into shared memory with independent loads, then one warp per row turns
-    // them into weights exp2(m - M) and the row's denominator
-    float2* ml_s = reinterpret_cast<float2*>(smem_raw);  // [n_g][n_splits]; o_s has been written out above
-    __syncthreads();
-    for (int i = threadIdx.x; i < n_g * n_splits; i += DEC_THREADS)
-        ml_s[i] = __ldcg(reinterpret_cast<const float2*>(part_ml) + part_row0 + i);
-    __syncthreads();
-    for (int r = warp; r < n_g; r += DEC_WARPS) {
-        float m = QF_NEG_BIG;
-        for (int sp = lane; sp < n_splits; sp += 32) m = fmaxf(m, ml_s[r * n_splits + sp].x);
-        m = warp_max(m);
-        float den = 0.f;
-        for (int sp = lane; sp < n_splits; sp += 32) {
-            const float2 v = ml_s[r * n_splits + sp];
-            const float w = exp2f(v.x - m);
-            den += w * v.y;
-            ml_s[r * n_splits + sp].x = w;
+    if (threadIdx.x == 0) {
+        int* counter = counters + (size_t)seq * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        if (ticket == n_splits - 1) {
+            // the last block of this (sequence, kv head, chunk): every partial is visible after this fence; the
+            // block barrier below hands that on to the other threads
+            __threadfence();
+            *counter = 0;
         }
-        den = warp_sum(den);
-        if (lane == 0) l_s[0][r] = den;
+        ticket_s = ticket;
     }
     __syncthreads();
+    if (ticket_s != n_splits - 1) return;
+    // Every output element folds its row's partials in split order, eight at a time with independent loads, keeping
+    // a running maximum: out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s.
     for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
         const int r = i / D, d = i % D;
+        const float2* ml = reinterpret_cast<const float2*>(part_ml) + part_row0 + (size_t)r * n_splits;
         const float* po = part_o + (part_row0 + (size_t)r * n_splits) * D + d;
-        float num = 0.f;
+        float big = QF_NEG_BIG, den = 0.f, num = 0.f;
         for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float2 a[8];
             float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = sp0 + j < n_splits ? __ldcg(po + (size_t)(sp0 + j) * D) : 0.f;
+            for (int j = 0; j < 8; ++j) {
+                const bool in = sp0 + j < n_splits;
+                a[j] = in ? __ldcg(ml + sp0 + j) : make_float2(QF_NEG_BIG, 0.f);
+                v[j] = in ? __ldcg(po + (size_t)(sp0 + j) * D) : 0.f;
+            }
+            float top = big;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (sp0 + j < n_splits) num += ml_s[r * n_splits + sp0 + j].x * v[j];
+            for (int j = 0; j < 8; ++j) top = fmaxf(top, a[j].x);
+            const float keep = exp2f(big - top);
+            den *= keep;
+            num *= keep;
+            big = top;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float w = exp2f(a[j].x - big);
+                den += w * a[j].y;
+                num += w * v[j];
+            }
         }
-        const float den = l_s[0][r];
         out_row[i] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
 }
