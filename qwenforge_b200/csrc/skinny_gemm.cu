@@ -92,6 +92,8 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t w_bar[2];
+    __shared__ int pos_s[16];        // QKV: position of each token row
+    __shared__ long long dst_s[16];  // QKV: element offset of the row's (page, position) in the cache, -1: nothing to write
     constexpr int MP = 8 * NT;
     const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per, rounds = STREAM ? plan.rounds : 1;
     // weights [tpb * 16][stride_w], one buffer, or two when the block works through several tile batches
@@ -158,6 +160,27 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     };
     fetch(0);
     if (rounds > 1) fetch(1);
+    if (EPI == EPI_QKV && threadIdx.x >= SK_THREADS - 16) {
+        // Where each token row goes: positions, slots and page tables are written by copies and by kernels that are not
+        // launched as programmatic dependents, so they are complete before any kernel of this chain starts, and the
+        // chain of dependent loads is walked here, before the wait, instead of by the lanes that write the cache.
+        const int m = threadIdx.x - (SK_THREADS - 16);
+        int pos = 0;
+        long long dst = -1;
+        if (m < a.m) {
+            pos = a.tok_pos[m];
+            if (a.write_cache) {
+                const int slot = a.slots[a.tok_seq[m]];
+                if (slot >= 0) {
+                    const int page = a.table[(long long)slot * a.table_stride + pos / QF_PAGE];
+                    if (page < 0) atomicOr(a.err, QF_ERR_NO_PAGE);
+                    else dst = (long long)page * a.page_elems + (long long)(pos % QF_PAGE) * a.head_dim;
+                }
+            }
+        }
+        pos_s[m] = pos;
+        dst_s[m] = dst;
+    }
     grid_launch_dependents();
     grid_dependency_wait();  // weights are nobody's output; everything below reads what earlier kernels wrote
 
@@ -166,28 +189,40 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
         for (int m = warp; m < MP; m += SK_WARPS) {
             bf16* dst = reinterpret_cast<bf16*>(x_s + (size_t)m * plan.stride_x);
             if (m < a.m) {
-                // the row is read in batches of independent 16-byte loads (a.k is a multiple of 8), so that the sum of
-                // squares costs a few memory round trips, not one per element
-                const float4* h4 = reinterpret_cast<const float4*>(a.hidden + (size_t)m * a.k);
+                // Everything is asked for at once, in independent 16-byte loads (a.k is a multiple of 8): the first 1024
+                // columns of this block's slice with their norm weights, which the second pass needs, and the whole
+                // row for the sum of squares; the row costs one memory round trip, not one per pass.
+                const float* h = a.hidden + (size_t)m * a.k;
+                const float4* h4 = reinterpret_cast<const float4*>(h);
                 const int n4 = a.k / 4;
+                const bool whole = ksplit == 1;  // the slice is the row: its registers serve the sum of squares too
+                float4 keep[8];
+                uint2 nw[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int c = (u * 32 + lane) * 4, kk = k_begin + c;
+                    const bool in = c < kslice && kk < a.k;
+                    keep[u] = in ? *reinterpret_cast<const float4*>(h + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    nw[u] = in ? *reinterpret_cast<const uint2*>(a.norm_w + kk) : make_uint2(0u, 0u);
+                }
                 float ss = 0.f;
-                float4 v[8];  // the first 1024 columns stay in registers for the second pass
-                for (int base = 0; base < n4; base += 32 * 8) {
-                    float4 u8[8];
+                if (whole) {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
+                    for (int u = 0; u < 8; ++u)
+                        ss += keep[u].x * keep[u].x + keep[u].y * keep[u].y + keep[u].z * keep[u].z + keep[u].w * keep[u].w;
+                }
+                for (int base = whole ? 32 * 8 : 0; base < n4; base += 32 * 4) {
+                    float4 u4[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
                         const int i = base + u * 32 + lane;
-                        u8[u] = i < n4 ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                        u4[u] = i < n4 ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        ss += u8[u].x * u8[u].x + u8[u].y * u8[u].y + u8[u].z * u8[u].z + u8[u].w * u8[u].w;
-                        if (base == 0) v[u] = u8[u];
-                    }
+                    for (int u = 0; u < 4; ++u) ss += u4[u].x * u4[u].x + u4[u].y * u4[u].y + u4[u].z * u4[u].z + u4[u].w * u4[u].w;
                 }
                 ss = warp_sum(ss);
                 const float inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
-                const float* h = a.hidden + (size_t)m * a.k;
                 // column c of the slice is column k_begin + c of the row; the lane handles float4 groups u * 32 + lane
                 for (int base = 0; base < kslice; base += 32 * 4 * 8) {
 #pragma unroll
@@ -196,8 +231,11 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                         if (c >= kslice) continue;
                         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
                         uint2 wv = make_uint2(0u, 0u);
-                        if (kk < a.k) {
-                            x = (k_begin == 0 && base == 0) ? v[u] : *reinterpret_cast<const float4*>(h + kk);
+                        if (base == 0) {
+                            x = keep[u];
+                            wv = nw[u];
+                        } else if (kk < a.k) {
+                            x = *reinterpret_cast<const float4*>(h + kk);
                             wv = *reinterpret_cast<const uint2*>(a.norm_w + kk);
                         }
                         const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv.x);
@@ -227,6 +265,20 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     for (int round = 0; round < rounds; ++round) {
     const unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
     const int block = block0 + round * plan.nblk;
+    // RESIDUAL: the values this lane will add to are asked for now, so that the epilogue is a store, not a round trip
+    float res[NT][4];
+    if (EPI == EPI_RESIDUAL && tile_leader && rank == 0) {
+        int ra, rb;
+        tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int m = 8 * nt + 2 * t + e;
+                res[nt][e] = (m < a.m && ra >= 0) ? a.residual[(size_t)m * a.n + ra] : 0.f;
+                res[nt][2 + e] = (m < a.m && rb >= 0) ? a.residual[(size_t)m * a.n + rb] : 0.f;
+            }
+    }
     if (!mbar_wait(&w_bar[round & 1], (round >> 1) & 1) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
 
     // ---- products: the warps of a tile take its k-blocks in turn
@@ -311,15 +363,15 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                 }
             } else if (EPI == EPI_RESIDUAL) {
                 float* h = a.residual + (size_t)m * a.n;
-                if (ra >= 0) h[ra] += va;
-                if (rb >= 0) h[rb] += vb;
+                if (ra >= 0) h[ra] = res[nt][e] + va;
+                if (rb >= 0) h[rb] = res[nt][2 + e] + vb;
             } else if (EPI == EPI_SWIGLU) {
                 if (ra >= 0)
                     reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(va / (1.0f + expf(-va)) * vb);
             } else if (ra >= 0) {  // EPI_QKV
                 const int D = a.head_dim, head = ra / D, j = ra % D;  // rb is component j + D/2 of the same head
                 float oa = va, ob = vb;
-                const int pos = a.tok_pos[m];
+                const int pos = pos_s[m];
                 if (head < a.n_heads + a.kv_heads && a.inv_freq) {
                     // rotation pairs j with j + rot/2; the tile pairs j with j + D/2: the same when rot_dim == head_dim
                     float s, c;
@@ -331,21 +383,10 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                     bf16* qo = a.q_out + (size_t)m * a.n_heads * D + (size_t)head * D;
                     qo[j] = __float2bfloat16_rn(oa);
                     qo[j + D / 2] = __float2bfloat16_rn(ob);
-                } else if (a.write_cache) {
-                    const int slot = a.slots[a.tok_seq[m]];
-                    if (slot >= 0) {
-                        const int which = head < a.n_heads + a.kv_heads ? 0 : 1;
-                        const int h = head - a.n_heads - which * a.kv_heads;
-                        const int page = a.table[(long long)slot * a.table_stride + pos / QF_PAGE];
-                        if (page < 0) {
-                            atomicOr(a.err, QF_ERR_NO_PAGE);
-                        } else {
-                            bf16* dst = a.kv_base + (long long)page * a.page_elems +
-                                        ((long long)(which * a.kv_heads + h) * QF_PAGE + (pos % QF_PAGE)) * D;
-                            dst[j] = __float2bfloat16_rn(oa);
-                            dst[j + D / 2] = __float2bfloat16_rn(ob);
-                        }
-                    }
+                } else if (dst_s[m] >= 0) {  // keys are heads n_heads .., values follow them: [2][kv_heads] planes of a page
+                    bf16* dst = a.kv_base + dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D;
+                    dst[j] = __float2bfloat16_rn(oa);
+                    dst[j + D / 2] = __float2bfloat16_rn(ob);
                 }
             }
         }
