@@ -1,6 +1,7 @@
 // Weight-streaming matrix products for a handful of token rows (decode steps): out[m][n] = sum_k x[m][k] W[n][k],
 // M <= 16 rows, bf16 weights read once from HBM, with what surrounds the product fused in:
-//   prologue  NORM     x = rmsnorm(hidden) * norm_weight, from the float32 residual stream (statistics in float32)
+//   prologue  NORM     x = rmsnorm(hidden) * norm_weight, from the float32 residual stream (statistics in float32;
+//                      the rows enter the product scaled by norm_weight, the sums are divided by the row's rms)
 //   epilogue  PLAIN    out (bf16 or float32) = product (+ bias)
 //             RESIDUAL hidden[m][n] += product            (the float32 residual stream, in place)
 //             SWIGLU   out[m][i] = silu(gate_i) * up_i    (W = [gate rows | up rows])
@@ -92,6 +93,8 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t w_bar[2];
+    __shared__ float ss_s[16];       // NORM: sum of squares of each token row over this block's slice
+    __shared__ float ss_part[7][16]; // NORM: the same of the other blocks of the cluster, written into the first block
     __shared__ int pos_s[16];        // QKV: position of each token row
     __shared__ long long dst_s[16];  // QKV: element offset of the row's (page, position) in the cache, -1: nothing to write
     constexpr int MP = 8 * NT;
@@ -186,69 +189,44 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
 
     // ---- this block's slice of the token rows, normalised on the way if asked
     if (NORM) {
+        // rmsnorm(x) W^T = (x * norm_weight) W^T / rms(x): the rows go into the product scaled by the norm weights only,
+        // in one pass over this block's slice, and the row's 1 / rms, a float32 scalar, multiplies the sums in the
+        // epilogue. A block adds up the squares of its own slice; the blocks of a cluster add theirs in rank order.
         for (int m = warp; m < MP; m += SK_WARPS) {
             bf16* dst = reinterpret_cast<bf16*>(x_s + (size_t)m * plan.stride_x);
+            float ss = 0.f;
             if (m < a.m) {
-                // Everything is asked for at once, in independent 16-byte loads (a.k is a multiple of 8): the first 1024
-                // columns of this block's slice with their norm weights, which the second pass needs, and the whole
-                // row for the sum of squares; the row costs one memory round trip, not one per pass.
                 const float* h = a.hidden + (size_t)m * a.k;
-                const float4* h4 = reinterpret_cast<const float4*>(h);
-                const int n4 = a.k / 4;
-                const bool whole = ksplit == 1;  // the slice is the row: its registers serve the sum of squares too
-                float4 keep[8];
-                uint2 nw[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int c = (u * 32 + lane) * 4, kk = k_begin + c;
-                    const bool in = c < kslice && kk < a.k;
-                    keep[u] = in ? *reinterpret_cast<const float4*>(h + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    nw[u] = in ? *reinterpret_cast<const uint2*>(a.norm_w + kk) : make_uint2(0u, 0u);
-                }
-                float ss = 0.f;
-                if (whole) {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        ss += keep[u].x * keep[u].x + keep[u].y * keep[u].y + keep[u].z * keep[u].z + keep[u].w * keep[u].w;
-                }
-                for (int base = whole ? 32 * 8 : 0; base < n4; base += 32 * 4) {
-                    float4 u4[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int i = base + u * 32 + lane;
-                        u4[u] = i < n4 ? h4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) ss += u4[u].x * u4[u].x + u4[u].y * u4[u].y + u4[u].z * u4[u].z + u4[u].w * u4[u].w;
-                }
-                ss = warp_sum(ss);
-                const float inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
-                // column c of the slice is column k_begin + c of the row; the lane handles float4 groups u * 32 + lane
+                // column c of the slice is column k_begin + c of the row; the lane handles float4 groups u * 32 + lane,
+                // eight independent 16-byte loads (a.k is a multiple of 8) of the row and of the weights at a time
                 for (int base = 0; base < kslice; base += 32 * 4 * 8) {
+                    float4 x[8];
+                    uint2 wv[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         const int c = base + (u * 32 + lane) * 4, kk = k_begin + c;
+                        const bool in = c < kslice && kk < a.k;
+                        x[u] = in ? *reinterpret_cast<const float4*>(h + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        wv[u] = in ? *reinterpret_cast<const uint2*>(a.norm_w + kk) : make_uint2(0u, 0u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int c = base + (u * 32 + lane) * 4;
                         if (c >= kslice) continue;
-                        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                        uint2 wv = make_uint2(0u, 0u);
-                        if (base == 0) {
-                            x = keep[u];
-                            wv = nw[u];
-                        } else if (kk < a.k) {
-                            x = *reinterpret_cast<const float4*>(h + kk);
-                            wv = *reinterpret_cast<const uint2*>(a.norm_w + kk);
-                        }
-                        const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv.x);
-                        const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv.y);
+                        ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                        const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv[u].x);
+                        const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv[u].y);
                         uint2 o;
-                        o.x = pack_bf16(x.x * inv * __low2float(w01), x.y * inv * __high2float(w01));
-                        o.y = pack_bf16(x.z * inv * __low2float(w23), x.w * inv * __high2float(w23));
+                        o.x = pack_bf16(x[u].x * __low2float(w01), x[u].y * __high2float(w01));
+                        o.y = pack_bf16(x[u].z * __low2float(w23), x[u].w * __high2float(w23));
                         *reinterpret_cast<uint2*>(dst + c) = o;
                     }
                 }
             } else {
                 for (int c = lane; c < kslice; c += 32) dst[c] = __float2bfloat16_rn(0.f);
             }
+            ss = warp_sum(ss);
+            if (lane == 0) ss_s[m] = ss;
         }
     } else {
         const int chunks = kslice / 8;
@@ -326,6 +304,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
 #pragma unroll
                 for (int e = 0; e < 4; ++e) remote[(nt * 4 + e) * 32 + lane] = acc[nt][e];
         }
+        if (NORM && rank > 0 && threadIdx.x < MP) cluster.map_shared_rank(&ss_part[0][0], 0)[(rank - 1) * 16 + threadIdx.x] = ss_s[threadIdx.x];
         cluster.sync();
         if (rank == 0 && tile_leader) {
             for (int r = 1; r < ksplit; ++r) {
@@ -350,7 +329,13 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
         for (int e = 0; e < 2; ++e) {
             const int m = 8 * nt + 2 * t + e;
             if (m >= a.m) continue;
-            const float va = acc[nt][e] + bias_a, vb = acc[nt][2 + e] + bias_b;
+            float inv = 1.f;
+            if (NORM) {
+                float ss = ss_s[m];
+                for (int r = 1; r < ksplit; ++r) ss += ss_part[r - 1][m];
+                inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
+            }
+            const float va = acc[nt][e] * inv + bias_a, vb = acc[nt][2 + e] * inv + bias_b;
             if (EPI == EPI_PLAIN) {
                 if (a.out_f32) {
                     float* o = reinterpret_cast<float*>(a.out) + (size_t)m * a.ldo;

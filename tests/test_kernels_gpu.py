@@ -376,9 +376,12 @@ def test_attention_decode_padding_and_far_key(ops):
 
 # ------------------------------------------------------------------------------------------------ fused skinny products
 
-def _rms_rows(hidden, weight, eps):
+def _normed_product(hidden, weight, eps, w):
+    """rmsnorm(hidden) * weight times w^T with the kernel's one rounding of the operand: the rows enter the product
+    as bfloat16(hidden * weight), and the sums are divided by the row's root mean square in float32 or better."""
     x = hidden.double()
-    return (x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * weight.double()).to(torch.bfloat16).double()
+    scaled = (x * weight.double()).to(torch.bfloat16).double()
+    return (scaled @ w.double().T) * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps)
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
@@ -403,7 +406,7 @@ def test_skinny_gemm_plain_and_residual(ops, m, n, k):
     nw = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).to(DEV)
     out = torch.empty(m, n, dtype=torch.float32, device=DEV)
     ops.skinny_gemm(ops.EPI_PLAIN, w, hidden=stream, norm_weight=nw, eps=1e-5, out=out)
-    assert max_err(out, _rms_rows(stream, nw, 1e-5) @ w.double().T) <= bound / 10
+    assert max_err(out, _normed_product(stream, nw, 1e-5, w)) <= bound / 10
     # a row's result does not depend on the other rows of the call
     if m > 1:
         one = torch.empty(1, n, dtype=torch.float32, device=DEV)
@@ -420,7 +423,7 @@ def test_skinny_gemm_swiglu(ops, m, inter, k):
     w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
     out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
     ops.skinny_gemm(ops.EPI_SWIGLU, w, hidden=stream, norm_weight=nw, eps=1e-6, out=out)
-    gu = _rms_rows(stream, nw, 1e-6) @ w.double().T
+    gu = _normed_product(stream, nw, 1e-6, w)
     want = gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]
     assert max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
 
@@ -449,7 +452,7 @@ def test_skinny_gemm_qkv(ops, m, nh, kvh, d, rotary):
                     qkv=dict(n_heads=nh, site=ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d), inv_freq=inv_freq,
                              rot_dim=d if rotary else 0, tok_pos=tok_pos, tok_seq=tok_seq, slots=slots_t, q_out=q1,
                              write_cache=True, err=e))
-    qkv = (_rms_rows(stream, nw, 1e-6) @ w.double().T + b.double()).to(torch.float32)
+    qkv = (_normed_product(stream, nw, 1e-6, w) + b.double()).to(torch.float32)
     q2 = torch.empty(m, nh * d, dtype=torch.float32, device=DEV)
     site_b.storage = site_b.storage.float()
     ref.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, d if rotary else 0, nh, q2, site_b, True, None)
