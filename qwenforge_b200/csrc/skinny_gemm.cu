@@ -243,7 +243,16 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     for (int round = 0; round < rounds; ++round) {
     const unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
     const int block = block0 + round * plan.nblk;
-    // RESIDUAL: the values this lane will add to are asked for now, so that the epilogue is a store, not a round trip
+    // What the epilogue reads from global memory is asked for now, so that it ends in stores, not in round trips:
+    // bias and rotation frequency (constants), and for RESIDUAL the values this lane will add to
+    float bias_a = 0.f, bias_b = 0.f, freq = 0.f;
+    if (tile_leader && rank == 0) {
+        int ra, rb;
+        tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
+        if (a.bias && ra >= 0) bias_a = __bfloat162float(a.bias[ra]);
+        if (a.bias && rb >= 0) bias_b = __bfloat162float(a.bias[rb]);
+        if (EPI == EPI_QKV && a.inv_freq && ra >= 0) freq = a.inv_freq[ra % a.head_dim];
+    }
     float res[NT][4];
     if (EPI == EPI_RESIDUAL && tile_leader && rank == 0) {
         int ra, rb;
@@ -321,8 +330,6 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     int ra, rb;
     tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
     // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
-    const float bias_a = (a.bias && ra >= 0) ? __bfloat162float(a.bias[ra]) : 0.f;
-    const float bias_b = (a.bias && rb >= 0) ? __bfloat162float(a.bias[rb]) : 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -360,7 +367,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                 if (head < a.n_heads + a.kv_heads && a.inv_freq) {
                     // rotation pairs j with j + rot/2; the tile pairs j with j + D/2: the same when rot_dim == head_dim
                     float s, c;
-                    sincosf((float)pos * a.inv_freq[j], &s, &c);
+                    sincosf((float)pos * freq, &s, &c);
                     oa = va * c - vb * s;
                     ob = vb * c + va * s;
                 }
@@ -404,7 +411,11 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
         return plan_smem(p, nt);
     };
     if (tiles <= sms) {
+        // K is split only as far as a block's weights need it: up to 48 KB a block has them in flight long before its
+        // token rows are ready, and a cluster's exchange of partial sums would only add to the chain of waits
         int ksplit = 2 * sms / tiles;
+        const int by_bytes = (int)(((size_t)16 * a.k * 2 + 48 * 1024 - 1) / (48 * 1024));
+        if (ksplit > by_bytes) ksplit = by_bytes;
         if (ksplit > 4) ksplit = 4;
         while (ksplit > 1 && (n_kb + ksplit - 1) / ksplit < 4) --ksplit;
         if (ksplit == 3) ksplit = 2;
