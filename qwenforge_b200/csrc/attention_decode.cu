@@ -185,16 +185,26 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             }
             const bool full = key0 >= lo && key0 + HALF <= L;  // every key of the half is visible
             float mx[2] = {QF_NEG_BIG, QF_NEG_BIG};
+            if (full) {
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
+                for (int t = 0; t < 4; ++t) {
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
-                    const bool ok = full || (kj >= lo && kj < L);
-                    s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
-                    s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
-                    mx[0] = fmaxf(mx[0], s[t][e]);
-                    mx[1] = fmaxf(mx[1], s[t][2 + e]);
+                    for (int e = 0; e < 4; ++e) s[t][e] *= scale_log2;
+                    mx[0] = fmaxf(mx[0], fmaxf(s[t][0], s[t][1]));
+                    mx[1] = fmaxf(mx[1], fmaxf(s[t][2], s[t][3]));
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int kj = key0 + 8 * t + 2 * (lane & 3) + e;
+                        const bool ok = kj >= lo && kj < L;
+                        s[t][e] = ok ? s[t][e] * scale_log2 : QF_NEG_BIG;
+                        s[t][2 + e] = ok ? s[t][2 + e] * scale_log2 : QF_NEG_BIG;
+                        mx[0] = fmaxf(mx[0], s[t][e]);
+                        mx[1] = fmaxf(mx[1], s[t][2 + e]);
+                    }
                 }
             }
             float corr[2], sum[2] = {0.f, 0.f};
@@ -203,16 +213,17 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                corr[r] = exp2f(m_run[r] - m_new);
+                corr[r] = fast_exp2(m_run[r] - m_new);
                 m_run[r] = m_new;
             }
+            // A live half holds a visible key, and the one token's heads all see the same keys: the running maximum is
+            // a real score from here on, and a masked score (QF_NEG_BIG) gets the weight 2^(-huge) = 0.
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    // a masked score is QF_NEG_BIG: its weight is 0 even while the running maximum is QF_NEG_BIG too
-                    s[t][e] = s[t][e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][e] - m_run[0]) : 0.f;
-                    s[t][2 + e] = s[t][2 + e] > 0.5f * QF_NEG_BIG ? exp2f(s[t][2 + e] - m_run[1]) : 0.f;
+                    s[t][e] = fast_exp2(s[t][e] - m_run[0]);
+                    s[t][2 + e] = fast_exp2(s[t][2 + e] - m_run[1]);
                     sum[0] += s[t][e];
                     sum[1] += s[t][2 + e];
                 }
@@ -320,37 +331,54 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     }
     __syncthreads();
     if (ticket_s != n_splits - 1) return;
-    // Every output element folds its row's partials in split order, eight at a time with independent loads, keeping
-    // a running maximum: out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s.
-    for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
-        const int r = i / D, d = i % D;
-        const float2* ml = reinterpret_cast<const float2*>(part_ml) + part_row0 + (size_t)r * n_splits;
-        const float* po = part_o + (part_row0 + (size_t)r * n_splits) * D + d;
-        float big = QF_NEG_BIG, den = 0.f, num = 0.f;
+    // Every output element folds its row's partials in split order, eight at a time, keeping a running maximum:
+    // out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s. A thread takes two elements at once, so that the loads
+    // of both are in flight together.
+    const int n_out = n_g * D;
+    for (int i0 = threadIdx.x; i0 < n_out; i0 += 2 * DEC_THREADS) {
+        const float2* ml[2];
+        const float* po[2];
+        bool live[2];
+        float big[2] = {QF_NEG_BIG, QF_NEG_BIG}, den[2] = {0.f, 0.f}, num[2] = {0.f, 0.f};
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int i = i0 + x * DEC_THREADS;
+            live[x] = i < n_out;
+            const int r = live[x] ? i / D : 0, d = live[x] ? i % D : 0;
+            ml[x] = reinterpret_cast<const float2*>(part_ml) + part_row0 + (size_t)r * n_splits;
+            po[x] = part_o + (part_row0 + (size_t)r * n_splits) * D + d;
+        }
         for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
-            float2 a[8];
-            float v[8];
+            float2 a[2][8];
+            float v[2][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool in = sp0 + j < n_splits;
-                a[j] = in ? __ldcg(ml + sp0 + j) : make_float2(QF_NEG_BIG, 0.f);
-                v[j] = in ? __ldcg(po + (size_t)(sp0 + j) * D) : 0.f;
-            }
-            float top = big;
+            for (int x = 0; x < 2; ++x)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) top = fmaxf(top, a[j].x);
-            const float keep = exp2f(big - top);
-            den *= keep;
-            num *= keep;
-            big = top;
+                for (int j = 0; j < 8; ++j) {
+                    const bool in = live[x] && sp0 + j < n_splits;
+                    a[x][j] = in ? __ldcg(ml[x] + sp0 + j) : make_float2(QF_NEG_BIG, 0.f);
+                    v[x][j] = in ? __ldcg(po[x] + (size_t)(sp0 + j) * D) : 0.f;
+                }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float w = exp2f(a[j].x - big);
-                den += w * a[j].y;
-                num += w * v[j];
+            for (int x = 0; x < 2; ++x) {
+                float top = big[x];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) top = fmaxf(top, a[x][j].x);
+                const float keep = exp2f(big[x] - top);
+                den[x] *= keep;
+                num[x] *= keep;
+                big[x] = top;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float w = exp2f(a[x][j].x - top);
+                    den[x] += w * a[x][j].y;
+                    num[x] += w * v[x][j];
+                }
             }
         }
-        out_row[i] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+            if (live[x]) out_row[i0 + x * DEC_THREADS] = __float2bfloat16_rn(den[x] > 0.f ? num[x] / den[x] : 0.f);
     }
 }
 
