@@ -235,6 +235,31 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill")
 
 
+TC_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
+                         slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
+                         window: int, err: torch.Tensor) -> None:
+    """The same attention on the fifth-generation tensor cores (tcgen05, accumulators in tensor memory): blocks of
+    128 query rows; bfloat16, head sizes 64 and 128, cache pages without gaps."""
+    _dev("q", q, torch.bfloat16)
+    _dev("out", out, torch.bfloat16)
+    _dev("cache", site.storage, torch.bfloat16)
+    d = site.head_dim
+    if d not in TC_ATTENTION_HEAD_DIMS:
+        raise KernelError(f"attention_prefill_tc: head_dim {d} has no tcgen05 kernel (have {TC_ATTENTION_HEAD_DIMS}); "
+                          "use attention_prefill")
+    if q.shape[1] != n_heads * d or out.shape != q.shape:
+        raise KernelError("attention_prefill_tc: q/out widths do not match the head count")
+    if site.page_elems != 2 * site.kv_heads * site.storage.shape[-2] * d:
+        raise KernelError("attention_prefill_tc: the cache pages have gaps; use attention_prefill")
+    _check(library("attention_prefill_tc").qf_attention_prefill_tc(
+        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
+        _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
+        _I(max_q_len), _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill_tc")
+
+
 class DecodeScratch:
     """Scratch of the split-K decode attention: float32 partial numerators and (max, sum) pairs per
     (sequence, head, split), and the ticket counters (kept zero between calls by the kernel itself).

@@ -303,6 +303,31 @@ def test_attention_prefill(ops, nh, kvh, d, q_lens, starts, window):
     assert max_err(out, want) <= 3e-2
 
 
+TC_PREFILL_SHAPES = [
+    # nh, kvh, d, q_lens, starts, window
+    (14, 2, 64, [130, 3, 64], [0, 125, 0], 0),
+    (7, 1, 64, [1, 65, 200], [0, 63, 1], 0),
+    (4, 2, 128, [70, 129], [10, 0], 0),
+    (2, 1, 64, [700], [0], 0),                           # several blocks of rows, pages far left of the diagonal
+    (3, 3, 64, [300, 128], [100, 64], 150),              # window across blocks of rows
+    (16, 2, 128, [257], [0], 100),
+    (2, 2, 128, [40], [1000], 0),                        # a short continuation over a long cache
+]
+
+
+@pytest.mark.parametrize("nh,kvh,d,q_lens,starts,window", TC_PREFILL_SHAPES)
+def test_attention_prefill_tc(ops, nh, kvh, d, q_lens, starts, window):
+    out, want = run_attention(ops, "attention_prefill_tc", torch.bfloat16, nh, kvh, d, q_lens, starts, window)
+    assert max_err(out, want) <= 3e-2
+
+
+def test_attention_prefill_tc_padding_entry_and_refusal(ops):
+    out, want = run_attention(ops, "attention_prefill_tc", torch.bfloat16, 4, 2, 64, [3, 2, 70], [0, 0, 7], 0, slots=[1, -1, 0])
+    assert max_err(out, want) <= 3e-2 and float(out[3:5].float().abs().max()) == 0.0
+    with pytest.raises(ops.KernelError, match="head_dim 32"):
+        run_attention(ops, "attention_prefill_tc", torch.bfloat16, 5, 1, 32, [4], [0], 0)
+
+
 def test_attention_prefill_padding_entry_and_refusal(ops):
     out, want = run_attention(ops, "attention_prefill", torch.bfloat16, 4, 2, 64, [3, 2, 70], [0, 0, 7], 0, slots=[1, -1, 0])
     assert max_err(out, want) <= 3e-2 and float(out[3:5].float().abs().max()) == 0.0
