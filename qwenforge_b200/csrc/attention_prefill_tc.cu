@@ -2,26 +2,34 @@
 // cores (tcgen05), bf16, head sizes 64 and 128. Same contract as the mma.sync kernel of attention_prefill.cu: the
 // span's own keys are in the cache already, a query at position p sees keys max(0, p - window + 1) <= j <= p.
 //
-// A block of 128 threads serves 128 consecutive query tokens of one (sequence, query head); thread t owns query row
-// t, which is lane t of the block's tensor memory. Per 64-position page of the head's kv head:
-//   S = Q K^T     one thread issues D / 16 products of 128 x 64 x 16 into 64 columns of tensor memory; Q (once)
-//                 and the page's keys come by tiled copies of the tensor memory accelerator, 128-byte swizzle
-//   softmax       every thread loads its row of S (64 float32) into registers: maximum, base-2 exponentials and sum
-//                 need no exchange between threads; the weights go to shared memory as bf16 in the swizzled
-//                 K-major layout the tensor cores read
-//   PV            four products of 128 x D x 16, the page's values read as they lie (MN-major), into D further columns
-//   O             every thread folds its row of PV into its float32 running output, rescaled when the maximum moved
-// Keys and values of the next page are on their way while a page is worked on (two stages), and S of the next page
-// is issued together with PV, so that it is ready when the threads come back for it. Several blocks share an SM;
-// one's exponentials overlap another's products. Every wait on a barrier is bounded: a wait that runs out sets
-// QF_ERR_COPY_TIMEOUT, and the block still frees its tensor memory and returns. No copy uses cluster multicast.
+// A block serves 128 consecutive query tokens of one (sequence, query head). Thread t of its first four warps owns
+// query row t, which is lane t of the block's tensor memory; one thread of a fifth warp issues every copy and every
+// product. Per 64-position page of the head's kv head:
+//   S = Q K^T     D / 16 products of 128 x 64 x 16 into 64 columns of tensor memory; Q (once) and the page's keys
+//                 come by tiled copies of the tensor memory accelerator, 128-byte swizzle
+//   softmax       every row thread loads its row of S (64 float32) into registers: maximum, base-2 exponentials and
+//                 sum need no exchange between threads; the weights go to shared memory as bf16 in the swizzled
+//                 K-major layout the tensor cores read, and the thread arrives at a barrier of 128 arrivals
+//   PV            when all rows have arrived: S of the next page is issued first (the rows wait for nothing else), then
+//                 four products of 128 x D x 16, the page's values read as they lie (MN-major), ADDED to the
+//                 running output O in D further columns of tensor memory
+//   O             stays in tensor memory. The exponentials of a row are taken against a reference maximum that is
+//                 only moved when the true maximum has grown by more than 2^8 since (weights stay below 256, well
+//                 inside bf16 and float32); only then does the warp rescale its rows of O (load, multiply, store).
+//                 Numerator and denominator carry the same reference, so the quotient at the end is unchanged.
+// Keys and values of the page after next are fetched as soon as a page's products are done (two stages). There is
+// no block-wide barrier inside the loop: rows and issuer hand over through shared-memory barriers. Several blocks
+// share an SM; one's exponentials overlap another's products. Every wait on a barrier is bounded: a wait that runs
+// out sets QF_ERR_COPY_TIMEOUT and ends the thread's loop, and the block still frees its tensor memory and returns.
+// No copy uses cluster multicast.
 #include "tcgen05.cuh"
 
 #define TA_BM 128
-#define TA_THREADS 128
+#define TA_ROW_THREADS 128
+#define TA_THREADS 160  // four warps of row threads and the issuing warp
 
 template <int D>
-__global__ void __launch_bounds__(TA_THREADS)
+__global__ void __launch_bounds__(TA_THREADS, 3)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   bf16* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                   const int* __restrict__ slots, KvSite<bf16> site, int n_heads, float scale_log2, int window, int* err) {
@@ -37,9 +45,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     unsigned char* k_s = q_s + CB * Q_BLOCK;            // [2][CB][64][64]
     unsigned char* v_s = k_s + 2 * KV_BYTES;            // [2][CB][64][64]
     unsigned char* p_s = v_s + 2 * KV_BYTES;            // [128][64]
-    __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_pv;
+    __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_pv, bar_p;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_s;
 
     const int seq = blockIdx.z, head = blockIdx.y;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
@@ -61,8 +68,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int last_pos = pos0 + n_rows - 1;
     const int p_begin = (window > 0 ? max(0, pos0 - window + 1) : 0) / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
     const int n_tiles = p_end - p_begin;
-    const int row_pos = pos0 + t, row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
-    const int* table_row = site.table + (long long)slot * site.table_stride;
 
     if (t == 0) {
         mbar_init(&bar_q, 1);
@@ -70,9 +75,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         mbar_init(&bar_kv[1], 1);
         mbar_init(&bar_s, 1);
         mbar_init(&bar_pv, 1);
-        abort_s = 0;
+        mbar_init(&bar_p, TA_ROW_THREADS);
     }
-    if (warp == 0) {
+    if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
@@ -80,152 +85,210 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    bool timed_out = false;
+    // A warp waits as one: the loads and stores of tensor memory and the choice of the issuing lane are collective, so
+    // the lanes of a warp must leave their loop together if a wait runs out.
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0; };
 
-    // ---- what thread 0 does besides owning row 0
-    auto fetch_page = [&](int j) {  // keys and values of the j-th page of the run into stage j & 1
-        const int stage = j & 1;
-        int page = table_row[p_begin + j];
-        if (page < 0) {  // a page the sequence does not hold: reported; some held memory is read instead
-            atomicOr(err, QF_ERR_NO_PAGE);
-            page = 0;
-        }
-        // row of the cache seen as one matrix [pages * 2 * kv_heads * 64][D]
-        const long long k_row = ((long long)page * 2 * site.kv_heads + kvh) * QF_PAGE;
-        const long long v_row = k_row + (long long)site.kv_heads * QF_PAGE;
-        mbar_expect_tx(&bar_kv[stage], 2 * KV_BYTES);
-#pragma unroll
-        for (int cb = 0; cb < CB; ++cb) {
-            tma_load_2d(k_s + stage * KV_BYTES + cb * KV_BLOCK, &kv_map, cb * 64, (int)k_row, &bar_kv[stage]);
-            tma_load_2d(v_s + stage * KV_BYTES + cb * KV_BLOCK, &kv_map, cb * 64, (int)v_row, &bar_kv[stage]);
-        }
-    };
-    auto issue_s = [&](int j) {  // S = Q K^T of page j; false if its keys did not arrive
-        if (!mbar_wait(&bar_kv[j & 1], (j >> 1) & 1)) return false;
-        tc_fence_after();
-        const unsigned char* kb = k_s + (j & 1) * KV_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {  // 16 columns = 32 bytes = 2 units of the descriptor's address field
-            const uint64_t da = smem_desc_sw128(q_s + (ks / 4) * Q_BLOCK) + 2 * (ks % 4);
-            const uint64_t db = smem_desc_sw128(kb + (ks / 4) * KV_BLOCK) + 2 * (ks % 4);
-            umma_bf16(tmem, da, db, umma_idesc_bf16(TA_BM, QF_PAGE, false), ks > 0 ? 1u : 0u);
-        }
-        umma_commit(&bar_s);
-        return true;
-    };
-    auto issue_pv = [&](int j) {  // PV of page j: weights [128][64 keys] K-major, values [64 keys][D] as they lie
-        const unsigned char* vb = v_s + (j & 1) * KV_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < QF_PAGE / 16; ++kk) {  // 16 keys: 32 bytes of a weight row, two 8-row groups of the values
-            const uint64_t da = smem_desc_sw128(p_s) + 2 * kk;
-            const uint64_t db = smem_desc_mn_sw128(vb + kk * 2048, KV_BLOCK);
-            umma_bf16(tmem + PV_COL, da, db, umma_idesc_bf16(TA_BM, D, true), kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bar_pv);
-    };
-
-    if (t == 0) {
-        mbar_expect_tx(&bar_q, CB * Q_BLOCK);
-#pragma unroll
-        for (int cb = 0; cb < CB; ++cb) tma_load_2d(q_s + cb * Q_BLOCK, &q_map, head * D + cb * 64, q_begin + row0, &bar_q);
-        fetch_page(0);
-        if (n_tiles > 1) fetch_page(1);
-        if (!mbar_wait(&bar_q, 0) || !issue_s(0)) abort_s = 1;
-    }
-
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m_run = QF_NEG_BIG, l_run = 0.f;
-
-    for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait(&bar_s, j & 1)) abort_s = 1;
-        tc_fence_after();
-        float s[QF_PAGE];
+    if (warp == 4) {
         {
-            uint32_t raw[32];
-            tmem_load_32(lane_base, raw);
+            // ---- the issuing warp: copies and products. All lanes run the loop (uniform values); one lane issues.
+            const bool leader = elect_one();
+            const int* table_row = site.table + (long long)slot * site.table_stride;
+            auto fetch_page = [&](int j) {  // keys and values of the j-th page of the run into stage j & 1
+                const int stage = j & 1;
+                int page = table_row[p_begin + j];
+                if (page < 0) {  // a page the sequence does not hold: reported; some held memory is read instead
+                    if (leader) atomicOr(err, QF_ERR_NO_PAGE);
+                    page = 0;
+                }
+                // row of the cache seen as one matrix [pages * 2 * kv_heads * 64][D]
+                const long long k_row = ((long long)page * 2 * site.kv_heads + kvh) * QF_PAGE;
+                const long long v_row = k_row + (long long)site.kv_heads * QF_PAGE;
+                if (leader) {
+                    mbar_expect_tx(&bar_kv[stage], 2 * KV_BYTES);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(raw[i]);
-            tmem_load_32(lane_base + 32, raw);
+                    for (int cb = 0; cb < CB; ++cb) {
+                        tma_load_2d(k_s + stage * KV_BYTES + cb * KV_BLOCK, &kv_map, cb * 64, (int)k_row, &bar_kv[stage]);
+                        tma_load_2d(v_s + stage * KV_BYTES + cb * KV_BLOCK, &kv_map, cb * 64, (int)v_row, &bar_kv[stage]);
+                    }
+                }
+                __syncwarp();
+            };
+            // descriptors: an address field counts 16 bytes, so 16 columns of a K-major row (32 bytes) are 2 units
+            const uint64_t desc_q = smem_desc_sw128(q_s), desc_p = smem_desc_sw128(p_s);
+            const uint64_t desc_k = smem_desc_sw128(k_s), desc_v = smem_desc_mn_sw128(v_s, KV_BLOCK);
+            constexpr uint32_t idesc_s = umma_idesc_bf16(TA_BM, QF_PAGE, false), idesc_pv = umma_idesc_bf16(TA_BM, D, true);
+            auto issue_s = [&](int j) {  // S = Q K^T of page j; false if its keys did not arrive
+                if (!wait_all(&bar_kv[j & 1], (j >> 1) & 1)) return false;
+                tc_fence_after();
+                const uint64_t dk = desc_k + (uint64_t)((j & 1) * (KV_BYTES >> 4));
+                if (leader) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(raw[i]);
-        }
-        const int key0 = (p_begin + j) * QF_PAGE;
-        // a page that every row of the block sees whole needs no mask
-        const bool full = key0 + QF_PAGE - 1 <= pos0 && key0 >= (window > 0 ? max(0, pos0 + TA_BM - 1 - window + 1) : 0);
-        float corr, sum = 0.f;
-        if (full) {
-            float mx = s[0];
+                    for (int ks = 0; ks < D / 16; ++ks)
+                        umma_bf16(tmem, desc_q + (uint64_t)((ks / 4) * (Q_BLOCK >> 4) + 2 * (ks % 4)),
+                                  dk + (uint64_t)((ks / 4) * (KV_BLOCK >> 4) + 2 * (ks % 4)), idesc_s, ks > 0 ? 1u : 0u);
+                    umma_commit(&bar_s);
+                }
+                __syncwarp();
+                return true;
+            };
+            if (leader) {
+                mbar_expect_tx(&bar_q, CB * Q_BLOCK);
 #pragma unroll
-            for (int i = 1; i < QF_PAGE; ++i) mx = fmaxf(mx, s[i]);
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            corr = fast_exp2(m_run - m_new);
-            m_run = m_new;
-#pragma unroll
-            for (int i = 0; i < QF_PAGE; ++i) {
-                s[i] = fast_exp2(fmaf(s[i], scale_log2, -m_new));
-                sum += s[i];
+                for (int cb = 0; cb < CB; ++cb) tma_load_2d(q_s + cb * Q_BLOCK, &q_map, head * D + cb * 64, q_begin + row0, &bar_q);
             }
-        } else {
-            float mx = QF_NEG_BIG;
+            __syncwarp();
+            fetch_page(0);
+            if (n_tiles > 1) fetch_page(1);
+            timed_out = !wait_all(&bar_q, 0) || !issue_s(0);
+            for (int j = 0; j < n_tiles && !timed_out; ++j) {
+                if (!wait_all(&bar_p, j & 1)) {  // every row has read S and written its weights
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                // PV of page j: weights [128][64 keys] K-major; values [64 keys][D] as they lie, 16 keys are two groups
+                // of 8 rows (2048 bytes)
+                if (j + 1 < n_tiles && !issue_s(j + 1)) {  // S is free: every row has read it
+                    timed_out = true;
+                    break;
+                }
+                const uint64_t dv = desc_v + (uint64_t)((j & 1) * (KV_BYTES >> 4));
+                if (leader) {
 #pragma unroll
-            for (int i = 0; i < QF_PAGE; ++i) {
-                const int kj = key0 + i;
-                s[i] = (kj <= row_pos && kj >= row_lo) ? s[i] * scale_log2 : QF_NEG_BIG;
-                mx = fmaxf(mx, s[i]);
-            }
-            const float m_new = fmaxf(m_run, mx);
-            corr = fast_exp2(m_run - m_new);
-            m_run = m_new;
-#pragma unroll
-            for (int i = 0; i < QF_PAGE; ++i) {
-                // a masked score is QF_NEG_BIG: its weight is 0 even while the running maximum is QF_NEG_BIG too
-                s[i] = s[i] > 0.5f * QF_NEG_BIG ? fast_exp2(s[i] - m_new) : 0.f;
-                sum += s[i];
+                    for (int kk = 0; kk < QF_PAGE / 16; ++kk)
+                        umma_bf16(tmem + PV_COL, desc_p + (uint64_t)(2 * kk), dv + (uint64_t)(kk * (2048 >> 4)), idesc_pv,
+                                  (j > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&bar_pv);
+                }
+                __syncwarp();
+                if (j + 2 < n_tiles && !timed_out) {
+                    // keys and values of page j have been read when its PV is done: their stage takes the page after next
+                    if (!wait_all(&bar_pv, j & 1)) timed_out = true;
+                    else fetch_page(j + 2);
+                }
             }
         }
-        l_run = l_run * corr + sum;
-        // the row of weights, bf16, 16-byte chunk c at chunk position c ^ (row % 8) of the row's 128 bytes
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const uint4 chunk = make_uint4(pack_bf16(s[8 * c], s[8 * c + 1]), pack_bf16(s[8 * c + 2], s[8 * c + 3]),
-                                           pack_bf16(s[8 * c + 4], s[8 * c + 5]), pack_bf16(s[8 * c + 6], s[8 * c + 7]));
-            *reinterpret_cast<uint4*>(p_s + t * 128 + ((c ^ (t & 7)) << 4)) = chunk;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read what the threads wrote
-        tc_fence_before();
-        __syncthreads();  // every row of S has been read, every row of the weights written
-        if (abort_s) break;
-        if (t == 0) {
+    } else {
+        // ---- the row threads
+        const int row_pos = pos0 + t, row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        float m_ref = QF_NEG_BIG, l_run = 0.f;  // the reference maximum of the exponentials, and their sum
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!wait_all(&bar_s, j & 1)) {
+                timed_out = true;
+                break;
+            }
             tc_fence_after();
-            issue_pv(j);
-            if (j + 1 < n_tiles && !issue_s(j + 1)) abort_s = 1;
+            float s[QF_PAGE];
+            {
+                uint32_t raw[32];
+                tmem_load_32(lane_base, raw);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(raw[i]);
+                tmem_load_32(lane_base + 32, raw);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(raw[i]);
+            }
+            const int key0 = (p_begin + j) * QF_PAGE;
+            // a page that every row of the block sees whole needs no mask
+            const bool full = key0 + QF_PAGE - 1 <= pos0 && key0 >= (window > 0 ? max(0, pos0 + TA_BM - 1 - window + 1) : 0);
+            float mx[4];  // four chains instead of one: the comparisons do not wait for each other
+            if (full) {  // the scores stay unscaled; the scale is folded into the exponent below
+#pragma unroll
+                for (int i = 0; i < QF_PAGE; ++i) mx[i & 3] = i < 4 ? s[i] : fmaxf(mx[i & 3], s[i]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx[i] *= scale_log2;
+            } else {
+#pragma unroll
+                for (int i = 0; i < QF_PAGE; ++i) {
+                    const int kj = key0 + i;
+                    s[i] = (kj <= row_pos && kj >= row_lo) ? s[i] * scale_log2 : QF_NEG_BIG;
+                    mx[i & 3] = i < 4 ? s[i] : fmaxf(mx[i & 3], s[i]);
+                }
+            }
+            const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+            // the products of the page before read the weights' buffer and add to O: both must be done before this
+            // thread writes either
+            if (j > 0 && !wait_all(&bar_pv, (j - 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            if (j == 0) {
+                m_ref = m_true;  // nothing to rescale yet: the first products overwrite O
+            } else {
+                const bool moved = m_true - m_ref > 8.0f;
+                if (__any_sync(0xffffffffu, moved)) {  // the warp's 32 rows of O are loaded and stored together
+                    tc_fence_after();
+                    const float f = moved ? fast_exp2(m_ref - m_true) : 1.0f;
+                    if (moved) {
+                        m_ref = m_true;
+                        l_run *= f;
+                    }
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t raw[32];
+                        tmem_load_32(lane_base + PV_COL + c0, raw);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * f);
+                        tmem_store_32(lane_base + PV_COL + c0, raw);
+                    }
+                    tmem_store_wait();
+                }
+            }
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < QF_PAGE; ++i) {
+                    s[i] = fast_exp2(fmaf(s[i], scale_log2, -m_ref));
+                    part[i & 3] += s[i];
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < QF_PAGE; ++i) {
+                    // a masked score is QF_NEG_BIG: its weight is 0 even while the reference is QF_NEG_BIG too
+                    s[i] = s[i] > 0.5f * QF_NEG_BIG ? fast_exp2(s[i] - m_ref) : 0.f;
+                    part[i & 3] += s[i];
+                }
+            }
+            l_run += (part[0] + part[1]) + (part[2] + part[3]);
+            // the row of weights, bf16, 16-byte chunk c at chunk position c ^ (row % 8) of the row's 128 bytes
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 chunk = make_uint4(pack_bf16(s[8 * c], s[8 * c + 1]), pack_bf16(s[8 * c + 2], s[8 * c + 3]),
+                                               pack_bf16(s[8 * c + 4], s[8 * c + 5]), pack_bf16(s[8 * c + 6], s[8 * c + 7]));
+                *reinterpret_cast<uint4*>(p_s + t * 128 + ((c ^ (t & 7)) << 4)) = chunk;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor cores read what this thread wrote
+            tc_fence_before();
+            mbar_arrive(&bar_p);
         }
-        if (!mbar_wait(&bar_pv, j & 1)) abort_s = 1;
+        if (!timed_out && !wait_all(&bar_pv, (n_tiles - 1) & 1)) timed_out = true;
         tc_fence_after();
-        // keys and values of page j have been read: their stage takes the page after next
-        if (t == 0 && j + 2 < n_tiles) fetch_page(j + 2);
+        if (!timed_out) {  // the loads are collective: every lane of the warp takes part, rows beyond the span store nothing
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t raw[32];
-            tmem_load_32(lane_base + PV_COL + c0, raw);
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t raw[32];
+                tmem_load_32(lane_base + PV_COL + c0, raw);
+                if (t < n_rows) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(raw[i]));
+                    for (int c = 0; c < 32; c += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(raw[c + i]) * inv;
+                        *reinterpret_cast<uint4*>(out_row + c0 + c) =
+                            make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                    }
+                }
+            }
         }
     }
-    if (abort_s && t == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
-    if (t < n_rows && !abort_s) {
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-#pragma unroll
-        for (int c = 0; c < D; c += 8)
-            *reinterpret_cast<uint4*>(out_row + c) =
-                make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
-                           pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
-    }
+    if (timed_out) atomicOr(err, QF_ERR_COPY_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0)
+    if (warp == 4)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
 }
 

@@ -25,6 +25,15 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool
            ((uint32_t)(m >> 4) << 24);
 }
 
+// One lane of the (converged) warp is chosen. The warp that issues copies and products runs its loop with all lanes,
+// so that addresses, descriptors and loop counters stay warp-uniform values, and only the instructions themselves
+// are given to the chosen lane.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(chosen));
+    return chosen != 0;
+}
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
@@ -50,6 +59,19 @@ __device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&r)[32]) {
         : "r"(addr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// 32 consecutive columns of this thread's lane from registers into tensor memory (complete after tmem_store_wait).
+__device__ __forceinline__ void tmem_store_32(uint32_t addr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(addr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -24,6 +24,10 @@ from .registry import build_part, register_part
 SM_COUNT = 148  # streaming multiprocessors of a B200
 
 
+# Fewest new tokens of a step, by head size, from which the tcgen05 prefill attention runs instead of the mma.sync one.
+TC_PREFILL_MIN_TOKENS = {64: 4096, 128: 256}
+
+
 class GqaAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, out_bias, scale, window, position (PartSpec | None).
     tensors: q_weight, k_weight, v_weight, o_weight (+ q_bias, k_bias, v_bias, o_bias when enabled)."""
@@ -74,6 +78,8 @@ class GqaAttention(Mixer):
             libs.add("gemm_f32")
         elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
             libs |= {"attention_decode", "attention_prefill", "skinny_gemm"}
+            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
+                libs.add("attention_prefill_tc")
         return libs
 
     def cache_need(self):
@@ -109,8 +115,13 @@ class GqaAttention(Mixer):
             ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
                                  self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
         elif fast:
-            ops.attention_prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                                  ctx.max_q_len, self.scale, self.window, ctx.err)
+            # the tcgen05 kernel works on blocks of 128 query rows, a long chain of pages per block: it pays for steps
+            # with many rows (measured: head size 128 from a few hundred tokens, head size 64 from a few thousand)
+            least = TC_PREFILL_MIN_TOKENS.get(self.head_dim)
+            prefill = (ops.attention_prefill_tc if least is not None and n >= least and ctx.max_q_len >= 128
+                       else ops.attention_prefill)
+            prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                    ctx.max_q_len, self.scale, self.window, ctx.err)
         else:
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
                                   ctx.max_q_len, self.scale, self.window, ctx.err)

@@ -341,3 +341,29 @@ def test_own_tensor_core_products_in_the_model(folders):
     finally:
         ops.use_own_tensor_core_products(False)
     assert_logits_close(logits, ref, torch.bfloat16, "own tcgen05 products")
+
+
+@pytest.mark.parametrize("name", ["small_64", "small_128"])
+def test_tcgen05_prefill_attention_in_the_model(folders, name, monkeypatch):
+    """With the tcgen05 prefill attention chosen for every step of 128 rows or more: a batch of unequal prompts, then a
+    continuation over the cache it left, give the plain implementation's logits."""
+    from qwenforge_b200.parts import attention
+    monkeypatch.setattr(attention, "TC_PREFILL_MIN_TOKENS", {64: 1, 128: 1})
+    model = get_model(folders, name, torch.bfloat16)
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    limit = ALL_CONFIGS[name]["max_position_embeddings"]
+    long_n = min(200, limit - 140)
+    a, b = random_tokens(vocab, long_n, 910), random_tokens(vocab, 130, 911)
+    more = random_tokens(vocab, 135, 912)
+    cache = model.new_cache(1024, 4)
+    sa, sb = cache.open(), cache.open()
+    logits = model.step(cache, [(sa, a), (sb, b)], want=[list(range(long_n)), list(range(130))])
+    model.raise_on_kernel_error()
+    assert_logits_close(logits[:long_n], plain_logits(folders, name, a), torch.bfloat16, f"{name} tcgen05 prefill a")
+    assert_logits_close(logits[long_n:], plain_logits(folders, name, b), torch.bfloat16, f"{name} tcgen05 prefill b")
+    cache.close(sb)
+    logits = model.step(cache, [(sa, more)], want=[list(range(135))])
+    model.raise_on_kernel_error()
+    whole = plain_logits(folders, name, a + more)
+    assert_logits_close(logits, whole[long_n:], torch.bfloat16, f"{name} tcgen05 continuation")
+    cache.close(sa)
