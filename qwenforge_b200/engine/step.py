@@ -11,6 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -46,9 +47,8 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
     """entries: (slot, start_position, token ids) per batch entry; want: per entry, the places among its
     tokens whose logits are wanted (None: the last token of every entry with a real slot)."""
     n = len(entries)
-    ids: list[int] = []
-    tok_seq: list[int] = []
-    tok_pos: list[int] = []
+    # the step's integers, piece by piece, for ONE host-to-device copy: ids | tok_seq | tok_pos | slots | cu_q | rows
+    id_parts, seq_parts, pos_parts = [], [], []
     slots: list[int] = []
     cu_q = [0]
     rows: list[int] = []
@@ -57,9 +57,9 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
         if q == 0:
             raise ValueError(f"step: entry {s} brings no tokens")
         base = cu_q[-1]
-        ids.extend(tokens)
-        tok_seq.extend([s] * q)
-        tok_pos.extend(range(start, start + q))
+        id_parts.append(np.asarray(tokens, dtype=np.int32))
+        seq_parts.append(np.full(q, s, dtype=np.int32))
+        pos_parts.append(np.arange(start, start + q, dtype=np.int32))
         slots.append(slot)
         cu_q.append(base + q)
         if want is None:
@@ -71,8 +71,9 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
                     raise ValueError(f"step: entry {s} wants place {place} of {q} tokens")
                 rows.append(base + place)
     total = cu_q[-1]
-    # one host-to-device copy; from pageable memory it is complete when the call returns, so the host lists may go
-    dev = torch.tensor(ids + tok_seq + tok_pos + slots + cu_q + rows, dtype=torch.int32).to(device)
+    packed = np.concatenate(id_parts + seq_parts + pos_parts + [np.asarray(slots + cu_q + rows, dtype=np.int32)])
+    # from pageable memory the copy is complete when the call returns, so the host array may go
+    dev = torch.from_numpy(packed).to(device)
     o = 0
 
     def take(count):
