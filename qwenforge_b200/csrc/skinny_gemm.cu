@@ -86,6 +86,98 @@ static inline int pad_to_16_mod_128(int bytes) { return bytes + ((16 - bytes % 1
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 
+// What a lane's epilogue reads from global memory, fetched before the products: bias and rotation frequency of its
+// two weight rows (constants), and for RESIDUAL the values it will add to.
+template <int NT> struct EpiloguePre {
+    float bias_a = 0.f, bias_b = 0.f, freq = 0.f;
+    float res[NT][4];
+};
+
+template <int NT, int EPI>
+__device__ __forceinline__ void skinny_epilogue_prefetch(const SkinnyArgs& a, int tile, int g, int t, EpiloguePre<NT>& pre) {
+    int ra, rb;
+    tile_rows<EPI>(a, tile, g, ra, rb);
+    if (a.bias && ra >= 0) pre.bias_a = __bfloat162float(a.bias[ra]);
+    if (a.bias && rb >= 0) pre.bias_b = __bfloat162float(a.bias[rb]);
+    if (EPI == EPI_QKV && a.inv_freq && ra >= 0) pre.freq = a.inv_freq[ra % a.head_dim];
+    if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int m = 8 * nt + 2 * t + e;
+                pre.res[nt][e] = (m < a.m && ra >= 0) ? a.residual[(size_t)m * a.n + ra] : 0.f;
+                pre.res[nt][2 + e] = (m < a.m && rb >= 0) ? a.residual[(size_t)m * a.n + rb] : 0.f;
+            }
+    }
+}
+
+// The epilogue of one 16-row tile, run by the 32 lanes that hold its sums. ss_s: sums of squares of the token rows
+// over this block's K (NORM), ss_part: the same of the cluster's other blocks; pos_s, dst_s: position and cache
+// offset of each token row (QKV).
+template <int NT, int EPI, bool NORM>
+__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, int tile, int g, int t, const float (&acc)[NT][4],
+                                                const EpiloguePre<NT>& pre, const float* ss_s, const float (*ss_part)[16],
+                                                int ksplit, const int* pos_s, const long long* dst_s) {
+    int ra, rb;
+    tile_rows<EPI>(a, tile, g, ra, rb);
+    const float bias_a = pre.bias_a, bias_b = pre.bias_b, freq = pre.freq;
+    // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int m = 8 * nt + 2 * t + e;
+            if (m >= a.m) continue;
+            float inv = 1.f;
+            if (NORM) {
+                float ss = ss_s[m];
+                for (int r = 1; r < ksplit; ++r) ss += ss_part[r - 1][m];
+                inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
+            }
+            const float va = acc[nt][e] * inv + bias_a, vb = acc[nt][2 + e] * inv + bias_b;
+            if (EPI == EPI_PLAIN) {
+                if (a.out_f32) {
+                    float* o = reinterpret_cast<float*>(a.out) + (size_t)m * a.ldo;
+                    if (ra >= 0) o[ra] = va;
+                    if (rb >= 0) o[rb] = vb;
+                } else {
+                    bf16* o = reinterpret_cast<bf16*>(a.out) + (size_t)m * a.ldo;
+                    if (ra >= 0) o[ra] = __float2bfloat16_rn(va);
+                    if (rb >= 0) o[rb] = __float2bfloat16_rn(vb);
+                }
+            } else if (EPI == EPI_RESIDUAL) {
+                float* h = a.residual + (size_t)m * a.n;
+                if (ra >= 0) h[ra] = pre.res[nt][e] + va;
+                if (rb >= 0) h[rb] = pre.res[nt][2 + e] + vb;
+            } else if (EPI == EPI_SWIGLU) {
+                if (ra >= 0)
+                    reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(va / (1.0f + expf(-va)) * vb);
+            } else if (ra >= 0) {  // EPI_QKV
+                const int D = a.head_dim, head = ra / D, j = ra % D;  // rb is component j + D/2 of the same head
+                float oa = va, ob = vb;
+                const int pos = pos_s[m];
+                if (head < a.n_heads + a.kv_heads && a.inv_freq) {
+                    // rotation pairs j with j + rot/2; the tile pairs j with j + D/2: the same when rot_dim == head_dim
+                    float s, c;
+                    sincosf((float)pos * freq, &s, &c);
+                    oa = va * c - vb * s;
+                    ob = vb * c + va * s;
+                }
+                if (head < a.n_heads) {
+                    bf16* qo = a.q_out + (size_t)m * a.n_heads * D + (size_t)head * D;
+                    qo[j] = __float2bfloat16_rn(oa);
+                    qo[j + D / 2] = __float2bfloat16_rn(ob);
+                } else if (dst_s[m] >= 0) {  // keys are heads n_heads .., values follow them: [2][kv_heads] planes of a page
+                    bf16* dst = a.kv_base + dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D;
+                    dst[j] = __float2bfloat16_rn(oa);
+                    dst[j + D / 2] = __float2bfloat16_rn(ob);
+                }
+            }
+        }
+    }
+}
+
 // STREAM: the block works through several tile batches (plan.rounds > 1); without it the loop and the second
 // buffer compile away.
 template <int NT, int EPI, bool NORM, bool STREAM>
@@ -243,29 +335,9 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     for (int round = 0; round < rounds; ++round) {
     const unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
     const int block = block0 + round * plan.nblk;
-    // What the epilogue reads from global memory is asked for now, so that it ends in stores, not in round trips:
-    // bias and rotation frequency (constants), and for RESIDUAL the values this lane will add to
-    float bias_a = 0.f, bias_b = 0.f, freq = 0.f;
-    if (tile_leader && rank == 0) {
-        int ra, rb;
-        tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
-        if (a.bias && ra >= 0) bias_a = __bfloat162float(a.bias[ra]);
-        if (a.bias && rb >= 0) bias_b = __bfloat162float(a.bias[rb]);
-        if (EPI == EPI_QKV && a.inv_freq && ra >= 0) freq = a.inv_freq[ra % a.head_dim];
-    }
-    float res[NT][4];
-    if (EPI == EPI_RESIDUAL && tile_leader && rank == 0) {
-        int ra, rb;
-        tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int m = 8 * nt + 2 * t + e;
-                res[nt][e] = (m < a.m && ra >= 0) ? a.residual[(size_t)m * a.n + ra] : 0.f;
-                res[nt][2 + e] = (m < a.m && rb >= 0) ? a.residual[(size_t)m * a.n + rb] : 0.f;
-            }
-    }
+    // What the epilogue reads from global memory is asked for now, so that it ends in stores, not in round trips
+    EpiloguePre<NT> pre;
+    if (tile_leader && rank == 0) skinny_epilogue_prefetch<NT, EPI>(a, block * tpb + tile_local, g, t, pre);
     if (!mbar_wait(&w_bar[round & 1], (round >> 1) & 1) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
 
     // ---- products: the warps of a tile take its k-blocks in turn
@@ -326,65 +398,214 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
         }
         if (rounds > 1) cluster.sync();  // the first block has read the partial sums before the next batch overwrites them
     }
-    if (tile_leader && rank == 0) {
-    int ra, rb;
-    tile_rows<EPI>(a, block * tpb + tile_local, g, ra, rb);
-    // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int m = 8 * nt + 2 * t + e;
-            if (m >= a.m) continue;
-            float inv = 1.f;
-            if (NORM) {
-                float ss = ss_s[m];
-                for (int r = 1; r < ksplit; ++r) ss += ss_part[r - 1][m];
-                inv = 1.0f / sqrtf(ss / (float)a.k + a.eps);
-            }
-            const float va = acc[nt][e] * inv + bias_a, vb = acc[nt][2 + e] * inv + bias_b;
-            if (EPI == EPI_PLAIN) {
-                if (a.out_f32) {
-                    float* o = reinterpret_cast<float*>(a.out) + (size_t)m * a.ldo;
-                    if (ra >= 0) o[ra] = va;
-                    if (rb >= 0) o[rb] = vb;
-                } else {
-                    bf16* o = reinterpret_cast<bf16*>(a.out) + (size_t)m * a.ldo;
-                    if (ra >= 0) o[ra] = __float2bfloat16_rn(va);
-                    if (rb >= 0) o[rb] = __float2bfloat16_rn(vb);
-                }
-            } else if (EPI == EPI_RESIDUAL) {
-                float* h = a.residual + (size_t)m * a.n;
-                if (ra >= 0) h[ra] = res[nt][e] + va;
-                if (rb >= 0) h[rb] = res[nt][2 + e] + vb;
-            } else if (EPI == EPI_SWIGLU) {
-                if (ra >= 0)
-                    reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + ra] = __float2bfloat16_rn(va / (1.0f + expf(-va)) * vb);
-            } else if (ra >= 0) {  // EPI_QKV
-                const int D = a.head_dim, head = ra / D, j = ra % D;  // rb is component j + D/2 of the same head
-                float oa = va, ob = vb;
-                const int pos = pos_s[m];
-                if (head < a.n_heads + a.kv_heads && a.inv_freq) {
-                    // rotation pairs j with j + rot/2; the tile pairs j with j + D/2: the same when rot_dim == head_dim
-                    float s, c;
-                    sincosf((float)pos * freq, &s, &c);
-                    oa = va * c - vb * s;
-                    ob = vb * c + va * s;
-                }
-                if (head < a.n_heads) {
-                    bf16* qo = a.q_out + (size_t)m * a.n_heads * D + (size_t)head * D;
-                    qo[j] = __float2bfloat16_rn(oa);
-                    qo[j + D / 2] = __float2bfloat16_rn(ob);
-                } else if (dst_s[m] >= 0) {  // keys are heads n_heads .., values follow them: [2][kv_heads] planes of a page
-                    bf16* dst = a.kv_base + dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D;
-                    dst[j] = __float2bfloat16_rn(oa);
-                    dst[j + D / 2] = __float2bfloat16_rn(ob);
+    if (tile_leader && rank == 0)
+        skinny_epilogue<NT, EPI, NORM>(a, block * tpb + tile_local, g, t, acc, pre, ss_s, ss_part, ksplit, pos_s, dst_s);
+    }  // tile batches
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same products for weights that are too many for one wave of blocks (wide layers, the vocabulary): one block
+// per SM walks its share of the 16-row tiles, and a tile's K comes in chunks of 512 columns through a ring of
+// shared-memory stages. A ninth warp does nothing but fetch: it keeps the ring full across chunk and tile
+// boundaries (bulk asynchronous copies, a 'full' barrier per stage counting bytes), so the memory pipe does not
+// wait for the products; the eight product warps take the k-blocks of a chunk in turn, hand the stage back through
+// its 'empty' barrier (one arrival per warp) and meet only at the end of a tile, to add up their sums and run the
+// epilogue. There is no split of K over blocks and no cluster. The token rows stay in shared memory for the whole
+// kernel, normalised as in the kernel above; when they are too long for that (a feed-forward's second product),
+// their chunks travel through the ring beside the weights' (XS; rows that need the norm cannot).
+// Requirements beyond the kernel above: K a multiple of 32.
+struct StreamPlan {
+    int stages;    // ring depth
+    int n_chunks;  // chunks of SK_CHUNK columns per tile
+    int stride_x;  // bytes between token rows in shared memory when they are resident
+    int nblk;      // blocks launched; block b takes tiles b, b + nblk, ...
+};
+#define SK_CHUNK 512
+#define SK_STAGE_STRIDE (SK_CHUNK * 2 + 16)  // bytes between rows of a stage (16 modulo 128: conflict-free ldmatrix)
+#define SK_STREAM_THREADS (SK_THREADS + 32)
+
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(SK_THREADS) : "memory"); }
+
+template <int NT, int EPI, bool NORM, bool XS>
+__global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(const SkinnyArgs a, const StreamPlan plan, int tiles) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int MP = 8 * NT;
+    constexpr int STAGE_ROWS = 16 + (XS ? MP : 0);
+    constexpr int STAGE_BYTES = STAGE_ROWS * SK_STAGE_STRIDE;
+    constexpr int MAX_STAGES = 16;
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES];
+    __shared__ float ss_s[16];
+    __shared__ int pos_s[16];
+    __shared__ long long dst_s[16];
+    const int stages = plan.stages, n_chunks = plan.n_chunks;
+    unsigned char* ring = smem_raw;                                      // [stages][STAGE_ROWS][SK_STAGE_STRIDE]
+    unsigned char* x_s = ring + (size_t)stages * STAGE_BYTES;            // [MP][stride_x] (not XS)
+    float* red = reinterpret_cast<float*>(x_s + (XS ? 0 : (size_t)MP * plan.stride_x));  // [SK_WARPS][NT * 4][32]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int n_kb = a.k / 32;
+
+    if (threadIdx.x == 0)
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], SK_WARPS);
+        }
+    if (EPI == EPI_QKV && threadIdx.x >= SK_THREADS - 16 && threadIdx.x < SK_THREADS) {
+        // where each token row goes (see the kernel above: complete before any kernel of this chain starts)
+        const int m = threadIdx.x - (SK_THREADS - 16);
+        int pos = 0;
+        long long dst = -1;
+        if (m < a.m) {
+            pos = a.tok_pos[m];
+            if (a.write_cache) {
+                const int slot = a.slots[a.tok_seq[m]];
+                if (slot >= 0) {
+                    const int page = a.table[(long long)slot * a.table_stride + pos / QF_PAGE];
+                    if (page < 0) atomicOr(a.err, QF_ERR_NO_PAGE);
+                    else dst = (long long)page * a.page_elems + (long long)(pos % QF_PAGE) * a.head_dim;
                 }
             }
         }
+        pos_s[m] = pos;
+        dst_s[m] = dst;
     }
-    }  // the lanes that own outputs
-    }  // tile batches
+    __syncthreads();  // barriers and row metadata are set; the only block-wide barrier of the kernel
+    grid_launch_dependents();
+
+    if (warp == SK_WARPS) {
+        // ---- the fetching warp: lanes 0..15 copy the 16 weight rows of a stage, lanes 16.. the token rows (XS)
+        if (XS) grid_dependency_wait();  // the token rows are the previous kernel's output; the weights are nobody's
+        int idx = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += plan.nblk) {
+            int ra, rb;
+            tile_rows<EPI>(a, tile, lane & 7, ra, rb);
+            const int grow = lane < 16 ? (lane < 8 ? ra : rb) : -1;
+            const int xrow = (XS && lane >= 16 && lane - 16 < a.m) ? lane - 16 : -1;
+            const unsigned rows_mask = __ballot_sync(0xffffffffu, grow >= 0 || xrow >= 0);
+            for (int c = 0; c < n_chunks; ++c, ++idx) {
+                const int s = idx % stages;
+                if (idx >= stages && !mbar_wait(&empty_bar[s], ((idx / stages) - 1) & 1)) {
+                    if (lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
+                    return;
+                }
+                const uint32_t bytes = (uint32_t)min(SK_CHUNK, a.k - c * SK_CHUNK) * 2;
+                unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
+                if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * __popc(rows_mask));
+                __syncwarp();
+                if (grow >= 0)
+                    bulk_copy_g2s(stage + (size_t)lane * SK_STAGE_STRIDE, a.w + (size_t)grow * a.ldw + (size_t)c * SK_CHUNK, bytes, &full_bar[s]);
+                if (xrow >= 0)
+                    bulk_copy_g2s(stage + (size_t)(16 + xrow) * SK_STAGE_STRIDE, a.x + (size_t)xrow * a.ldx + (size_t)c * SK_CHUNK, bytes,
+                                  &full_bar[s]);
+            }
+        }
+        return;
+    }
+
+    // ---- the eight product warps
+    grid_dependency_wait();
+    if (!XS) {
+        const int kpad = n_chunks * SK_CHUNK;  // the rows are padded with zeros to whole chunks
+        if (NORM) {
+            // as in the kernel above: the rows enter scaled by the norm weights, 1 / rms multiplies the sums at the end
+            for (int m = warp; m < MP; m += SK_WARPS) {
+                bf16* dst = reinterpret_cast<bf16*>(x_s + (size_t)m * plan.stride_x);
+                float ss = 0.f;
+                if (m < a.m) {
+                    const float* h = a.hidden + (size_t)m * a.k;
+                    for (int base = 0; base < kpad; base += 32 * 4 * 8) {
+                        float4 x[8];
+                        uint2 wv[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int c = base + (u * 32 + lane) * 4;
+                            const bool in = c < a.k;
+                            x[u] = in ? *reinterpret_cast<const float4*>(h + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            wv[u] = in ? *reinterpret_cast<const uint2*>(a.norm_w + c) : make_uint2(0u, 0u);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int c = base + (u * 32 + lane) * 4;
+                            if (c >= kpad) continue;
+                            ss += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
+                            const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wv[u].x);
+                            const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wv[u].y);
+                            uint2 o;
+                            o.x = pack_bf16(x[u].x * __low2float(w01), x[u].y * __high2float(w01));
+                            o.y = pack_bf16(x[u].z * __low2float(w23), x[u].w * __high2float(w23));
+                            *reinterpret_cast<uint2*>(dst + c) = o;
+                        }
+                    }
+                } else {
+                    for (int c = lane * 8; c < kpad; c += 32 * 8) *reinterpret_cast<uint4*>(dst + c) = make_uint4(0, 0, 0, 0);
+                }
+                ss = warp_sum(ss);
+                if (lane == 0) ss_s[m] = ss;
+            }
+        } else {
+            const int chunks = kpad / 8;
+            for (int i = threadIdx.x; i < MP * chunks; i += SK_THREADS) {
+                const int m = i / chunks, c = (i % chunks) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (m < a.m && c < a.k) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + c);
+                *reinterpret_cast<uint4*>(x_s + (size_t)m * plan.stride_x + c * 2) = v;
+            }
+        }
+        consumer_barrier();  // the token rows are staged
+    }
+    int idx = 0;
+    bool dead = false;  // a wait ran out: reported; the warp goes on without waiting, so that every barrier is still met
+    for (int tile = blockIdx.x; tile < tiles; tile += plan.nblk) {
+        EpiloguePre<NT> pre;
+        if (warp == 0) skinny_epilogue_prefetch<NT, EPI>(a, tile, g, t, pre);
+        float acc[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        for (int c = 0; c < n_chunks; ++c, ++idx) {
+            const int s = idx % stages;
+            if (!dead && !mbar_wait(&full_bar[s], (idx / stages) & 1)) {
+                if (lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
+                dead = true;
+            }
+            const unsigned char* stage = ring + (size_t)s * STAGE_BYTES;
+            const unsigned char* a_addr = stage + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * SK_STAGE_STRIDE + (lane >> 4) * 16;
+            const unsigned char* x_base = XS ? stage + (size_t)16 * SK_STAGE_STRIDE : x_s + (size_t)c * SK_CHUNK * 2;
+            const int x_stride = XS ? SK_STAGE_STRIDE : plan.stride_x;
+            const int kbs = min(SK_CHUNK / 32, n_kb - c * (SK_CHUNK / 32));
+            for (int kb = warp; kb < kbs; kb += SK_WARPS) {
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, a_addr + (kb * 32 + ks * 16) * 2);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const unsigned char* xr = x_base + (size_t)(8 * nt + g) * x_stride + (kb * 32 + ks * 16 + 2 * t) * 2;
+                        mma_bf16_16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(xr), *reinterpret_cast<const uint32_t*>(xr + 16));
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);  // this warp is done with the stage
+        }
+        // ---- the tile's sums: the warps' parts are added in warp order, then the first warp runs the epilogue
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) red[((size_t)warp * NT * 4 + nt * 4 + e) * 32 + lane] = acc[nt][e];
+        consumer_barrier();
+        if (warp == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int w = 0; w < SK_WARPS; ++w) sum += red[((size_t)w * NT * 4 + nt * 4 + e) * 32 + lane];
+                    acc[nt][e] = sum;
+                }
+        }
+        consumer_barrier();  // the parts have been read: the next tile may overwrite them
+        if (warp == 0) skinny_epilogue<NT, EPI, NORM>(a, tile, g, t, acc, pre, ss_s, nullptr, 1, pos_s, dst_s);
+    }
 }
 
 static size_t plan_smem(const SkinnyPlan& p, int nt) {
@@ -446,7 +667,43 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
     return false;
 }
 
+template <int NT, int EPI, bool NORM, bool XS>
+static int launch_stream_variant(const SkinnyArgs& a, int tiles, const StreamPlan& sp, size_t smem, cudaStream_t stream) {
+    auto kernel = skinny_stream_kernel<NT, EPI, NORM, XS>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_pdl(kernel, dim3(sp.nblk), dim3(SK_STREAM_THREADS), smem, stream, a, sp, tiles);
+}
+
+// The streaming kernel for products of more tiles than one wave of blocks holds; false if it does not take the shape.
+template <int NT, int EPI, bool NORM> static bool launch_stream(const SkinnyArgs& a, int tiles, cudaStream_t stream, int& code) {
+    const int sms = 148;
+    const size_t most = 224 * 1024;
+    if (a.k % 32 || tiles <= sms) return false;
+    StreamPlan sp;
+    sp.n_chunks = (a.k + SK_CHUNK - 1) / SK_CHUNK;
+    sp.stride_x = pad_to_16_mod_128(sp.n_chunks * SK_CHUNK * 2);
+    sp.nblk = tiles < sms ? tiles : sms;
+    const size_t red = (size_t)SK_WARPS * NT * 4 * 32 * 4, x_bytes = (size_t)8 * NT * sp.stride_x;
+    // the token rows stay in shared memory while that leaves the ring eight stages; rows that need no norm may travel
+    // through the ring instead
+    const size_t stage = (size_t)16 * SK_STAGE_STRIDE, stage_xs = (size_t)(16 + 8 * NT) * SK_STAGE_STRIDE;
+    const bool resident = red + x_bytes + 8 * stage <= most;
+    if (!resident && NORM) return false;
+    const size_t per_stage = resident ? stage : stage_xs, fixed = red + (resident ? x_bytes : 0);
+    size_t stages = (most - fixed) / per_stage;
+    if (stages > 16) stages = 16;
+    if (stages < 4) return false;
+    sp.stages = (int)stages;
+    const size_t smem = fixed + stages * per_stage;
+    if (resident) code = launch_stream_variant<NT, EPI, NORM, false>(a, tiles, sp, smem, stream);
+    else code = launch_stream_variant<NT, EPI, false, true>(a, tiles, sp, smem, stream);
+    return true;
+}
+
 template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
+    int code = 0;
+    if (launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
     SkinnyPlan p;
     if (!make_plan(a, tiles, NT, p)) return (int)cudaErrorInvalidValue;
     const size_t smem = plan_smem(p, NT);
