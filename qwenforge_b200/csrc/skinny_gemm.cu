@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
 
 // ------------------------------------------------------------------------------------------------------------------
 // The same products for weights that are too many for one wave of blocks (wide layers, the vocabulary): one block
-// per SM walks its share of the 16-row tiles, and a tile's K comes in chunks of 512 columns through a ring of
+// per SM walks its share of the 16-row tiles, and a tile's K comes in chunks of 1,024 columns through a ring of
 // shared-memory stages. A ninth warp does nothing but fetch: it keeps the ring full across chunk and tile
 // boundaries (bulk asynchronous copies, a 'full' barrier per stage counting bytes), so the memory pipe does not
 // wait for the products; the eight product warps take the k-blocks of a chunk in turn, hand the stage back through
@@ -420,7 +420,7 @@ struct StreamPlan {
     int stride_x;  // bytes between token rows in shared memory when they are resident
     int nblk;      // blocks launched; block b takes tiles b, b + nblk, ...
 };
-#define SK_CHUNK 512
+#define SK_CHUNK 1024  // columns of a chunk: one bulk copy per row and chunk (2 KB); smaller copies are bound by their issue
 #define SK_STAGE_STRIDE (SK_CHUNK * 2 + 16)  // bytes between rows of a stage (16 modulo 128: conflict-free ldmatrix)
 #define SK_STREAM_THREADS (SK_THREADS + 32)
 
@@ -504,7 +504,7 @@ __global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(con
     // ---- the eight product warps
     grid_dependency_wait();
     if (!XS) {
-        const int kpad = n_chunks * SK_CHUNK;  // the rows are padded with zeros to whole chunks
+        const int kpad = a.k;  // a multiple of 32: whole k-blocks, no padding needed
         if (NORM) {
             // as in the kernel above: the rows enter scaled by the norm weights, 1 / rms multiplies the sums at the end
             for (int m = warp; m < MP; m += SK_WARPS) {
@@ -679,21 +679,21 @@ static int launch_stream_variant(const SkinnyArgs& a, int tiles, const StreamPla
 template <int NT, int EPI, bool NORM> static bool launch_stream(const SkinnyArgs& a, int tiles, cudaStream_t stream, int& code) {
     const int sms = 148;
     const size_t most = 224 * 1024;
-    if (a.k % 32 || tiles <= sms) return false;
+    if (a.k % 32) return false;
     StreamPlan sp;
     sp.n_chunks = (a.k + SK_CHUNK - 1) / SK_CHUNK;
-    sp.stride_x = pad_to_16_mod_128(sp.n_chunks * SK_CHUNK * 2);
+    sp.stride_x = pad_to_16_mod_128(a.k * 2);
     sp.nblk = tiles < sms ? tiles : sms;
     const size_t red = (size_t)SK_WARPS * NT * 4 * 32 * 4, x_bytes = (size_t)8 * NT * sp.stride_x;
-    // the token rows stay in shared memory while that leaves the ring eight stages; rows that need no norm may travel
-    // through the ring instead
+    // the token rows stay in shared memory while that leaves the ring four stages (three when they need the norm and
+    // so cannot travel); rows that need no norm may travel through the ring instead
     const size_t stage = (size_t)16 * SK_STAGE_STRIDE, stage_xs = (size_t)(16 + 8 * NT) * SK_STAGE_STRIDE;
-    const bool resident = red + x_bytes + 8 * stage <= most;
+    const bool resident = red + x_bytes + (NORM ? 3 : 4) * stage <= most;
     if (!resident && NORM) return false;
     const size_t per_stage = resident ? stage : stage_xs, fixed = red + (resident ? x_bytes : 0);
     size_t stages = (most - fixed) / per_stage;
     if (stages > 16) stages = 16;
-    if (stages < 4) return false;
+    if (stages < 3) return false;
     sp.stages = (int)stages;
     const size_t smem = fixed + stages * per_stage;
     if (resident) code = launch_stream_variant<NT, EPI, NORM, false>(a, tiles, sp, smem, stream);
@@ -702,10 +702,14 @@ template <int NT, int EPI, bool NORM> static bool launch_stream(const SkinnyArgs
 }
 
 template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
-    int code = 0;
-    if (launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
     SkinnyPlan p;
-    if (!make_plan(a, tiles, NT, p)) return (int)cudaErrorInvalidValue;
+    const bool planned = make_plan(a, tiles, NT, p);
+    // The streaming kernel takes what does not fit one wave of blocks; and products of at least half as many tiles as
+    // SMs whose tiles weigh 128 KB or more, where one block per tile streaming its whole K beats a cluster sharing it.
+    const bool heavy_tiles = tiles <= 148 && 2 * tiles > 148 && (size_t)16 * a.k * 2 >= 128 * 1024;
+    int code = 0;
+    if ((!planned || p.rounds > 1 || heavy_tiles) && launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
+    if (!planned) return (int)cudaErrorInvalidValue;
     const size_t smem = plan_smem(p, NT);
     auto kernel = p.rounds > 1 ? skinny_gemm_kernel<NT, EPI, NORM, true> : skinny_gemm_kernel<NT, EPI, NORM, false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
