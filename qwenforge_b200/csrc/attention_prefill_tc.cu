@@ -45,7 +45,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     unsigned char* k_s = q_s + CB * Q_BLOCK;            // [2][CB][64][64]
     unsigned char* v_s = k_s + 2 * KV_BYTES;            // [2][CB][64][64]
     unsigned char* p_s = v_s + 2 * KV_BYTES;            // [128][64]
-    __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_pv, bar_p;
+    __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_sfree, bar_pv, bar_p;
     __shared__ uint32_t tmem_base_s;
 
     const int seq = blockIdx.z, head = blockIdx.y;
@@ -76,6 +76,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         mbar_init(&bar_s, 1);
         mbar_init(&bar_pv, 1);
         mbar_init(&bar_p, TA_ROW_THREADS);
+        mbar_init(&bar_sfree, TA_ROW_THREADS);
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(TMEM_COLS));
@@ -143,17 +144,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             if (n_tiles > 1) fetch_page(1);
             timed_out = !wait_all(&bar_q, 0) || !issue_s(0);
             for (int j = 0; j < n_tiles && !timed_out; ++j) {
-                if (!wait_all(&bar_p, j & 1)) {  // every row has read S and written its weights
+                // as soon as every row holds its S in registers, S of the next page is multiplied under their softmax
+                if (!wait_all(&bar_sfree, j & 1)) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                if (j + 1 < n_tiles && !issue_s(j + 1)) {
+                    timed_out = true;
+                    break;
+                }
+                if (!wait_all(&bar_p, j & 1)) {  // every row has written its weights
                     timed_out = true;
                     break;
                 }
                 tc_fence_after();
                 // PV of page j: weights [128][64 keys] K-major; values [64 keys][D] as they lie, 16 keys are two groups
                 // of 8 rows (2048 bytes)
-                if (j + 1 < n_tiles && !issue_s(j + 1)) {  // S is free: every row has read it
-                    timed_out = true;
-                    break;
-                }
                 const uint64_t dv = desc_v + (uint64_t)((j & 1) * (KV_BYTES >> 4));
                 if (leader) {
 #pragma unroll
@@ -191,6 +198,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 #pragma unroll
                 for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(raw[i]);
             }
+            tc_fence_before();
+            mbar_arrive(&bar_sfree);  // S is in this thread's registers
             const int key0 = (p_begin + j) * QF_PAGE;
             // a page that every row of the block sees whole needs no mask
             const bool full = key0 + QF_PAGE - 1 <= pos0 && key0 >= (window > 0 ? max(0, pos0 + TA_BM - 1 - window + 1) : 0);
@@ -209,33 +218,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
             }
             const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
-            // the products of the page before read the weights' buffer and add to O: both must be done before this
-            // thread writes either
-            if (j > 0 && !wait_all(&bar_pv, (j - 1) & 1)) {
-                timed_out = true;
-                break;
-            }
+            // The reference maximum moves before the exponentials; O, which carries the old one, is rescaled after them,
+            // when the products of the page before are surely done.
+            float f_o = 1.0f;
+            bool moved = false;
             if (j == 0) {
                 m_ref = m_true;  // nothing to rescale yet: the first products overwrite O
-            } else {
-                const bool moved = m_true - m_ref > 8.0f;
-                if (__any_sync(0xffffffffu, moved)) {  // the warp's 32 rows of O are loaded and stored together
-                    tc_fence_after();
-                    const float f = moved ? fast_exp2(m_ref - m_true) : 1.0f;
-                    if (moved) {
-                        m_ref = m_true;
-                        l_run *= f;
-                    }
-#pragma unroll
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t raw[32];
-                        tmem_load_32(lane_base + PV_COL + c0, raw);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * f);
-                        tmem_store_32(lane_base + PV_COL + c0, raw);
-                    }
-                    tmem_store_wait();
-                }
+            } else if (m_true - m_ref > 8.0f) {
+                moved = true;
+                f_o = fast_exp2(m_ref - m_true);
+                m_ref = m_true;
+                l_run *= f_o;
             }
             float part[4] = {0.f, 0.f, 0.f, 0.f};
             if (full) {
@@ -253,6 +246,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
             }
             l_run += (part[0] + part[1]) + (part[2] + part[3]);
+            // the products of the page before read the weights' buffer and add to O: both must be done before this
+            // thread writes either
+            if (j > 0 && !wait_all(&bar_pv, (j - 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            if (__any_sync(0xffffffffu, moved)) {  // the warp's 32 rows of O are loaded and stored together
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t raw[32];
+                    tmem_load_32(lane_base + PV_COL + c0, raw);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * f_o);
+                    tmem_store_32(lane_base + PV_COL + c0, raw);
+                }
+                tmem_store_wait();
+            }
             // the row of weights, bf16, 16-byte chunk c at chunk position c ^ (row % 8) of the row's 128 bytes
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
