@@ -15,6 +15,8 @@
 // streams and all blocks are resident in one wave. Partial sums are added in a fixed order: first the warps of a
 // block, then the blocks of a cluster through distributed shared memory, so results do not change from run to run.
 // It is launched as a programmatic dependent: the weight copies start while the previous kernel still runs.
+// Products that do not fit one wave of blocks, or whose tiles are heavy, run in the second kernel of this file,
+// which streams K through a ring of stages (see there).
 // The 16 rows of a tile are chosen so that the two rows a lane holds (g and g + 8) are the pair its epilogue
 // needs: component j and j + D/2 of a head for the rotation, gate row i and up row i for SwiGLU.
 #include <cooperative_groups.h>
@@ -77,8 +79,7 @@ struct SkinnyPlan {
     int per;       // k-blocks (of 32) per slice
     int stride_w;  // bytes between weight rows in shared memory (16 modulo 128: conflict-free ldmatrix)
     int stride_x;  // bytes between token rows in shared memory (16 modulo 128: conflict-free fragment loads)
-    int rounds;    // tile batches a block works through, one after another, two weight buffers in turn (1: all at once)
-    int nblk;      // blocks (clusters) launched; in round r a block takes tile batch  its index + r * nblk
+    int nblk;      // blocks (clusters) launched
 };
 
 static inline int pad_to_16_mod_128(int bytes) { return bytes + ((16 - bytes % 128) + 128) % 128; }
@@ -178,28 +179,24 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, int tile, i
     }
 }
 
-// STREAM: the block works through several tile batches (plan.rounds > 1); without it the loop and the second
-// buffer compile away.
-template <int NT, int EPI, bool NORM, bool STREAM>
+template <int NT, int EPI, bool NORM>
 __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const SkinnyArgs a, const SkinnyPlan plan) {
     namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t w_bar[2];
+    __shared__ __align__(8) uint64_t w_bar[1];
     __shared__ float ss_s[16];       // NORM: sum of squares of each token row over this block's slice
     __shared__ float ss_part[7][16]; // NORM: the same of the other blocks of the cluster, written into the first block
     __shared__ int pos_s[16];        // QKV: position of each token row
     __shared__ long long dst_s[16];  // QKV: element offset of the row's (page, position) in the cache, -1: nothing to write
     constexpr int MP = 8 * NT;
-    const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per, rounds = STREAM ? plan.rounds : 1;
-    // weights [tpb * 16][stride_w], one buffer, or two when the block works through several tile batches
-    const size_t w_bytes = rounds > 1 ? (size_t)tpb * 16 * plan.stride_w
-                                      : max((size_t)tpb * 16 * plan.stride_w, (size_t)SK_WARPS * NT * 4 * 32 * 4);
+    const int tpb = plan.tpb, ksplit = plan.ksplit, per = plan.per;
+    // weights [tpb * 16][stride_w]; the partial sums of the warps, red [SK_WARPS][NT * 4][32] floats, take their place
+    // once the products are done
+    const size_t w_bytes = max((size_t)tpb * 16 * plan.stride_w, (size_t)SK_WARPS * NT * 4 * 32 * 4);
     unsigned char* w_base = smem_raw;
-    unsigned char* x_s = w_base + (rounds > 1 ? 2 : 1) * w_bytes;            // [MP][stride_x]
+    unsigned char* x_s = w_base + w_bytes;                                     // [MP][stride_x]
     float* part = reinterpret_cast<float*>(x_s + (size_t)MP * plan.stride_x);  // [ksplit - 1][tpb][NT * 4][32]
-    // partial sums of the warps, red [SK_WARPS][NT * 4][32] floats: a single tile batch lends them the weights'
-    // space once its products are done; with several batches the weights stay in use and red has its own space
-    float* red = rounds > 1 ? part + (size_t)(ksplit - 1) * tpb * NT * 4 * 32 : reinterpret_cast<float*>(w_base);
+    float* red = reinterpret_cast<float*>(w_base);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int rank = ksplit > 1 ? (int)(blockIdx.x % ksplit) : 0;
     const int block0 = blockIdx.x / ksplit;
@@ -212,15 +209,12 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     // the lanes of warp 0 and completing on the buffer's shared-memory barrier; the other warps zero what no copy fills
     const int slice_bytes = max(0, min(per * 64, (a.k - k_begin) * 2));  // valid bytes of a row slice (multiple of 16)
     if (warp == 0) {  // warp 0 alone touches the barriers until the block-wide barrier after the token rows are staged
-        if (lane == 0) {
-            mbar_init(&w_bar[0], 1);
-            mbar_init(&w_bar[1], 1);
-        }
+        if (lane == 0) mbar_init(&w_bar[0], 1);
         __syncwarp();
     }
-    auto fetch = [&](int round) {
-        unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
-        const int block = block0 + round * plan.nblk;
+    {
+        unsigned char* w_s = w_base;
+        const int block = block0;
         if (warp == 0) {
             uint32_t mine = 0;
             for (int row = lane; row < tpb * 16; row += 32) {
@@ -229,7 +223,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                 if (((row & 15) < 8 ? ra : rb) >= 0) mine += slice_bytes;
             }
             const uint32_t total = warp_sum_u32(mine);
-            if (lane == 0) mbar_expect_tx(&w_bar[round & 1], total);
+            if (lane == 0) mbar_expect_tx(&w_bar[0], total);
             __syncwarp();
             if (slice_bytes > 0)
                 for (int row = lane; row < tpb * 16; row += 32) {
@@ -238,7 +232,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                     const int grow = (row & 15) < 8 ? ra : rb;
                     if (grow >= 0)
                         bulk_copy_g2s(w_s + (size_t)row * plan.stride_w, a.w + (size_t)grow * a.ldw + k_begin, slice_bytes,
-                                      &w_bar[round & 1]);
+                                      &w_bar[0]);
                 }
         } else {
             // rows that do not exist, and the tail of a slice beyond K, must be zero: they meet zero token values
@@ -252,9 +246,7 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                     *reinterpret_cast<uint4*>(w_s + (size_t)row * plan.stride_w + (size_t)(first + c) * 16) = make_uint4(0, 0, 0, 0);
             }
         }
-    };
-    fetch(0);
-    if (rounds > 1) fetch(1);
+    }
     if (EPI == EPI_QKV && threadIdx.x >= SK_THREADS - 16) {
         // Where each token row goes: positions, slots and page tables are written by copies and by kernels that are not
         // launched as programmatic dependents, so they are complete before any kernel of this chain starts, and the
@@ -332,13 +324,12 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     __syncthreads();  // the token rows are staged
     const int wpt = SK_WARPS / tpb, tile_local = warp / wpt, sub = warp % wpt;
     const bool tile_leader = sub == 0;
-    for (int round = 0; round < rounds; ++round) {
-    const unsigned char* w_s = w_base + (size_t)(round & 1) * w_bytes;
-    const int block = block0 + round * plan.nblk;
+    const unsigned char* w_s = w_base;
+    const int block = block0;
     // What the epilogue reads from global memory is asked for now, so that it ends in stores, not in round trips
     EpiloguePre<NT> pre;
     if (tile_leader && rank == 0) skinny_epilogue_prefetch<NT, EPI>(a, block * tpb + tile_local, g, t, pre);
-    if (!mbar_wait(&w_bar[round & 1], (round >> 1) & 1) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
+    if (!mbar_wait(&w_bar[0], 0) && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
 
     // ---- products: the warps of a tile take its k-blocks in turn
     float acc[NT][4];
@@ -360,7 +351,6 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     }
     // ---- sum the warps of each tile in a fixed order, then the blocks of the cluster in rank order
     __syncthreads();  // every warp is done with this buffer's weights
-    if (round + 2 < rounds) fetch(round + 2);  // the batch after next goes into the buffer that has just been read
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -396,11 +386,9 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
                     for (int e = 0; e < 4; ++e) acc[nt][e] += p[(nt * 4 + e) * 32 + lane];
             }
         }
-        if (rounds > 1) cluster.sync();  // the first block has read the partial sums before the next batch overwrites them
     }
     if (tile_leader && rank == 0)
         skinny_epilogue<NT, EPI, NORM>(a, block * tpb + tile_local, g, t, acc, pre, ss_s, ss_part, ksplit, pos_s, dst_s);
-    }  // tile batches
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -611,23 +599,22 @@ __global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(con
 static size_t plan_smem(const SkinnyPlan& p, int nt) {
     size_t w = (size_t)p.tpb * 16 * p.stride_w;
     const size_t red = (size_t)SK_WARPS * nt * 4 * 32 * 4;
-    if (p.rounds == 1 && w < red) w = red;  // a single batch lends the partial sums the weights' space
-    return (p.rounds > 1 ? 2 * w + red : w) + (size_t)8 * nt * p.stride_x + (size_t)(p.ksplit - 1) * p.tpb * nt * 4 * 32 * 4;
+    if (w < red) w = red;  // the partial sums take the weights' place
+    return w + (size_t)8 * nt * p.stride_x + (size_t)(p.ksplit - 1) * p.tpb * nt * 4 * 32 * 4;
 }
 
-// How a product is cut into blocks: few tiles share their K among the blocks of a cluster so that every SM streams
-// weights; many tiles are grouped so that all blocks are resident at once (one wave) and the norm prologue is not
-// repeated more often than needed.
+// How a product is cut into blocks of the one-wave kernel: few tiles share their K among the blocks of a cluster so
+// that every SM streams weights; many tiles are grouped so that all blocks are resident at once and the norm
+// prologue is not repeated more often than needed. False: the product does not fit one wave.
 static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
     const int sms = 148, n_kb = (a.k + 31) / 32;
-    const size_t budget = 200 * 1024, most = 224 * 1024;
-    auto fill = [&](int tpb, int ksplit, int rounds) {
+    const size_t budget = 200 * 1024;
+    auto fill = [&](int tpb, int ksplit) {
         p.tpb = tpb;
         p.ksplit = ksplit;
         p.per = (n_kb + ksplit - 1) / ksplit;
         p.stride_w = pad_to_16_mod_128(p.per * 64);
         p.stride_x = pad_to_16_mod_128(p.per * 64);
-        p.rounds = rounds;
         p.nblk = (tiles + tpb - 1) / tpb;
         return plan_smem(p, nt);
     };
@@ -641,29 +628,18 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
         while (ksplit > 1 && (n_kb + ksplit - 1) / ksplit < 4) --ksplit;
         if (ksplit == 3) ksplit = 2;
         for (; ksplit <= 8; ksplit *= 2)
-            if (fill(1, ksplit, 1) <= budget) return true;
+            if (fill(1, ksplit) <= budget) return true;
         return false;
     }
     // every block resident at once, in one wave
     for (int tpb = 1; tpb <= 8; tpb *= 2) {
-        const size_t smem = fill(tpb, 1, 1);
+        const size_t smem = fill(tpb, 1);
         if (smem > budget) break;
         const int resident = (int)((227 * 1024) / (smem + 1024));
         const int blocks = (tiles + tpb - 1) / tpb;
         if (blocks <= sms * (resident > 3 ? 3 : resident)) return true;  // the launch bounds allow three blocks of 256 threads
     }
-    // too many tiles for one wave: one block per SM (or cluster) streams its share of the tile batches through two
-    // weight buffers, the token rows staged once; K is split over a cluster where two buffers of whole rows do not fit
-    for (int ksplit = 1; ksplit <= 8; ksplit *= 2) {
-        for (int tpb = 2; tpb >= 1; --tpb) {
-            if (fill(tpb, ksplit, 2) > most) continue;
-            const int batches = (tiles + tpb - 1) / tpb, nblk = sms / ksplit;
-            p.nblk = batches < nblk ? batches : nblk;
-            p.rounds = (batches + p.nblk - 1) / p.nblk;
-            if (p.rounds == 1) fill(tpb, ksplit, 1), p.nblk = batches;
-            return true;
-        }
-    }
+    // too many tiles for one wave: the streaming kernel's case
     return false;
 }
 
@@ -708,10 +684,10 @@ template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a,
     // SMs whose tiles weigh 128 KB or more, where one block per tile streaming its whole K beats a cluster sharing it.
     const bool heavy_tiles = tiles <= 148 && 2 * tiles > 148 && (size_t)16 * a.k * 2 >= 128 * 1024;
     int code = 0;
-    if ((!planned || p.rounds > 1 || heavy_tiles) && launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
+    if ((!planned || heavy_tiles) && launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
     if (!planned) return (int)cudaErrorInvalidValue;
     const size_t smem = plan_smem(p, NT);
-    auto kernel = p.rounds > 1 ? skinny_gemm_kernel<NT, EPI, NORM, true> : skinny_gemm_kernel<NT, EPI, NORM, false>;
+    auto kernel = skinny_gemm_kernel<NT, EPI, NORM>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t config = {};
