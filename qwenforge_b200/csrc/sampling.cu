@@ -42,12 +42,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
     const bool sample = temperature > 0.f;
     const uint32_t key = sample ? row_key(seed, seq_ids[row], steps[row]) : 0u;
     const float inv_t = sample ? 1.0f / temperature : 1.0f;
-    const int per = (vocab + chunks - 1) / chunks;
-    const int begin = chunk * per, end = min(vocab, begin + per);
+    const int per = (((vocab + chunks - 1) / chunks) + 3) & ~3;  // a multiple of 4: chunks start on 16 bytes when rows do
+    const int begin = min(vocab, chunk * per), end = min(vocab, begin + per);
     float bv = -FLT_MAX;
     int bi = 0x7fffffff;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        float s = x[i];
+    auto consider = [&](float s, int i) {
         if (sample) {
             const uint32_t bits = mix32(key ^ mix32((uint32_t)i ^ 0x27D4EB2Fu));
             const float u = ((float)(bits >> 9) + 0.5f) * (1.0f / 8388608.0f);
@@ -57,7 +56,34 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
             bv = s;
             bi = i;
         }
+    };
+    int done = begin;  // ids below `done` have been considered by some thread
+    if ((reinterpret_cast<uintptr_t>(x + begin) & 15) == 0) {
+        // four 16-byte loads in flight per thread: the scan is a stream, not a chain of round trips
+        const float4* x4 = reinterpret_cast<const float4*>(x + begin);
+        const int n4 = (end - begin) / 4;
+        for (int j0 = threadIdx.x; j0 < n4; j0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u * blockDim.x;
+                v[u] = j < n4 ? x4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = j0 + u * blockDim.x;
+                if (j < n4) {
+                    const int i = begin + 4 * j;
+                    consider(v[u].x, i);
+                    consider(v[u].y, i + 1);
+                    consider(v[u].z, i + 2);
+                    consider(v[u].w, i + 3);
+                }
+            }
+        }
+        done = begin + 4 * n4;
     }
+    for (int i = done + threadIdx.x; i < end; i += blockDim.x) consider(x[i], i);
     auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
