@@ -174,6 +174,7 @@ def main():
     with tempfile.TemporaryDirectory(prefix="qf_bench_") as folder, torch.inference_mode():
         write_random_model(config, seed=0, out_dir=folder, store_dtype=torch.bfloat16)
         model = Model.from_dir(folder, args.dtype, "cuda:0")
+        model.enable_prefill_graphs()  # as StudentEngine does: a prompt shape that comes back is replayed from a graph
         vocab = config.vocab_size
         cache = model.new_cache(max(batch, 64 if not args.no_points else batch) * context, 64)
 

@@ -167,10 +167,14 @@ class SequenceCache:
     max_len      the longest sequence a slot can hold (sizes the page tables)
     """
 
+    _serials = 0
+
     def __init__(self, needs: Sequence[Optional[object]], max_tokens: int, max_seqs: int, max_len: int,
                  dtype: torch.dtype, device):
         self.device = torch.device(device)
         self.dtype = dtype
+        SequenceCache._serials += 1
+        self.serial = SequenceCache._serials  # tells caches apart for whoever keeps things per cache (captured graphs)
         n_pages = max(1, round_up(max_tokens, PAGE_TOKENS) // PAGE_TOKENS)
         self.n_pages = n_pages
         self.max_seqs = max(1, min(max_seqs, n_pages))

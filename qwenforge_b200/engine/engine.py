@@ -113,6 +113,8 @@ class StudentEngine:
         self.tokenizer = load_tokenizer(model_dir, self.model.spec.vocab_size, self.local_files_only)
         self._max_cache_tokens = max_cache_tokens
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and GraphDecoder.supported(self.model)
+        if self.cuda_graphs:
+            self.model.enable_prefill_graphs()  # prompts whose shape comes back are replayed too
         self.cache = None
         self.graph_decoder: Optional[GraphDecoder] = None
         self.last_loop: Optional[GenerationLoop] = None

@@ -135,3 +135,70 @@ class GraphDecoder:
         while len(self.graphs) > self.keep:
             self.graphs.pop(next(iter(self.graphs)))
         return graph
+
+
+class PrefillGraphs:
+    """Steps of whole prompts or continuations replayed from CUDA graphs when their shape comes back.
+
+    A step of a few thousand tokens of a small model is bound by the host: two hundred launches take longer to issue
+    than to run. What fixes those launches is the step's shape (tokens, entries, longest entry, wanted rows) and
+    the cache it works on; everything else (token ids, positions, slots, page tables) is data in device buffers.
+    The second step of a shape is captured, with its integers in a buffer of the graph's own; every later one
+    copies its integers there and replays. Steps of more than `MAX_TOKENS` tokens are bound by the GPU and are
+    left alone, as are single-token steps (the decode graphs' business). The newest `keep` graphs are kept; they
+    share one memory pool, since no two run at the same time.
+    """
+
+    MAX_TOKENS = 8192
+
+    def __init__(self, model, keep: int = 8):
+        self.model, self.keep = model, keep
+        self.seen: dict = {}     # shape -> how often it came
+        self.graphs: dict = {}   # shape -> (graph, integer buffer, logits); newest last
+        self.pool = None
+        self.replays = 0
+
+    def takes(self, step) -> bool:
+        return 1 < step.max_q_len and step.n_tokens <= self.MAX_TOKENS
+
+    def run(self, cache, step) -> Optional[torch.Tensor]:
+        """The step's logits by replay, or None if this shape has no graph yet (the caller then runs it as usual;
+        the second time a shape comes it is captured here and its logits are returned)."""
+        model = self.model
+        key = (cache.serial,) + step.shape_key
+        held = self.graphs.pop(key, None)
+        if held is None:
+            self.seen[key] = self.seen.get(key, 0) + 1
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            if self.seen[key] < 2:
+                return None
+            held = self._capture(cache, step)
+        self.graphs[key] = held  # newest last
+        while len(self.graphs) > self.keep:
+            self.graphs.pop(next(iter(self.graphs)))
+        graph, integers, logits, launches = held
+        # from pageable memory the copy is complete when the call returns, so the host array may go
+        integers.copy_(torch.from_numpy(step.packed))
+        graph.replay()
+        self.replays += 1
+        ops.kernels.launches += launches
+        return None if logits is None else logits.clone()
+
+    def _capture(self, cache, step):
+        from .step import context_of
+        model = self.model
+        integers = torch.zeros(step.packed.size, dtype=torch.int32, device=model.device)
+        integers.copy_(torch.from_numpy(step.packed))
+        ctx = context_of(step, integers, model.err, model.dtype, model.attention, model.decode_scratch)
+        ctx.host_slots = ctx.host_starts = ctx.host_q_lens = None  # a replay's differ: no part may plan on them
+        stream = torch.cuda.Stream(device=model.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        torch.cuda.synchronize()
+        before = ops.kernels.launches
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, pool=self.pool):
+            logits = model.forward(ctx, cache)
+        if self.pool is None:
+            self.pool = graph.pool()
+        return graph, integers, logits, ops.kernels.launches - before

@@ -18,7 +18,7 @@ from ..config import ModelConfig, ModelSpec, load_config, resolve_dtype
 from ..csrc import prepare
 from ..parts import build_block, build_part
 from ..weights import load_weights
-from .step import StepContext, build_context
+from .step import StepContext, build_context, context_of, pack_step
 
 
 def _walk(part):
@@ -40,6 +40,7 @@ class Model:
         self.head = build_part("head", spec.head)
         self.err = None
         self.decode_scratch = None
+        self.prefill_graphs = None  # engine.graphs.PrefillGraphs once enabled
         self._bound = False
 
     # ------------------------------------------------------------------ structure
@@ -135,12 +136,27 @@ class Model:
             raise ValueError("step: a slot appears twice in one batch")
         cache.reserve(grow)
         cache.flush()
-        ctx = build_context(triples, want, self.err, self.dtype, self.device, self.attention, self.decode_scratch)
-        logits = self.forward(ctx, cache)
+        step = pack_step(triples, want)
+        logits, replayed = None, False
+        if self.prefill_graphs is not None and self.prefill_graphs.takes(step):
+            before = self.prefill_graphs.replays
+            logits = self.prefill_graphs.run(cache, step)
+            replayed = self.prefill_graphs.replays > before
+        if not replayed:
+            # from pageable memory the copy is complete when the call returns, so the host array may go
+            dev = torch.from_numpy(step.packed).to(self.device)
+            ctx = context_of(step, dev, self.err, self.dtype, self.attention, self.decode_scratch)
+            logits = self.forward(ctx, cache)
         for slot, tokens in entries:
             if slot >= 0:
                 cache.advance(slot, len(tokens))
         return logits
+
+    def enable_prefill_graphs(self, on: bool = True) -> None:
+        """Replay steps of whole prompts whose shape comes back from CUDA graphs (bfloat16, graph-safe parts only)."""
+        from .graphs import GraphDecoder, PrefillGraphs
+        usable = on and self.dtype == torch.bfloat16 and self.device.type == "cuda" and GraphDecoder.supported(self)
+        self.prefill_graphs = PrefillGraphs(self) if usable else None
 
     def raise_on_kernel_error(self) -> None:
         """Read the device error word (synchronises) and raise if a kernel met a bad index."""

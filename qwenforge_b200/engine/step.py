@@ -41,13 +41,28 @@ class StepContext:
         return self.max_q_len == 1
 
 
-def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]],
-                  err: torch.Tensor, dtype: torch.dtype, device, attention: str = "auto",
-                  decode_scratch=None) -> StepContext:
+@dataclass
+class PackedStep:
+    """A step's integers on the host, ready for ONE copy: ids | tok_seq | tok_pos | slots | cu_q | rows."""
+    packed: np.ndarray
+    n_seqs: int
+    n_tokens: int
+    n_rows: int
+    max_q_len: int
+    max_kv_len: int
+    host_slots: list
+    host_starts: list
+    host_q_lens: list
+
+    @property
+    def shape_key(self) -> tuple:
+        """What fixes the launches of a step of whole prompts or continuations (not the values they work on)."""
+        return (self.n_tokens, self.n_seqs, self.max_q_len, self.n_rows)
+
+
+def pack_step(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]]) -> PackedStep:
     """entries: (slot, start_position, token ids) per batch entry; want: per entry, the places among its
     tokens whose logits are wanted (None: the last token of every entry with a real slot)."""
-    n = len(entries)
-    # the step's integers, piece by piece, for ONE host-to-device copy: ids | tok_seq | tok_pos | slots | cu_q | rows
     id_parts, seq_parts, pos_parts = [], [], []
     slots: list[int] = []
     cu_q = [0]
@@ -70,10 +85,15 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
                 if not 0 <= place < q:
                     raise ValueError(f"step: entry {s} wants place {place} of {q} tokens")
                 rows.append(base + place)
-    total = cu_q[-1]
     packed = np.concatenate(id_parts + seq_parts + pos_parts + [np.asarray(slots + cu_q + rows, dtype=np.int32)])
-    # from pageable memory the copy is complete when the call returns, so the host array may go
-    dev = torch.from_numpy(packed).to(device)
+    return PackedStep(packed=packed, n_seqs=len(entries), n_tokens=cu_q[-1], n_rows=len(rows),
+                      max_q_len=max(len(e[2]) for e in entries), max_kv_len=max(e[1] + len(e[2]) for e in entries),
+                      host_slots=list(slots), host_starts=[e[1] for e in entries], host_q_lens=[len(e[2]) for e in entries])
+
+
+def context_of(step: PackedStep, dev: torch.Tensor, err: torch.Tensor, dtype: torch.dtype, attention: str = "auto",
+               decode_scratch=None) -> StepContext:
+    """The context whose tensors are views of `dev`, a device copy of `step.packed` (or a buffer that will hold one)."""
     o = 0
 
     def take(count):
@@ -82,11 +102,21 @@ def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optio
         o += count
         return piece
 
+    n, total = step.n_seqs, step.n_tokens
     return StepContext(
-        n_seqs=n, n_tokens=total, max_q_len=max(len(e[2]) for e in entries),
-        max_kv_len=max(e[1] + len(e[2]) for e in entries),
+        n_seqs=n, n_tokens=total, max_q_len=step.max_q_len, max_kv_len=step.max_kv_len,
         token_ids=take(total), tok_seq=take(total), tok_pos=take(total), slots=take(n), cu_q=take(n + 1),
-        want_rows=take(len(rows)) if rows else None, err=err, dtype=dtype, attention=attention,
+        want_rows=take(step.n_rows) if step.n_rows else None, err=err, dtype=dtype, attention=attention,
         decode_scratch=decode_scratch,
-        host_slots=list(slots), host_starts=[e[1] for e in entries], host_q_lens=[len(e[2]) for e in entries],
+        host_slots=step.host_slots, host_starts=step.host_starts, host_q_lens=step.host_q_lens,
     )
+
+
+def build_context(entries: Sequence[tuple[int, int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]],
+                  err: torch.Tensor, dtype: torch.dtype, device, attention: str = "auto",
+                  decode_scratch=None) -> StepContext:
+    """Pack the step on the host, copy it to the device in one copy, and view the copy as the step's tensors."""
+    step = pack_step(entries, want)
+    # from pageable memory the copy is complete when the call returns, so the host array may go
+    dev = torch.from_numpy(step.packed).to(device)
+    return context_of(step, dev, err, dtype, attention, decode_scratch)

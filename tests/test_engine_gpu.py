@@ -367,3 +367,33 @@ def test_tcgen05_prefill_attention_in_the_model(folders, name, monkeypatch):
     whole = plain_logits(folders, name, a + more)
     assert_logits_close(logits, whole[long_n:], torch.bfloat16, f"{name} tcgen05 continuation")
     cache.close(sa)
+
+
+def test_prefill_graphs_replay_equals_the_plain_implementation(folders):
+    """Steps of whole prompts are captured the second time their shape comes and replayed from then on: other
+    tokens, other slots, other start positions through the same graph give the plain implementation's logits."""
+    from qwenforge_b200.engine import Model
+    name = "small_64"
+    model = Model.from_dir(folders[name][0], torch.bfloat16, "cuda")
+    model.enable_prefill_graphs()
+    assert model.prefill_graphs is not None
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    cache = model.new_cache(2048, 4)
+    for round_ in range(4):
+        a, b = random_tokens(vocab, 70, 950 + round_), random_tokens(vocab, 130, 960 + round_)
+        slots = [cache.open(), cache.open()]
+        if round_ % 2:
+            slots.reverse()   # the same shape with the sequences in other slots
+        logits = model.step(cache, [(slots[0], a), (slots[1], b)], want=[[0, 69], list(range(130))])
+        model.raise_on_kernel_error()
+        assert_logits_close(logits[:2], plain_logits(folders, name, a)[[0, 69]], torch.bfloat16, f"graph round {round_} a")
+        assert_logits_close(logits[2:], plain_logits(folders, name, b), torch.bfloat16, f"graph round {round_} b")
+        if round_ == 3:  # a continuation of the same shape: 70 and 130 further tokens after 70 and 130
+            more_a, more_b = random_tokens(vocab, 70, 970), random_tokens(vocab, 130, 971)
+            logits = model.step(cache, [(slots[0], more_a), (slots[1], more_b)], want=[[0, 69], list(range(130))])
+            model.raise_on_kernel_error()
+            assert_logits_close(logits[:2], plain_logits(folders, name, a + more_a)[[70, 139]], torch.bfloat16, "graph continuation a")
+            assert_logits_close(logits[2:], plain_logits(folders, name, b + more_b)[130:], torch.bfloat16, "graph continuation b")
+        for slot in slots:
+            cache.close(slot)
+    assert model.prefill_graphs.replays == 4   # rounds 1, 2, 3 and the continuation; round 0 ran as usual
