@@ -173,7 +173,14 @@ class PrefillGraphs:
                 self.seen.clear()
             if self.seen[key] < 2:
                 return None
-            held = self._capture(cache, step)
+            try:
+                held = self._capture(cache, step)
+            except RuntimeError as exc:  # e.g. no memory for the graph's pool: this shape goes on launch by launch
+                import sys
+                print(f"[qwenforge_b200] a prompt step of shape {step.shape_key} could not be captured ({exc}); "
+                      "it runs launch by launch", file=sys.stderr, flush=True)
+                self.seen[key] = -(1 << 30)
+                return None
         self.graphs[key] = held  # newest last
         while len(self.graphs) > self.keep:
             self.graphs.pop(next(iter(self.graphs)))
