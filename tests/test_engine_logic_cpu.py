@@ -121,3 +121,21 @@ def test_no_cpu_path_in_the_package(tmp_path):
     folder, _ = make_model_dir(CONFIGS["tiny_a"], 0, tmp_path)
     with pytest.raises(KernelError, match="no CPU execution path|CUDA devices only"):
         Model.from_dir(folder, "float32", "cpu")
+
+
+def test_pack_step_layout_and_shape_key():
+    """The step's integers lie as ids | tok_seq | tok_pos | slots | cu_q | rows; steps of equal shape share a key
+    whatever their tokens, slots and start positions are."""
+    import numpy as np
+    from qwenforge_b200.engine.step import pack_step
+    a = pack_step([(3, 0, [5, 6, 7]), (-1, 0, [9]), (0, 10, [1, 2])], None)
+    assert a.n_tokens == 6 and a.n_seqs == 3 and a.n_rows == 2 and a.max_q_len == 3 and a.max_kv_len == 12
+    want = [5, 6, 7, 9, 1, 2] + [0, 0, 0, 1, 2, 2] + [0, 1, 2, 0, 10, 11] + [3, -1, 0] + [0, 3, 4, 6] + [2, 5]
+    assert a.packed.dtype == np.int32 and a.packed.tolist() == want
+    b = pack_step([(1, 40, [8, 8, 8]), (2, 7, [4]), (5, 0, [3, 3])], [[0], [], [1]])
+    assert b.shape_key == a.shape_key
+    c = pack_step([(1, 0, [8, 8, 8, 8]), (2, 0, [4, 4])], None)
+    assert c.shape_key != a.shape_key
+    import pytest
+    with pytest.raises(ValueError, match="wants place 3"):
+        pack_step([(0, 0, [1, 2, 3])], [[3]])
