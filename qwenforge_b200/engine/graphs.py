@@ -164,7 +164,6 @@ class PrefillGraphs:
     def run(self, cache, step) -> Optional[torch.Tensor]:
         """The step's logits by replay, or None if this shape has no graph yet (the caller then runs it as usual;
         the second time a shape comes it is captured here and its logits are returned)."""
-        model = self.model
         key = (cache.serial,) + step.shape_key
         held = self.graphs.pop(key, None)
         if held is None:
