@@ -379,16 +379,16 @@ def test_prefill_graphs_replay_equals_the_plain_implementation(folders):
     assert model.prefill_graphs is not None
     vocab = ALL_CONFIGS[name]["vocab_size"]
     cache = model.new_cache(2048, 4)
-    for round_ in range(4):
-        a, b = random_tokens(vocab, 70, 950 + round_), random_tokens(vocab, 130, 960 + round_)
+    for turn in range(4):
+        a, b = random_tokens(vocab, 70, 950 + turn), random_tokens(vocab, 130, 960 + turn)
         slots = [cache.open(), cache.open()]
-        if round_ % 2:
+        if turn % 2:
             slots.reverse()   # the same shape with the sequences in other slots
         logits = model.step(cache, [(slots[0], a), (slots[1], b)], want=[[0, 69], list(range(130))])
         model.raise_on_kernel_error()
-        assert_logits_close(logits[:2], plain_logits(folders, name, a)[[0, 69]], torch.bfloat16, f"graph round {round_} a")
-        assert_logits_close(logits[2:], plain_logits(folders, name, b), torch.bfloat16, f"graph round {round_} b")
-        if round_ == 3:  # a continuation of the same shape: 70 and 130 further tokens after 70 and 130
+        assert_logits_close(logits[:2], plain_logits(folders, name, a)[[0, 69]], torch.bfloat16, f"graph turn {turn} a")
+        assert_logits_close(logits[2:], plain_logits(folders, name, b), torch.bfloat16, f"graph turn {turn} b")
+        if turn == 3:  # a continuation of the same shape: 70 and 130 further tokens after 70 and 130
             more_a, more_b = random_tokens(vocab, 70, 970), random_tokens(vocab, 130, 971)
             logits = model.step(cache, [(slots[0], more_a), (slots[1], more_b)], want=[[0, 69], list(range(130))])
             model.raise_on_kernel_error()
@@ -396,4 +396,4 @@ def test_prefill_graphs_replay_equals_the_plain_implementation(folders):
             assert_logits_close(logits[2:], plain_logits(folders, name, b + more_b)[130:], torch.bfloat16, "graph continuation b")
         for slot in slots:
             cache.close(slot)
-    assert model.prefill_graphs.replays == 4   # rounds 1, 2, 3 and the continuation; round 0 ran as usual
+    assert model.prefill_graphs.replays == 4   # turns 1, 2, 3 and the continuation; turn 0 ran launch by launch
