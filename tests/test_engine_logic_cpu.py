@@ -139,3 +139,50 @@ def test_pack_step_layout_and_shape_key():
     import pytest
     with pytest.raises(ValueError, match="wants place 3"):
         pack_step([(0, 0, [1, 2, 3])], [[3]])
+
+
+def test_prompt_graphs_decisions_without_a_gpu():
+    """Which steps are replayed: not the first of a shape, every later one; other shapes and other caches have graphs
+    of their own; only the newest `keep` stay; a shape whose capture fails is left alone from then on."""
+    import types
+    import torch
+    from qwenforge_b200.engine.graphs import PrefillGraphs
+    from qwenforge_b200.engine.step import pack_step
+
+    class FakeGraph:
+        def __init__(self):
+            self.replayed = 0
+
+        def replay(self):
+            self.replayed += 1
+
+    captured = []
+
+    def fake_capture(self, cache, step):
+        if step.n_tokens == 13:
+            raise RuntimeError("no memory")
+        graph = FakeGraph()
+        captured.append((cache.serial, step.shape_key, graph))
+        return graph, torch.zeros(step.packed.size, dtype=torch.int32), torch.full((step.n_rows, 4), float(len(captured))), 7
+
+    graphs = PrefillGraphs(model=types.SimpleNamespace(), keep=2)
+    graphs._capture = types.MethodType(fake_capture, graphs)
+    cache_a, cache_b = types.SimpleNamespace(serial=1), types.SimpleNamespace(serial=2)
+    step = lambda lens, slot0=0: pack_step([(slot0 + i, 0, list(range(n))) for i, n in enumerate(lens)], None)
+
+    assert not graphs.takes(step([1, 1])) and graphs.takes(step([2, 1])) and not graphs.takes(step([9000]))
+    assert graphs.run(cache_a, step([5, 3])) is None and not captured           # first of its shape: launch by launch
+    out = graphs.run(cache_a, step([5, 3], slot0=4))                             # second: captured and replayed
+    assert out is not None and out.shape == (2, 4) and len(captured) == 1 and captured[0][2].replayed == 1
+    held_integers = graphs.graphs[(1, 8, 2, 5, 2)][1]
+    assert held_integers.tolist() == step([5, 3], slot0=4).packed.tolist()      # the replay's own integers went in
+    graphs.run(cache_a, step([5, 3]))
+    assert captured[0][2].replayed == 2 and graphs.replays == 2 and len(captured) == 1
+    assert graphs.run(cache_b, step([5, 3])) is None                             # another cache: its own count
+    assert graphs.run(cache_a, step([4, 4])) is None                             # same tokens, another longest entry
+    for lens in ([6, 1], [7, 1]):
+        graphs.run(cache_a, step(lens))
+        graphs.run(cache_a, step(lens))
+    assert len(graphs.graphs) == 2 and (1, 8, 2, 5, 2) not in graphs.graphs      # the oldest graph was dropped
+    assert graphs.run(cache_a, step([13])) is None and graphs.run(cache_a, step([13])) is None
+    assert graphs.run(cache_a, step([13])) is None and len(captured) == 3       # the failed capture is not tried again
