@@ -7,12 +7,12 @@
 // product. Per 64-position page of the head's kv head:
 //   S = Q K^T     D / 16 products of 128 x 64 x 16 into 64 columns of tensor memory; Q (once) and the page's keys
 //                 come by tiled copies of the tensor memory accelerator, 128-byte swizzle
-//   softmax       every row thread loads its row of S (64 float32) into registers: maximum, base-2 exponentials and
-//                 sum need no exchange between threads; the weights go to shared memory as bf16 in the swizzled
-//                 K-major layout the tensor cores read, and the thread arrives at a barrier of 128 arrivals
-//   PV            when all rows have arrived: S of the next page is issued first (the rows wait for nothing else), then
-//                 four products of 128 x D x 16, the page's values read as they lie (MN-major), ADDED to the
-//                 running output O in D further columns of tensor memory
+//   softmax       every row thread loads its row of S (64 float32) into registers and says so on a barrier of 128
+//                 arrivals: S of the NEXT page is then multiplied under this page's softmax. Maximum, base-2
+//                 exponentials and sum need no exchange between threads; the weights go to shared memory as bf16
+//                 in the swizzled K-major layout the tensor cores read, and the thread arrives at a second barrier
+//   PV            when all rows have arrived there: four products of 128 x D x 16, the page's values read as they
+//                 lie (MN-major), ADDED to the running output O in D further columns of tensor memory
 //   O             stays in tensor memory. The exponentials of a row are taken against a reference maximum that is
 //                 only moved when the true maximum has grown by more than 2^8 since (weights stay below 256, well
 //                 inside bf16 and float32); only then does the warp rescale its rows of O (load, multiply, store).
