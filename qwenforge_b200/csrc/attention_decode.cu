@@ -5,14 +5,16 @@
 // A block serves one (sequence, kv head, chunk of up to 16 query heads of the group, split). The query heads of
 // the group are the 16 rows of an m16n8k16 tensor-core tile, so keys and values are read once for the whole
 // group. Each WARP works alone on whole pages (64 positions: 64 x D keys, 64 x D values): the page arrives in two
-// halves through the warp's own two shared-memory buffers, by 16-byte asynchronous copies into padded rows (bulk copies of single 128-byte
-// rows were measured slower: a page is too many small requests for the copy engine), then S = Q K^T, online
-// softmax in float32 (base-2 exponentials, the scale folded in), O += P V. With eight warps a block has eight
-// pages in flight and no block-wide barrier inside the loop. The warps are merged in shared memory at the end.
-// With one split the block writes the output; otherwise it writes (max, sum, O) partials to scratch and takes a
-// ticket: the block that draws the last ticket of its (sequence, kv head, chunk) merges all partials and resets
-// the ticket counter. No block waits for another. (Merging the splits of a thread-block cluster through
-// distributed shared memory instead was measured slower at these sizes: 19.8 against 14.4 microseconds.)
+// halves through the warp's own two shared-memory buffers (tiled TMA copies, or 16-byte asynchronous copies into
+// padded rows; see below), then S = Q K^T, online softmax in float32 (base-2 exponentials, the scale folded in;
+// halves that are seen whole skip the mask), O += P V. With eight warps a block has eight pages in flight and no
+// block-wide barrier inside the loop. Halves that hold only positions before the new token are fetched before the
+// kernel waits for the one that wrote the new token. At the end every warp leaves its rescaled sums in its own
+// buffer and all threads add them up in warp order. With one split the block writes the output; otherwise it
+// writes (max, sum, O) partials to scratch and takes a ticket: the block that draws the last ticket of its
+// (sequence, kv head, chunk) folds all partials, two outputs per thread at once, and resets the ticket counter.
+// No block waits for another. (Merging the splits of a thread-block cluster through distributed shared memory
+// instead was measured slower, and so was a variant of sixteen warps with half a page each.)
 // The kernel is launched as a programmatic dependent of the kernel before it.
 #include "tma.cuh"
 
