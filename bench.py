@@ -145,14 +145,165 @@ def timed_decode(model, cache, batch, context, steps, warmup, vocab, torch):
     return ms, graph.kernels_per_step
 
 
+def check_decode_logits(model, cache, folder, batch, context, vocab, torch, rows_checked=2):
+    """Guards the number: 32 steps of the batch replayed from the decode graph that the timing used (same rows, same
+    length bound), then the last step's bfloat16 logits of two rows against the logits that a float32 model of the
+    same weights gives for the same tokens. Raises if they differ by more than the tests' bfloat16 tolerance."""
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.engine.graphs import CHUNK_STEPS, DecodeGraph
+    from qwenforge_b200.sampling import Sampler
+    sampler = Sampler()
+    prompt_len = context - CHUNK_STEPS - 1
+    g = torch.Generator().manual_seed(4321)
+    slots = [cache.open() for _ in range(batch)]
+    cache.reserve([(s, context) for s in slots])
+    prompts, first = [], []
+    for begin in range(0, batch, 8):
+        chunk = slots[begin:begin + 8]
+        part = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in chunk]
+        prompts += part
+        first += sampler(model.step(cache, list(zip(chunk, part)))).tolist()
+    cache.flush()
+    graph = DecodeGraph(model, cache, batch, context, sampler)
+    graph.capture()
+    graph.load(slots, first, [prompt_len] * batch, [1] * batch, [1 << 30] * batch, list(range(batch)), [])
+    produced = graph.run(CHUNK_STEPS)
+    got = graph.last_logits.float().cpu()
+    model.raise_on_kernel_error()
+    for s in slots:
+        cache.close(s)
+    exact = Model.from_dir(folder, "float32", "cuda:0")
+    exact_cache = exact.new_cache(2 * (context + 64), 2)
+    worst, bound = 0.0, 0.0
+    for row in sorted({0, batch - 1})[:rows_checked]:
+        tokens = prompts[row] + [first[row]] + [step[row] for step in produced[:-1]]
+        slot = exact_cache.open()
+        ref = exact.step(exact_cache, [(slot, tokens)]).float().cpu()[0]
+        exact_cache.close(slot)
+        err = float((got[row] - ref).abs().max())
+        limit = 2e-2 + 4e-2 * float(ref.abs().max())
+        if err > limit:
+            raise AssertionError(f"decode graph logits of row {row} differ from float32 by {err:.3e} (limit {limit:.3e})")
+        worst, bound = max(worst, err), max(bound, limit)
+    exact.raise_on_kernel_error()
+    del exact, exact_cache
+    torch.cuda.empty_cache()
+    return {"max_abs_diff_vs_fp32": round(worst, 5), "limit": round(bound, 5), "rows": rows_checked, "steps_replayed": CHUNK_STEPS}
+
+
+class _StubTokenizer:
+    """Stands where the reference loads a tokenizer (there are no tokenizer files and no network): a prompt is the text
+    "<length> <seed>" and encodes to that many seeded uniform-random token ids; ids decode to their decimal text."""
+    pad_token_id, eos_token_id, bos_token_id = 0, 1, 1
+    pad_token, eos_token, padding_side = "<pad>", "<eos>", "right"
+
+    def __init__(self, vocab, torch):
+        self.vocab, self.torch = vocab, torch
+
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True):
+        return messages[0]["content"]
+
+    def __call__(self, texts, add_special_tokens=False, padding=True, return_attention_mask=True, return_tensors="pt"):
+        torch = self.torch
+        rows = []
+        for text in texts:
+            length, seed = (int(x) for x in text.split())
+            rows.append(torch.randint(2, self.vocab, (length,), generator=torch.Generator().manual_seed(seed)))
+        longest = max(len(r) for r in rows)
+        ids = torch.zeros(len(rows), longest, dtype=torch.long)
+        mask = torch.zeros(len(rows), longest, dtype=torch.long)
+        for i, r in enumerate(rows):
+            ids[i, :len(r)] = r
+            mask[i, :len(r)] = 1
+        return {"input_ids": ids, "attention_mask": mask}
+
+    def batch_decode(self, rows, skip_special_tokens=True, clean_up_tokenization_spaces=False):
+        return [" ".join(str(t) for t in row) for row in rows]
+
+
+def reference_arm(args):
+    """The unmodified reference (a plain copy of its tree under baseline/_ref) through its own entry point,
+    `StudentEngine(...).generate(prompts, max_new_tokens, batch_size)`, on the same random-weight model folder, batch,
+    context and step count. Only its tokenizer loader is replaced by a stub (it is a script tree that pip cannot
+    install, and its tokenizer files are not here). None of this library's kernels or models run: only the writer of
+    the random-weight folder. The decode rate is the difference of two calls that share the prompt step: one that
+    ends at the context length and one that stops `steps` tokens earlier."""
+    import types
+    unavailable = lambda why: print(json.dumps({"impl": "reference", "unavailable": why})) or 0
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "student_engine.py").exists():
+        return unavailable("baseline/_ref holds no copy of the reference tree (student_engine.py is missing)")
+    if args.gpus != 1:
+        return unavailable("the reference engine runs on one GPU")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        sys.path.insert(0, str(ref_root))
+        import student_engine as se
+        from qwenforge_b200.config import preset_config
+        from qwenforge_b200.weights import write_random_model
+        config = preset_config(args.preset, num_hidden_layers=args.layers) if args.layers else preset_config(args.preset)
+        layers_cfg = preset_config(args.preset).num_hidden_layers
+        steps, warmup, batch, context = args.steps, max(args.warmup, 3), args.batch, args.context
+        short_new = 9                       # the reference graphs runs of 8 or more new tokens (student_engine.py:1274)
+        long_new = short_new + steps
+        prompt_len = context - long_new + 1  # the long call's last token is fed at position context - 1
+        with tempfile.TemporaryDirectory(prefix="qf_ref_") as folder:
+            write_random_model(config, seed=0, out_dir=folder, store_dtype=torch.bfloat16)
+            stub = _StubTokenizer(config.vocab_size, torch)
+            se.AutoTokenizer = types.SimpleNamespace(from_pretrained=lambda *a, **k: stub)
+            dtype = "float16"  # the reference's default; its own attention kernels are written for float16
+            engine = se.StudentEngine(folder, device="cuda", dtype=dtype, attn_implementation="sdpa", local_files_only=True)
+            prompts = [f"{prompt_len} {100 + i}" for i in range(batch)]
+
+            def timed(new_tokens, texts=prompts, size=batch):
+                torch.cuda.synchronize()
+                start = time.perf_counter()
+                out = engine.generate(texts, new_tokens, batch_size=size)
+                torch.cuda.synchronize()
+                assert len(out) == len(texts) and all(len(o.split()) == new_tokens for o in out)
+                return (time.perf_counter() - start) * 1e3
+
+            for _ in range(2):  # warm-up: compiles its pointwise kernels, captures both decode graphs
+                timed(short_new)
+                timed(long_new)
+            repeats = 1 + max(1, warmup // 3)
+            with ClockSampler() as clocks:
+                shorts = sorted(timed(short_new) for _ in range(repeats))
+                longs = sorted(timed(long_new) for _ in range(repeats))
+            ms = (longs[len(longs) // 2] - shorts[len(shorts) // 2]) / steps
+            value = batch * 1e3 / ms
+            ttft = sorted(timed(1, [f"{args.prefill_tokens} 7"], 1) for _ in range(5))[2:]
+            prefill_ms = ttft[len(ttft) // 2]
+            graphs = bool(getattr(engine, "_graph_decode_enabled", False)) and bool(getattr(engine, "_graph_ctx", None))
+        line = {
+            "impl": "reference", "metric": "decode tokens/s (batch %d, context %d)" % (batch, context),
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp16", "data": "synthetic (seeded uniform-random token ids, seeded random weights)",
+            "config": {"model": args.preset, "layers": config.num_hidden_layers, "layers_in_config": layers_cfg,
+                       "global_batch": batch, "seq_len": context, "prefill_tokens": args.prefill_tokens,
+                       "parallelism": "single GPU", "decode_graphs": graphs,
+                       "timing": "host clock around generate(); decode = (call ending at the context - call ending "
+                                 "%d tokens earlier) / %d" % (steps, steps)},
+            "clocks": clocks.summary(),
+            "prefill": {"value": round(args.prefill_tokens / prefill_ms * 1e3, 1), "tokens": args.prefill_tokens,
+                        "ms": round(prefill_ms, 3), "note": "generate() of one prompt with max_new_tokens=1"},
+            "e2e": {"value": round(value, 1), "unit": "tokens/s",
+                    "note": "the same figure: every call goes through StudentEngine.generate, strings in and out"},
+            "call_ms": {"short": round(shorts[len(shorts) // 2], 2), "long": round(longs[len(longs) // 2], 2)},
+        }
+        print(json.dumps(line))
+        return 0
+    except Exception as exc:  # the reference could not be driven here: say why, in one line
+        return unavailable(f"{type(exc).__name__}: {str(exc).splitlines()[0] if str(exc) else ''}"[:300])
+
+
 def main():
     args = parse()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference has no setup.py or pyproject.toml, so pip cannot install it into baseline/_ref; "
-                          "its entry point also needs the Qwen2.5-0.5B-Instruct tokenizer and weights, which are not on "
-                          "the box (no network)"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print("bench.py: this library runs on ONE GPU; --gpus N > 1 is not supported")
         return 2
@@ -193,10 +344,26 @@ def main():
             times.append(a.elapsed_time(b))
             cache.close(slot)
         prefill_ms = sorted(times[2:])[len(times[2:]) // 2]
+        # the same prompt as a shape that was not seen before (another number of wanted rows): issued launch by launch
+        firsts = []
+        for extra in (2, 3, 4):
+            slot = cache.open()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            model.step(cache, [(slot, prompt)], want=[list(range(args.prefill_tokens - extra, args.prefill_tokens))])
+            b.record()
+            torch.cuda.synchronize()
+            firsts.append(a.elapsed_time(b))
+            cache.close(slot)
+        first_ms = sorted(firsts)[1]
         t = args.prefill_tokens
         prefill_flops = numbers["linear_flops_per_token"] * t + numbers["attn_flops"](t) + numbers["head_flops_per_row"]
-        prefill = {"value": round(t / prefill_ms * 1e3, 1), "tokens": t, "ms": round(prefill_ms, 3),
-                   "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        frac = lambda ms: round(prefill_flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+        prefill = {"value": round(t / prefill_ms * 1e3, 1), "tokens": t, "ms": round(prefill_ms, 3), "frac": frac(prefill_ms),
+                   "how": "a prompt shape that came before, replayed from its CUDA graph (median of 3)",
+                   "first_seen_ms": round(first_ms, 3), "first_seen_frac": frac(first_ms),
+                   "first_seen_value": round(t / first_ms * 1e3, 1)}
 
         # ---- the headline: decode at the default batch, with clocks sampled meanwhile
         with ClockSampler() as clocks:
@@ -208,6 +375,9 @@ def main():
         achieved = step_bytes / (ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
+
+        # ---- the timed path gives the right logits: a step replayed from the same decode graph against float32
+        logits_check = check_decode_logits(model, cache, folder, batch, context, vocab, torch)
 
         points, e2e = {}, None
         if not args.no_points:
@@ -245,7 +415,7 @@ def main():
                    "parallelism": "single GPU", "l2": "operands larger than L2 (weights ~1 GB per step); no flush",
                    "tied_head": config.tie_word_embeddings},
         "clocks": clocks.summary(), "gpu_launches": gpu_launches, "prefill": prefill, "roofline": roofline,
-        "points": points, "e2e": e2e,
+        "points": points, "e2e": e2e, "logits_check": logits_check,
     }
     print(json.dumps(line))
     return 0

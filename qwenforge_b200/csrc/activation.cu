@@ -35,10 +35,11 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
 QF_EXPORT int qf_swiglu(int is_bf16, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
     const size_t total = (size_t)rows * inter;
     if (total == 0) return 0;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;  // blocks that a grid-stride loop is given
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
     if (is_bf16 && inter % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
         const size_t total8 = total / 8;
-        const int b8 = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        const int b8 = (int)((total8 + 255) / 256 < most ? (total8 + 255) / 256 : most);
         swiglu_bf16x8_kernel<<<b8, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total8);
     } else if (is_bf16)
         swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total);

@@ -84,6 +84,20 @@ __device__ __forceinline__ T* kv_row(const KvSite<T>& s, int slot, int pos, int 
            ((long long)(which * s.kv_heads + h) * QF_PAGE + (pos % QF_PAGE)) * s.head_dim;
 }
 
+// Streaming multiprocessors of the current device, asked once per device (0 if the device cannot be asked): what
+// grids, split counts and one-wave plans are sized by.
+static inline int qf_sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // Programmatic dependent launch. A kernel launched with `launch_pdl` may start while the kernel before it on the
 // stream is still running; it must call grid_dependency_wait() before it reads anything that kernel wrote or
 // writes anything at all. What it does before that call (fetching weights, which no kernel writes) overlaps the

@@ -113,7 +113,8 @@ template <typename T> __global__ void residual_add_kernel(float* __restrict__ hi
 // hidden += delta over n elements (the residual stream catching up with a pending update).
 QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    const long long most = (long long)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 8;
+    const int blocks = (int)((n + 255) / 256 < most ? (n + 255) / 256 : most);
     if (is_bf16)
         residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(hidden, (const bf16*)delta, n);
     else

@@ -606,8 +606,8 @@ static size_t plan_smem(const SkinnyPlan& p, int nt) {
 // How a product is cut into blocks of the one-wave kernel: few tiles share their K among the blocks of a cluster so
 // that every SM streams weights; many tiles are grouped so that all blocks are resident at once and the norm
 // prologue is not repeated more often than needed. False: the product does not fit one wave.
-static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
-    const int sms = 148, n_kb = (a.k + 31) / 32;
+static bool make_plan(int k, int tiles, int nt, int sms, SkinnyPlan& p) {
+    const int n_kb = (k + 31) / 32;
     const size_t budget = 200 * 1024;
     auto fill = [&](int tpb, int ksplit) {
         p.tpb = tpb;
@@ -622,7 +622,7 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
         // K is split only as far as a block's weights need it: up to 48 KB a block has them in flight long before its
         // token rows are ready, and a cluster's exchange of partial sums would only add to the chain of waits
         int ksplit = 2 * sms / tiles;
-        const int by_bytes = (int)(((size_t)16 * a.k * 2 + 48 * 1024 - 1) / (48 * 1024));
+        const int by_bytes = (int)(((size_t)16 * k * 2 + 48 * 1024 - 1) / (48 * 1024));
         if (ksplit > by_bytes) ksplit = by_bytes;
         if (ksplit > 4) ksplit = 4;
         while (ksplit > 1 && (n_kb + ksplit - 1) / ksplit < 4) --ksplit;
@@ -643,57 +643,100 @@ static bool make_plan(const SkinnyArgs& a, int tiles, int nt, SkinnyPlan& p) {
     return false;
 }
 
-template <int NT, int EPI, bool NORM, bool XS>
-static int launch_stream_variant(const SkinnyArgs& a, int tiles, const StreamPlan& sp, size_t smem, cudaStream_t stream) {
-    auto kernel = skinny_stream_kernel<NT, EPI, NORM, XS>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    return (int)launch_pdl(kernel, dim3(sp.nblk), dim3(SK_STREAM_THREADS), smem, stream, a, sp, tiles);
-}
-
-// The streaming kernel for products of more tiles than one wave of blocks holds; false if it does not take the shape.
-template <int NT, int EPI, bool NORM> static bool launch_stream(const SkinnyArgs& a, int tiles, cudaStream_t stream, int& code) {
-    const int sms = 148;
+// The streaming kernel's geometry for a product; false if it does not take the shape (K not a multiple of 32, or
+// token rows that need the norm and do not fit beside three stages of the ring).
+static bool make_stream_plan(int k, int tiles, int nt, bool norm, int sms, StreamPlan& sp, bool& xs, size_t& smem) {
     const size_t most = 224 * 1024;
-    if (a.k % 32) return false;
-    StreamPlan sp;
-    sp.n_chunks = (a.k + SK_CHUNK - 1) / SK_CHUNK;
-    sp.stride_x = pad_to_16_mod_128(a.k * 2);
+    if (k % 32) return false;
+    sp.n_chunks = (k + SK_CHUNK - 1) / SK_CHUNK;
+    sp.stride_x = pad_to_16_mod_128(k * 2);
     sp.nblk = tiles < sms ? tiles : sms;
-    const size_t red = (size_t)SK_WARPS * NT * 4 * 32 * 4, x_bytes = (size_t)8 * NT * sp.stride_x;
+    const size_t red = (size_t)SK_WARPS * nt * 4 * 32 * 4, x_bytes = (size_t)8 * nt * sp.stride_x;
     // the token rows stay in shared memory while that leaves the ring four stages (three when they need the norm and
     // so cannot travel); rows that need no norm may travel through the ring instead
-    const size_t stage = (size_t)16 * SK_STAGE_STRIDE, stage_xs = (size_t)(16 + 8 * NT) * SK_STAGE_STRIDE;
-    const bool resident = red + x_bytes + (NORM ? 3 : 4) * stage <= most;
-    if (!resident && NORM) return false;
+    const size_t stage = (size_t)16 * SK_STAGE_STRIDE, stage_xs = (size_t)(16 + 8 * nt) * SK_STAGE_STRIDE;
+    const bool resident = red + x_bytes + (norm ? 3 : 4) * stage <= most;
+    if (!resident && norm) return false;
     const size_t per_stage = resident ? stage : stage_xs, fixed = red + (resident ? x_bytes : 0);
     size_t stages = (most - fixed) / per_stage;
     if (stages > 16) stages = 16;
     if (stages < 3) return false;
     sp.stages = (int)stages;
-    const size_t smem = fixed + stages * per_stage;
-    if (resident) code = launch_stream_variant<NT, EPI, NORM, false>(a, tiles, sp, smem, stream);
-    else code = launch_stream_variant<NT, EPI, false, true>(a, tiles, sp, smem, stream);
+    xs = !resident;
+    smem = fixed + stages * per_stage;
     return true;
 }
 
-template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
-    SkinnyPlan p;
-    const bool planned = make_plan(a, tiles, NT, p);
+// Which kernel runs a product, and with which geometry. The one place that decides it: the launch and the
+// host's question "would you take this shape" (`qf_skinny_gemm_takes`) both read it, so they cannot disagree.
+enum { SK_NONE = 0, SK_WAVE = 1, SK_STREAM = 2, SK_STREAM_XS = 3 };
+struct Decision {
+    int kind = SK_NONE;
+    int tiles = 0, nt = 1;
+    SkinnyPlan wave;
+    StreamPlan stream;
+    size_t smem = 0;
+};
+
+// Requirements of every variant: 1 <= m <= 16; k, ldw (and ldx without the norm) multiples of 8; SWIGLU: inter a
+// multiple of 8; QKV: head_dim a multiple of 16, rotation over the whole head.
+static Decision decide(int epilogue, bool norm, const SkinnyArgs& a, int sms) {
+    Decision d;
+    if (sms <= 0 || a.m < 1 || a.m > 16 || a.k % 8 || a.ldw % 8 || a.k <= 0 || a.n <= 0) return d;
+    if (!norm && a.ldx % 8) return d;
+    switch (epilogue) {
+        case EPI_PLAIN:
+        case EPI_RESIDUAL:
+            d.tiles = (a.n + 15) / 16;
+            break;
+        case EPI_SWIGLU:
+            if (a.inter <= 0 || a.inter % 8 || a.n != 2 * a.inter) return d;
+            d.tiles = a.inter / 8;
+            break;
+        case EPI_QKV:
+            if (a.head_dim <= 0 || a.head_dim % 16 || (a.inv_freq && a.rot_dim != a.head_dim) ||
+                a.n != (a.n_heads + 2 * a.kv_heads) * a.head_dim)
+                return d;
+            d.tiles = (a.n_heads + 2 * a.kv_heads) * (a.head_dim / 16);
+            break;
+        default:
+            return d;
+    }
+    d.nt = a.m <= 8 ? 1 : 2;
+    const bool planned = make_plan(a.k, d.tiles, d.nt, sms, d.wave);
     // The streaming kernel takes what does not fit one wave of blocks; and products of at least half as many tiles as
     // SMs whose tiles weigh 128 KB or more, where one block per tile streaming its whole K beats a cluster sharing it.
-    const bool heavy_tiles = tiles <= 148 && 2 * tiles > 148 && (size_t)16 * a.k * 2 >= 128 * 1024;
-    int code = 0;
-    if ((!planned || heavy_tiles) && launch_stream<NT, EPI, NORM>(a, tiles, stream, code)) return code;
-    if (!planned) return (int)cudaErrorInvalidValue;
-    const size_t smem = plan_smem(p, NT);
+    const bool heavy_tiles = d.tiles <= sms && 2 * d.tiles > sms && (size_t)16 * a.k * 2 >= 128 * 1024;
+    bool xs = false;
+    if ((!planned || heavy_tiles) && make_stream_plan(a.k, d.tiles, d.nt, norm, sms, d.stream, xs, d.smem)) {
+        d.kind = xs ? SK_STREAM_XS : SK_STREAM;
+        return d;
+    }
+    if (!planned) return d;
+    d.kind = SK_WAVE;
+    d.smem = plan_smem(d.wave, d.nt);
+    return d;
+}
+
+template <int NT, int EPI, bool NORM, bool XS>
+static int launch_stream_variant(const SkinnyArgs& a, const Decision& d, cudaStream_t stream) {
+    auto kernel = skinny_stream_kernel<NT, EPI, NORM, XS>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d.smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)launch_pdl(kernel, dim3(d.stream.nblk), dim3(SK_STREAM_THREADS), d.smem, stream, a, d.stream, d.tiles);
+}
+
+template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a, const Decision& d, cudaStream_t stream) {
+    if (d.kind == SK_STREAM) return launch_stream_variant<NT, EPI, NORM, false>(a, d, stream);
+    if (d.kind == SK_STREAM_XS) return launch_stream_variant<NT, EPI, false, true>(a, d, stream);
+    const SkinnyPlan& p = d.wave;
     auto kernel = skinny_gemm_kernel<NT, EPI, NORM>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)d.smem);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(p.nblk * p.ksplit);
     config.blockDim = dim3(SK_THREADS);
-    config.dynamicSmemBytes = smem;
+    config.dynamicSmemBytes = d.smem;
     config.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -707,36 +750,48 @@ template <int NT, int EPI, bool NORM> static int launch_one(const SkinnyArgs& a,
     return (int)cudaLaunchKernelEx(&config, kernel, a, p);
 }
 
-template <int EPI, bool NORM> static int launch_epi(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
-    if (a.m <= 8) return launch_one<1, EPI, NORM>(a, tiles, stream);
-    return launch_one<2, EPI, NORM>(a, tiles, stream);
+template <int EPI, bool NORM> static int launch_epi(const SkinnyArgs& a, const Decision& d, cudaStream_t stream) {
+    if (d.nt == 1) return launch_one<1, EPI, NORM>(a, d, stream);
+    return launch_one<2, EPI, NORM>(a, d, stream);
 }
 
-// One entry for all variants. Shapes that the kernel does not take return cudaErrorInvalidValue; the caller
-// then uses the unfused kernels. Requirements: 1 <= m <= 16; k, ldw, ldx multiples of 8; 16-byte aligned rows;
-// SWIGLU: inter a multiple of 8; QKV: head_dim a multiple of 16 and rot_dim == head_dim when inv_freq is given.
+// One entry for all variants. A shape that no kernel of this file takes returns cudaErrorInvalidValue and launches
+// nothing; `qf_skinny_gemm_takes` answers the same question beforehand.
 QF_EXPORT int qf_skinny_gemm(int epilogue, int norm, const SkinnyArgs* args, cudaStream_t stream) {
     const SkinnyArgs& a = *args;
-    if (a.m < 1 || a.m > 16 || a.k % 8 || a.ldw % 8 || a.k <= 0 || a.n <= 0) return (int)cudaErrorInvalidValue;
-    if (!norm && a.ldx % 8) return (int)cudaErrorInvalidValue;
-    int tiles;
+    const Decision d = decide(epilogue, norm != 0, a, qf_sm_count());
+    if (d.kind == SK_NONE) return (int)cudaErrorInvalidValue;
     switch (epilogue) {
         case EPI_PLAIN:
-            tiles = (a.n + 15) / 16;
-            return norm ? launch_epi<EPI_PLAIN, true>(a, tiles, stream) : launch_epi<EPI_PLAIN, false>(a, tiles, stream);
+            return norm ? launch_epi<EPI_PLAIN, true>(a, d, stream) : launch_epi<EPI_PLAIN, false>(a, d, stream);
         case EPI_RESIDUAL:
-            tiles = (a.n + 15) / 16;
-            return norm ? launch_epi<EPI_RESIDUAL, true>(a, tiles, stream) : launch_epi<EPI_RESIDUAL, false>(a, tiles, stream);
+            return norm ? launch_epi<EPI_RESIDUAL, true>(a, d, stream) : launch_epi<EPI_RESIDUAL, false>(a, d, stream);
         case EPI_SWIGLU:
-            if (a.inter % 8 || a.n != 2 * a.inter) return (int)cudaErrorInvalidValue;
-            tiles = a.inter / 8;
-            return norm ? launch_epi<EPI_SWIGLU, true>(a, tiles, stream) : launch_epi<EPI_SWIGLU, false>(a, tiles, stream);
+            return norm ? launch_epi<EPI_SWIGLU, true>(a, d, stream) : launch_epi<EPI_SWIGLU, false>(a, d, stream);
         case EPI_QKV:
-            if (a.head_dim % 16 || (a.inv_freq && a.rot_dim != a.head_dim) ||
-                a.n != (a.n_heads + 2 * a.kv_heads) * a.head_dim)
-                return (int)cudaErrorInvalidValue;
-            tiles = (a.n_heads + 2 * a.kv_heads) * (a.head_dim / 16);
-            return norm ? launch_epi<EPI_QKV, true>(a, tiles, stream) : launch_epi<EPI_QKV, false>(a, tiles, stream);
+            return norm ? launch_epi<EPI_QKV, true>(a, d, stream) : launch_epi<EPI_QKV, false>(a, d, stream);
     }
     return (int)cudaErrorInvalidValue;
+}
+
+// Whether `qf_skinny_gemm` would run a product of these sizes on the current device: 0 no; 1 the one-wave kernel;
+// 2 the streaming kernel with the token rows resident; 3 the streaming kernel with the token rows travelling
+// through the ring. Launches nothing. The sizes are those of the arguments: m token rows, weight [n][k] with rows
+// `ldw` apart, input rows `ldx` apart (ignored with the norm), `inter` for SWIGLU, the head counts for QKV
+// (`rotary` non-zero: the rotation is applied, over `rot_dim` components).
+QF_EXPORT int qf_skinny_gemm_takes(int epilogue, int norm, int m, int n, int k, int ldw, int ldx, int inter, int n_heads,
+                                   int kv_heads, int head_dim, int rotary, int rot_dim) {
+    SkinnyArgs a = {};
+    a.m = m;
+    a.n = n;
+    a.k = k;
+    a.ldw = ldw;
+    a.ldx = ldx;
+    a.inter = inter;
+    a.n_heads = n_heads;
+    a.kv_heads = kv_heads;
+    a.head_dim = head_dim;
+    a.rot_dim = rot_dim;
+    a.inv_freq = rotary ? reinterpret_cast<const float*>(&a) : nullptr;  // only tested against null
+    return decide(epilogue, norm != 0, a, qf_sm_count()).kind;
 }

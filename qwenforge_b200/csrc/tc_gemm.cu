@@ -187,12 +187,12 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
     if (epilogue == TC_SWIGLU) {
         if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
         const int inter = n / 2;
-        const bool wide = (long long)m_tiles * ((inter + 127) / 128) >= 148;
+        const bool wide = (long long)m_tiles * ((inter + 127) / 128) >= qf_sm_count();
         return wide ? launch_tc<TC_SWIGLU, 256>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 127) / 128, m_tiles), stream)
                     : launch_tc<TC_SWIGLU, 128>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 63) / 64, m_tiles), stream);
     }
     if (epilogue != TC_PLAIN) return (int)cudaErrorInvalidValue;
-    const bool wide = (long long)m_tiles * ((out_cols + 255) / 256) >= 148;
+    const bool wide = (long long)m_tiles * ((out_cols + 255) / 256) >= qf_sm_count();
     return wide ? launch_tc<TC_PLAIN, 256>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 255) / 256, m_tiles), stream)
                 : launch_tc<TC_PLAIN, 128>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, m_tiles), stream);
 }

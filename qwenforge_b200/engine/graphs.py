@@ -61,9 +61,11 @@ class DecodeGraph:
         self.sample_scratch = ops.SampleScratch()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
+        self.last_logits: Optional[torch.Tensor] = None  # float32 [rows, vocab] of the newest replayed step
 
     def _one_step(self) -> None:
         logits = self.model.forward(self.ctx, self.cache)
+        self.last_logits = logits  # inside a capture this is the graph's own buffer: every replay refills it
         self.sampler(logits, self.seq_ids, self.steps, out=self.sampled, scratch=self.sample_scratch)
         ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
                            self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor)

@@ -52,6 +52,17 @@ def require_cuda(device, what: str = "this operation") -> None:
 
 launches = 0  # kernels of this library launched by this process (the measurement reads it)
 
+_sm_counts: dict = {}
+
+
+def sm_count(device) -> int:
+    """Streaming multiprocessors of `device` (asked once): what grids and split counts are sized by."""
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _sm_counts[index]
+
 
 def _check(code: int, what: str) -> None:
     global launches
@@ -354,8 +365,8 @@ def sample(logits: torch.Tensor, temperature: float, seed: int, seq_ids: Optiona
         _dev("steps", steps, torch.int32)
         if seq_ids.numel() != rows or steps.numel() != rows:
             raise KernelError("sample: seq_ids and steps must have one element per row")
-    # enough blocks to fill the GPU when there are few rows, at least 2048 tokens of the vocabulary each
-    chunks = max(1, min(-(-vocab // 2048), -(-1184 // rows), 64))
+    # enough blocks to fill the GPU (eight per SM) when there are few rows, at least 2048 tokens of the vocabulary each
+    chunks = max(1, min(-(-vocab // 2048), -(-8 * sm_count(logits.device) // rows), 64))
     scratch = scratch or _sample_scratch
     if chunks > 1:
         scratch.ensure(rows, chunks, logits.device)
@@ -412,11 +423,30 @@ def _err_word_for(device) -> torch.Tensor:
     return _own_err_words[key]
 
 
-def skinny_gemm_takes(m: int, weight: torch.Tensor) -> bool:
-    """Whether the fused weight-streaming kernels take `m` token rows against `weight` [N, K] (bf16)."""
-    return (1 <= m <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0
-            and weight.stride(0) % 8 == 0 and weight.stride(1) == 1
-            and (16 + 8 * (2 if m > 8 else 1)) * (weight.shape[1] // 8 + 128) * 2 + 16384 < 200 * 1024)
+_skinny_answers: dict = {}
+
+
+def skinny_gemm_takes(m: int, weight: torch.Tensor, epilogue: int = EPI_PLAIN, norm: bool = False, *,
+                      ldx: Optional[int] = None, n_heads: int = 0, kv_heads: int = 0, head_dim: int = 0,
+                      rot_dim: int = 0) -> bool:
+    """Whether `skinny_gemm` runs `m` token rows against `weight` [N, K] with this epilogue and prologue. The answer
+    is the library's own (`qf_skinny_gemm_takes` runs the planning of the launch without launching), so a shape
+    that gets a yes here is never refused later. `ldx`: elements between input rows (default K); `rot_dim`: > 0 when
+    the QKV epilogue is to rotate that many components of each head."""
+    if not (weight.is_cuda and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1):
+        return False
+    n, k = weight.shape
+    key = (weight.device.index, int(m), n, k, weight.stride(0), epilogue, bool(norm), k if ldx is None else ldx,
+           n_heads, kv_heads, head_dim, rot_dim)
+    answer = _skinny_answers.get(key)
+    if answer is None:
+        with torch.cuda.device(weight.device):
+            answer = library("skinny_gemm").qf_skinny_gemm_takes(
+                _I(epilogue), _I(int(bool(norm))), _I(int(m)), _I(n), _I(k), _I(weight.stride(0)), _I(key[7]),
+                _I(n // 2 if epilogue == EPI_SWIGLU else 0), _I(n_heads), _I(kv_heads), _I(head_dim),
+                _I(1 if rot_dim > 0 else 0), _I(rot_dim)) != 0
+        _skinny_answers[key] = answer
+    return answer
 
 
 def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,

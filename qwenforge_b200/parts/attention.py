@@ -21,9 +21,6 @@ from .base import Mixer, TensorSpec
 from .registry import build_part, register_part
 
 
-SM_COUNT = 148  # streaming multiprocessors of a B200
-
-
 # Fewest new tokens of a step, by head size, from which the tcgen05 prefill attention runs instead of the mma.sync one.
 TC_PREFILL_MIN_TOKENS = {64: 4096, 128: 256}
 
@@ -135,7 +132,9 @@ class GqaAttention(Mixer):
         rotary = self.position.fused_rotary() if self.position is not None else None
         if self.position is not None and (rotary is None or rotary[1] != self.head_dim):
             return False
-        return (ops.skinny_gemm_takes(ctx.n_tokens, self.qkv_weight) and ops.skinny_gemm_takes(ctx.n_tokens, self.o_weight))
+        return (ops.skinny_gemm_takes(ctx.n_tokens, self.qkv_weight, ops.EPI_QKV, True, n_heads=self.n_heads,
+                                      kv_heads=self.n_kv, head_dim=self.head_dim, rot_dim=rotary[1] if rotary else 0)
+                and ops.skinny_gemm_takes(ctx.n_tokens, self.o_weight, ops.EPI_RESIDUAL, False))
 
     def fused_forward(self, hidden, rms, ctx, site, writes_cache):
         n = hidden.shape[0]
@@ -160,7 +159,7 @@ class GqaAttention(Mixer):
         warps = 8 if self.head_dim <= 64 else 4
         blocks = ctx.n_seqs * self.n_kv * (-(-(self.n_heads // self.n_kv) // 16))
         # measured on B200 (context 4096): batch 64 is fastest unsplit, batch 8 with 8 splits, batch 1 with 8 to 16
-        return max(1, min(-(-pages // warps), SM_COUNT // blocks, 64))
+        return max(1, min(-(-pages // warps), ops.sm_count(ctx.err.device) // blocks, 64))
 
 
 register_part("mixer", "gqa_attention", GqaAttention)

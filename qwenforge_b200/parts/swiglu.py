@@ -45,8 +45,8 @@ class SwiGlu(FeedForward):
     # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another
     def fused_takes(self, ctx) -> bool:
         return (ctx.dtype == torch.bfloat16 and ctx.attention == "auto" and self.inter % 8 == 0
-                and ops.skinny_gemm_takes(ctx.n_tokens, self.gate_up_weight)
-                and ops.skinny_gemm_takes(ctx.n_tokens, self.down_weight))
+                and ops.skinny_gemm_takes(ctx.n_tokens, self.gate_up_weight, ops.EPI_SWIGLU, True)
+                and ops.skinny_gemm_takes(ctx.n_tokens, self.down_weight, ops.EPI_RESIDUAL, False))
 
     def fused_forward(self, hidden, rms, ctx):
         act = torch.empty((hidden.shape[0], self.inter), dtype=torch.bfloat16, device=hidden.device)

@@ -335,6 +335,39 @@ def test_attention_prefill_padding_entry_and_refusal(ops):
         run_attention(ops, "attention_prefill", torch.bfloat16, 5, 1, 24, [4], [0], 0)
 
 
+@pytest.mark.parametrize("fn_name", ["attention_prefill", "attention_prefill_tc"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_prefill_far_key_and_window_edge(ops, fn_name, d):
+    """200 new rows continue a cache of 600 positions. One key is made to dominate every query's softmax, so each
+    row's output must be that key's value: far left of the diagonal without a window; with a window of 150 the key at
+    position 500 is the last one that row 649 sees and the first one that row 650 does not."""
+    nh, kvh, start, q_len = 2, 1, 600, 200
+    length = start + q_len
+    for window, far in ((0, 37), (150, 500)):
+        site = FakeSite(1, length, kvh, d, torch.bfloat16, 9)
+        fill_site(site, 0, length, 3, torch.bfloat16)
+        page, off = int(site.table[0, far // 64]), far % 64
+        site.storage[page, 0, 0, off] = 0
+        site.storage[page, 0, 0, off, 0] = 60.0
+        q = torch.zeros(q_len, nh * d, dtype=torch.bfloat16, device=DEV)
+        q[:, 0] = q[:, d] = 40.0
+        out = torch.full_like(q, 7.0)
+        cu = torch.tensor([0, q_len], dtype=torch.int32, device=DEV)
+        pos = torch.arange(start, length, dtype=torch.int32, device=DEV)
+        slots = torch.tensor([0], dtype=torch.int32, device=DEV)
+        e = err_word()
+        getattr(ops, fn_name)(q, out, cu, pos, slots, ops.KvSiteArgs(site.storage, site.table, kvh, d), nh, 1, q_len,
+                              d ** -0.5, window, e)
+        assert int(e) == 0
+        value = site.storage[page, 1, 0, off].float()
+        diff = (out.float().view(q_len, nh, d) - value).abs().amax(dim=(1, 2))   # per row
+        sees = (pos.cpu() - far < window) if window else torch.ones(q_len, dtype=torch.bool)
+        assert float(diff[sees.to(DEV)].max()) < 2e-2, f"{fn_name} d={d} window={window}: a row lost the dominant key"
+        if window:
+            assert int(sees.sum()) == 50 and float(diff[(~sees).to(DEV)].min()) > 0.1, \
+                f"{fn_name} d={d}: a row beyond the window's edge still sees the key"
+
+
 def run_decode(ops, nh, kvh, d, lengths, window, n_splits, slots=None, seed=12):
     n = len(lengths)
     slots = slots if slots is not None else list(range(n))[::-1]

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from tests import plain_qwen2 as plain
-from tests.helpers import TINY_A, TINY_W, assert_logits_close, make_model_dir, random_tokens
+from tests.helpers import TINY_A, TINY_B, TINY_W, assert_logits_close, make_model_dir, random_tokens
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -32,7 +32,7 @@ def read(out_dir, step, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("config", [TINY_A, TINY_W], ids=["tiny_a", "tiny_w"])
+@pytest.mark.parametrize("config", [TINY_A, TINY_B, TINY_W], ids=["tiny_a", "tiny_b", "tiny_w"])
 def test_three_ways_of_cutting(config, dtype, tmp_path):
     folder, weights = make_model_dir(config, 2, tmp_path / "model")
     vocab = config["vocab_size"]
