@@ -38,6 +38,10 @@ def parse():
     p.add_argument("--layers", type=int, default=None, help="run fewer layers than the preset has (both numbers are reported)")
     p.add_argument("--dtype", default="bfloat16")
     p.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
+    p.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                   help="run only this named workload (3B: 16 unequal prompts then 256 steps; 7B: batch 64 to context "
+                        "8192 at temperature 0.7) and print its line")
+    p.add_argument("--no-workloads", action="store_true", help="leave the 3B and 7B workloads out of the default run's points")
     return p.parse_args()
 
 
@@ -191,6 +195,95 @@ def check_decode_logits(model, cache, folder, batch, context, vocab, torch, rows
     return {"max_abs_diff_vs_fp32": round(worst, 5), "limit": round(bound, 5), "rows": rows_checked, "steps_replayed": CHUNK_STEPS}
 
 
+# The two larger workloads: 16 prompts of unequal lengths in ONE prompt step, then 256 decode steps, at Qwen2.5-3B layer
+# sizes; and batch 64 with 512-token prompts decoded to a context of 8,192 with temperature 0.7 at Qwen2.5-7B layer sizes.
+WORKLOADS = {
+    "3b": dict(preset="qwen2.5-3b", batch=16, prompt_range=(64, 2048), new_steps=256, temperature=0.0, seed=0),
+    "7b": dict(preset="qwen2.5-7b", batch=64, prompt_range=(512, 512), context=8192, temperature=0.7, seed=0),
+}
+
+
+def run_workload(name, pk, torch, layers=None, timed_last=256):
+    """One named workload with all of its layers (unless `layers` says otherwise), weights drawn on the device. All
+    prompts run in ONE step, then every decode step is replayed from one CUDA graph; the decode rate is that of ALL
+    the steps, and the last `timed_last` steps (the longest contexts) are also timed on their own."""
+    from qwenforge_b200.config import preset_config
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.engine.graphs import CHUNK_STEPS, DecodeGraph
+    from qwenforge_b200.sampling import Sampler, SamplingParams
+    w = WORKLOADS[name]
+    full = preset_config(w["preset"])
+    layers_run = layers or full.num_hidden_layers
+    config = preset_config(w["preset"], num_hidden_layers=layers_run)
+    numbers = model_numbers(config, layers_run)
+    batch = w["batch"]
+    g = torch.Generator().manual_seed(99)
+    lo, hi = w["prompt_range"]
+    lengths = [int(torch.randint(lo, hi + 1, (1,), generator=g)) for _ in range(batch)]
+    steps = w["new_steps"] if "new_steps" in w else w["context"] - max(lengths)
+    model = Model.from_random(config, w["seed"], "bfloat16", "cuda:0")
+    cache = model.new_cache(sum(-(-(n + steps) // 64) * 64 for n in lengths), batch, max(lengths) + steps)
+    sampler = Sampler(SamplingParams(w["temperature"], w["seed"]))
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
+    slots = [cache.open() for _ in range(batch)]
+    cache.reserve([(s, n + steps) for s, n in zip(slots, lengths)])
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    model.step(cache, [(-1, [1, 2, 3])], want=[[]])   # an untimed padding step: loads what a first step loads
+    torch.cuda.synchronize()
+    a, b = ev(), ev()
+    a.record()
+    logits = model.step(cache, list(zip(slots, prompts)))
+    b.record()
+    torch.cuda.synchronize()
+    prefill_ms = a.elapsed_time(b)
+    seq_ids = torch.arange(batch, dtype=torch.int64, device="cuda:0")
+    first = sampler(logits, seq_ids, torch.zeros(batch, dtype=torch.int32, device="cuda:0")).tolist()
+    cache.flush()
+    graph = DecodeGraph(model, cache, batch, max(lengths) + steps, sampler)
+    graph.capture()
+    graph.load(slots, first, lengths, [1] * batch, [1 << 30] * batch, list(range(batch)), [])
+    timed_last = min(timed_last, steps)
+    a, mid, b = ev(), ev(), ev()
+    with ClockSampler() as clocks:
+        a.record()
+        for i in range(steps):
+            if i % CHUNK_STEPS == 0:
+                graph.cursor.zero_()
+            if i == steps - timed_last:
+                mid.record()
+            graph.graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+    model.raise_on_kernel_error()
+    assert int(graph.tok_pos.max()) == max(lengths) + steps, "the decode steps did not reach the planned length"
+    ms_all, ms_last = a.elapsed_time(b) / steps, mid.elapsed_time(b) / timed_last
+    total_tokens = sum(lengths)
+    flops = numbers["linear_flops_per_token"] * total_tokens + numbers["head_flops_per_row"] * batch + sum(
+        numbers["attn_flops"](n) for n in lengths)
+    mean_len = sum(lengths) / batch
+    bytes_all = numbers["weight_bytes"] + batch * (mean_len + steps / 2) * numbers["kv_bytes_per_token"]
+    bytes_last = numbers["weight_bytes"] + batch * (mean_len + steps - timed_last / 2) * numbers["kv_bytes_per_token"]
+    gbs_all, gbs_last = bytes_all / (ms_all * 1e-3) / 1e9, bytes_last / (ms_last * 1e-3) / 1e9
+    out = {
+        "workload": name, "model": w["preset"], "layers": layers_run, "layers_in_config": full.num_hidden_layers,
+        "batch": batch, "prompt_tokens": total_tokens, "prompt_len_min": min(lengths), "prompt_len_max": max(lengths),
+        "decode_steps": steps, "temperature": w["temperature"],
+        "tokens_per_s": round(batch * 1e3 / ms_all, 1), "ms_per_step": round(ms_all, 4),
+        "bytes_per_step": int(bytes_all), "gbs": round(gbs_all, 1), "roofline_frac": round(gbs_all / pk["hbm_gbs"], 4),
+        "last_steps": timed_last, "last_ms_per_step": round(ms_last, 4), "last_tokens_per_s": round(batch * 1e3 / ms_last, 1),
+        "last_roofline_frac": round(gbs_last / pk["hbm_gbs"], 4),
+        "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(total_tokens / prefill_ms * 1e3, 1),
+        "prefill_frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+        "prefill_how": "ONE step of all prompts, seen for the first time (launch by launch)",
+        "kernels_per_step": graph.kernels_per_step, "clocks": clocks.summary(),
+    }
+    for s in slots:
+        cache.close(s)
+    del graph, cache, model
+    torch.cuda.empty_cache()
+    return out
+
+
 class _StubTokenizer:
     """Stands where the reference loads a tokenizer (there are no tokenizer files and no network): a prompt is the text
     "<length> <seed>" and encodes to that many seeded uniform-random token ids; ids decode to their decimal text."""
@@ -315,6 +408,23 @@ def main():
     from qwenforge_b200.weights import write_random_model
 
     pk = peaks()
+    if args.workload:
+        with torch.inference_mode():
+            out = run_workload(args.workload, pk, torch, args.layers)
+        line = {"metric": "decode tokens/s (%s workload: batch %d, %d steps)" % (args.workload, out["batch"], out["decode_steps"]),
+                "value": out["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": out["decode_steps"], "warmup": 0,
+                "ms_per_step": out["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, weights drawn on the device)",
+                "config": {k: out[k] for k in ("model", "layers", "layers_in_config", "batch", "prompt_tokens",
+                                               "prompt_len_min", "prompt_len_max", "decode_steps", "temperature")},
+                "clocks": out.pop("clocks"), "gpu_launches": out["kernels_per_step"] * out["decode_steps"],
+                "roofline": {"bound": "hbm", "achieved": out["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": out["roofline_frac"], "peaks": pk["source"]},
+                "prefill": {"value": out["prefill_tokens_per_s"], "tokens": out["prompt_tokens"], "ms": out["prefill_ms"],
+                            "frac": out["prefill_frac"], "how": out["prefill_how"]},
+                "workload": out}
+        print(json.dumps(line))
+        return 0
     full = preset_config(args.preset)
     layers_cfg = full.num_hidden_layers
     layers_run = args.layers or layers_cfg
@@ -401,6 +511,14 @@ def main():
                    "d2h_bytes_per_step": round(chunks * (4 * 32 * batch + 4) / max(loop.steps_run, 1), 2),
                    "note": "StudentEngine.generate_ids: host token ids in, host token ids out; decode replays CUDA "
                            "graphs and reads tokens back every 32 steps"}
+
+    if not args.no_points and not args.no_workloads and args.layers is None:
+        with torch.inference_mode():
+            for name in sorted(WORKLOADS):
+                out = run_workload(name, pk, torch)
+                for key in ("tokens_per_s", "ms_per_step", "roofline_frac", "last_ms_per_step", "last_roofline_frac",
+                            "prefill_ms", "prefill_frac"):
+                    points[f"w{name}_{key}"] = out[key]
 
     line = {
         "metric": "decode tokens/s (batch %d, context %d)" % (batch, context), "value": round(value, 1), "unit": "tokens/s",

@@ -73,8 +73,7 @@ class KvGroup:
         self.storage = torch.zeros((len(self.entries), n_pages, 2, need.kv_heads, PAGE_TOKENS, need.head_dim),
                                    dtype=dtype, device=device)
         self.table = torch.full((n_slots, pages_per_seq), -1, dtype=torch.int32, device=device)
-        self._host_table = torch.full((n_slots, pages_per_seq), -1, dtype=torch.int32,
-                                      pin_memory=torch.device(device).type == "cuda")
+        self._host_table = torch.full((n_slots, pages_per_seq), -1, dtype=torch.int32)
         self._held: list[dict[int, int]] = [dict() for _ in range(n_slots)]  # slot -> {logical page: page id}
         self._dirty: set[int] = set()
 
@@ -132,7 +131,9 @@ class KvGroup:
         self._dirty.clear()
         if len(rows) == 1 or rows[-1] - rows[0] + 1 == len(rows):
             lo, hi = rows[0], rows[-1] + 1
-            self.table[lo:hi].copy_(self._host_table[lo:hi], non_blocking=True)
+            # through a copy of the rows: `trim` and `release` may rewrite the host table as soon as this returns,
+            # and a copy from that pageable snapshot has left the host when the call returns
+            self.table[lo:hi].copy_(self._host_table[lo:hi].clone())
         else:
             index = torch.tensor(rows, dtype=torch.long)
             self.table.index_copy_(0, index.to(self.table.device), self._host_table[index].to(self.table.device))
@@ -275,6 +276,14 @@ class SequenceCache:
 
     def live_slots(self) -> list[int]:
         return [s for s in range(self.max_seqs) if self.slots.is_held(s)]
+
+    def read_bytes(self, lengths: Sequence[int]) -> int:
+        """Bytes of keys and values that one single-token step reads for sequences of these lengths."""
+        total = 0
+        for g in self.kv_groups:
+            per_token = len(g.entries) * 2 * g.need.kv_heads * g.need.head_dim * g.storage.element_size()
+            total += per_token * sum(min(n, g.need.window) if g.need.window > 0 else n for n in lengths)
+        return total
 
     def storage_bytes(self) -> int:
         total = sum(g.storage.numel() * g.storage.element_size() for g in self.kv_groups)

@@ -49,7 +49,7 @@ class Qwen2Config(ModelConfig):
     rms_norm_eps: float = 1e-6
     rope_theta: float = 10000.0
     max_position_embeddings: int = 32768
-    tie_word_embeddings: bool = False
+    tie_word_embeddings: Optional[bool] = False   # None: the key is absent; the files decide (student_engine.py:359)
     hidden_act: str = "silu"
     use_sliding_window: bool = False
     sliding_window: Optional[int] = None
@@ -90,7 +90,7 @@ class Qwen2Config(ModelConfig):
             rms_norm_eps=float(data.get("rms_norm_eps", 1e-6)),
             rope_theta=float(data.get("rope_theta", 10000.0)),
             max_position_embeddings=int(data.get("max_position_embeddings", 32768)),
-            tie_word_embeddings=bool(data.get("tie_word_embeddings", False)),
+            tie_word_embeddings=None if data.get("tie_word_embeddings") is None else bool(data["tie_word_embeddings"]),
             hidden_act=str(data.get("hidden_act", "silu")),
             use_sliding_window=bool(data.get("use_sliding_window", False)),
             sliding_window=None if data.get("sliding_window") is None else int(data["sliding_window"]),
@@ -169,8 +169,15 @@ class Qwen2Config(ModelConfig):
                 {"gate_weight": p + "mlp.gate_proj.weight", "up_weight": p + "mlp.up_proj.weight",
                  "down_weight": p + "mlp.down_proj.weight"},
             )
-            layers.append(LayerSpec("pre_norm", norm(p + "input_layernorm.weight"), mixer,
-                                    norm(p + "post_attention_layernorm.weight"), ffn))
+            layers.append(LayerSpec("pre_norm", {
+                "mixer_norm": norm(p + "input_layernorm.weight"), "mixer": mixer,
+                "feed_forward_norm": norm(p + "post_attention_layernorm.weight"), "feed_forward": ffn}))
+        if self.tie_word_embeddings:
+            head_tensors = {"weight": "model.embed_tokens.weight"}
+        elif self.tie_word_embeddings is None:   # config.json does not say: lm_head.weight if the files hold it
+            head_tensors = {"weight": "lm_head.weight", "weight_fallback": "model.embed_tokens.weight"}
+        else:
+            head_tensors = {"weight": "lm_head.weight"}
         spec = ModelSpec(
             architecture=self.architecture,
             vocab_size=self.vocab_size,
@@ -183,9 +190,12 @@ class Qwen2Config(ModelConfig):
             final_norm=norm("model.norm.weight"),
             head=PartSpec("linear_head",
                           {"vocab_size": self.vocab_size, "width": self.hidden_size,
-                           "tied": self.tie_word_embeddings},
-                          {"weight": "model.embed_tokens.weight" if self.tie_word_embeddings else "lm_head.weight"}),
+                           "tied": bool(self.tie_word_embeddings)},
+                          head_tensors),
             stop_token_ids=() if self.eos_token_id is None else (self.eos_token_id,),
+            # a tied model whose files also store the head: taken if it is the embedding table, as the reference
+            # takes it (student_engine.py:359)
+            redundant_tensors={"lm_head.weight": "model.embed_tokens.weight"} if self.tie_word_embeddings else {},
         )
         spec.validate()
         return spec

@@ -28,12 +28,21 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (`block`) of two norms, a mixer and a feed-forward."""
+    """One layer: an arrangement (`block`, the name of a registered block kind) over named part specs.
+
+    Which names there are, and which role each plays, is the block kind's business: `pre_norm` reads
+    `mixer_norm`, `mixer`, `feed_forward_norm` and `feed_forward`; an arrangement with post-norms, a parallel
+    residual or no feed-forward is another block kind with names of its own, and nothing else changes.
+    """
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    feed_forward_norm: PartSpec
-    feed_forward: PartSpec
+    parts: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def part(self, name: str) -> PartSpec:
+        try:
+            return self.parts[name]
+        except KeyError:
+            raise KeyError(f"layer spec of block {self.block!r} names no part {name!r}; it has "
+                           f"{', '.join(sorted(self.parts)) or 'none'}") from None
 
 
 @dataclass(frozen=True)
@@ -61,6 +70,9 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: tuple = ()
+    # tensor names that files may hold although no part asks for them, each with the wanted tensor it must
+    # equal (a stored copy of a shared table); a copy that differs is an error
+    redundant_tensors: Mapping[str, str] = field(default_factory=dict)
 
     def validate(self) -> None:
         if not self.schedule:

@@ -17,7 +17,7 @@ from ..cache import SequenceCache
 from ..config import ModelConfig, ModelSpec, load_config, resolve_dtype
 from ..csrc import prepare
 from ..parts import build_block, build_part
-from ..weights import load_weights
+from ..weights import load_weights, random_state_on_device
 from .step import StepContext, build_context, context_of, pack_step
 
 
@@ -56,6 +56,13 @@ class Model:
         """The tensors a model of this spec wants from its weight files (no device is touched)."""
         return Model(spec, torch.float32, "cpu").tensor_specs()
 
+    def step_weight_bytes(self) -> int:
+        """Bytes of weights that ONE step reads: every schedule entry's parts, the final norm and the head."""
+        def of(top):
+            return sum(t.numel() * t.element_size() for part in _walk(top) for t in part.step_weights())
+        total = of(self.embedding) + of(self.final_norm) + of(self.head)
+        return total + sum(of(self.blocks[entry.layer]) for entry in self.spec.schedule)
+
     def cache_needs(self) -> list:
         """Per schedule entry: what its mixer keeps per sequence; None when it reads another entry's cache."""
         return [None if e.cache_from is not None else self.blocks[e.layer].cache_need() for e in self.spec.schedule]
@@ -86,8 +93,18 @@ class Model:
         resolved = resolve_dtype(dtype, getattr(config, "torch_dtype", None))
         model = cls(config.model_spec(), resolved, device, attention)
         model.config = config
-        tensors = load_weights(model_dir, model.tensor_specs(), resolved, model.device)
+        tensors = load_weights(model_dir, model.tensor_specs(), resolved, model.device, model.spec.redundant_tensors)
         return model.bind(tensors)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int = 0, dtype="bfloat16", device="cuda", attention: str = "auto") -> "Model":
+        """A model of `config` whose weights are drawn on the device (no model folder): for measurements at sizes of
+        tens of GB. `write_random_model` + `from_dir` is the mode whose weights a plain implementation can read."""
+        resolved = resolve_dtype(dtype, getattr(config, "torch_dtype", None))
+        model = cls(config.model_spec(), resolved, device, attention)
+        model.config = config
+        ops.require_cuda(model.device, "the model")
+        return model.bind(random_state_on_device(model.tensor_specs(), seed, resolved, model.device))
 
     # ------------------------------------------------------------------ cache
     def new_cache(self, max_tokens: int, max_seqs: int = 256, max_len: Optional[int] = None) -> SequenceCache:
@@ -110,12 +127,14 @@ class Model:
         return self.head.forward(self.final_norm.forward(rows, None))
 
     def step(self, cache: SequenceCache, entries: Sequence[tuple[int, Sequence[int]]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+             want: Optional[Sequence[Sequence[int]]] = None, extras: Optional[dict] = None) -> Optional[torch.Tensor]:
         """One step of a batch.
 
         entries  (slot, next token ids) per sequence; slot -1 is a padding entry. Each sequence's tokens
                  continue at its own length in the cache; its keys/values (or state) are appended.
         want     per entry the places among its tokens whose logits are wanted; None = each entry's last.
+        extras   name -> per entry an array [tokens of the entry, ...]: side inputs for parts that read
+                 `ctx.extras[name]` (say, positions on several axes); laid out like the tokens, [T, ...].
         Returns float32 logits [wanted, vocab] in the order of the entries and of `want`.
         """
         if not self._bound:
@@ -138,7 +157,7 @@ class Model:
         cache.flush()
         step = pack_step(triples, want)
         logits, replayed = None, False
-        if self.prefill_graphs is not None and self.prefill_graphs.takes(step):
+        if self.prefill_graphs is not None and not extras and self.prefill_graphs.takes(step):
             before = self.prefill_graphs.replays
             logits = self.prefill_graphs.run(cache, step)
             replayed = self.prefill_graphs.replays > before
@@ -146,6 +165,13 @@ class Model:
             # from pageable memory the copy is complete when the call returns, so the host array may go
             dev = torch.from_numpy(step.packed).to(self.device)
             ctx = context_of(step, dev, self.err, self.dtype, self.attention, self.decode_scratch)
+            if extras:
+                ctx.extras = {}
+                for name, per_entry in extras.items():
+                    pieces = [torch.as_tensor(piece) for piece in per_entry]
+                    if [len(piece) for piece in pieces] != step.host_q_lens:
+                        raise ValueError(f"step: extra input {name!r} does not have one row per token of every entry")
+                    ctx.extras[name] = torch.cat(pieces).to(self.device)
             logits = self.forward(ctx, cache)
         for slot, tokens in entries:
             if slot >= 0:

@@ -31,6 +31,10 @@ class StepContext:
     dtype: torch.dtype
     attention: str = "auto"          # "auto": fastest kernel that takes the shape; "generic": the SIMT kernel
     decode_scratch: Optional[object] = None   # ops.DecodeScratch shared by the model's attention layers
+    # per-token side inputs named by whoever feeds the step, [T, ...] on the device: what a part needs beyond a
+    # token's index in its sequence (positions on several axes, token types). `tok_pos` stays the index that
+    # orders the cache and the causal mask.
+    extras: Optional[dict] = None
     # host copies, for parts that plan on the host (absent when a captured graph replays the step)
     host_slots: Optional[list] = None
     host_starts: Optional[list] = None

@@ -91,6 +91,9 @@ class GqaAttention(Mixer):
         if self.out_bias:
             self.o_bias_t = t("o_bias")
 
+    def step_weights(self):
+        return [t for t in (self.qkv_weight, self.qkv_bias_t, self.o_weight, self.o_bias_t) if t is not None]
+
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
         rotary = self.position.fused_rotary() if self.position is not None else None

@@ -46,11 +46,14 @@ class TensorSpec:
     keep  "compute": kept in the activation dtype (bfloat16, or float32 on the 32-bit path)
           "stored":  kept as the file stores it if that is a 32-bit float, else as "compute"
           "int32":   an integer table, kept as int32
+    fallback  another tensor name that stands in when the files do not hold `name` (a head that
+              shares the embedding table in files that say nothing about tying)
     """
     name: str
     shape: tuple
     init: str = "matrix"
     keep: str = "compute"
+    fallback: Optional[str] = None
 
 
 class Part:
@@ -79,6 +82,11 @@ class Part:
         pass
 
     def sub_parts(self) -> list["Part"]:
+        return []
+
+    def step_weights(self) -> list:
+        """The bound tensors that every step reads in full (for the measurement's byte counts); tables that a step
+        only gathers rows from are not among them."""
         return []
 
 

@@ -11,12 +11,14 @@ from .registry import build_part, register_part
 
 
 class PreNormBlock(Part):
+    """Reads the layer spec's parts `mixer_norm`, `mixer`, `feed_forward_norm`, `feed_forward`."""
+
     def __init__(self, layer_spec):
         self.kind = "pre_norm"
-        self.mixer_norm = build_part("norm", layer_spec.mixer_norm)
-        self.mixer = build_part("mixer", layer_spec.mixer)
-        self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward)
+        self.mixer_norm = build_part("norm", layer_spec.part("mixer_norm"))
+        self.mixer = build_part("mixer", layer_spec.part("mixer"))
+        self.feed_forward_norm = build_part("norm", layer_spec.part("feed_forward_norm"))
+        self.feed_forward = build_part("feed_forward", layer_spec.part("feed_forward"))
 
     def sub_parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]

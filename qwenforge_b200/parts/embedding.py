@@ -34,8 +34,9 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: vocab_size, width, tied. tensors: weight [vocab_size, width] (the embedding's tensor when tied).
-    Returns float32 logits in both precisions."""
+    """params: vocab_size, width, tied. tensors: weight [vocab_size, width] (the embedding's tensor when tied), and
+    optionally weight_fallback: the tensor that serves when the files hold no `weight` (the reference takes the
+    embedding table whenever lm_head.weight is absent, student_engine.py:359). Returns float32 logits in both precisions."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -44,13 +45,17 @@ class LinearHead(Part):
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.file_name("weight"), (self.vocab, self.width))]
+        return [TensorSpec(self.file_name("weight"), (self.vocab, self.width),
+                           fallback=self.spec.tensors.get("weight_fallback"))]
 
     def kernel_libraries(self, dtype):
         return {"gemm_f32"} if dtype == torch.float32 else set()
 
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.file_name("weight")]
+
+    def step_weights(self):
+        return [self.weight]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self.weight, None, out_dtype=torch.float32)

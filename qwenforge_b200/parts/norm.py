@@ -39,5 +39,8 @@ class RmsNorm(Norm):
     def fused_rms(self):
         return self.weight, self.eps
 
+    def step_weights(self):
+        return [self.weight]
+
 
 register_part("norm", "rms_norm", RmsNorm)

@@ -27,7 +27,7 @@ def registered_parts(role: str) -> list[str]:
 
 
 def build_block(layer_spec):
-    """The arrangement named by `layer_spec.block`, built over the layer's four part specs."""
+    """The arrangement named by `layer_spec.block`, built over the layer's named part specs."""
     kinds = _REGISTRY["block"]
     if layer_spec.block not in kinds:
         raise ValueError(f"no block of kind {layer_spec.block!r} is registered; known: {', '.join(sorted(kinds)) or 'none'}")

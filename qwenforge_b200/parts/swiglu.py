@@ -33,6 +33,9 @@ class SwiGlu(FeedForward):
                                         dim=0).contiguous()
         self.down_weight = tensors[self.file_name("down_weight")]
 
+    def step_weights(self):
+        return [self.gate_up_weight, self.down_weight]
+
     def forward(self, x, ctx):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         if self.inter % 8 == 0 and ops.own_tensor_core_products(x, self.gate_up_weight):

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Iterable, Sequence
+from typing import Iterable, Mapping, Optional, Sequence
 
 import torch
 
@@ -77,8 +77,11 @@ def _list(items: Sequence[str], limit: int = 12) -> str:
     return shown + (f", ... ({len(items) - limit} more)" if len(items) > limit else "")
 
 
-def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, device) -> dict[str, torch.Tensor]:
+def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, device,
+                 redundant: Optional[Mapping[str, str]] = None) -> dict[str, torch.Tensor]:
+    """`redundant`: names the files may hold beyond the wanted ones, each mapped to the wanted tensor it must equal."""
     wanted = merge_specs(specs)
+    redundant = dict(redundant or {})
     files = [SafetensorsFile(p) for p in weight_files(model_dir)]
     try:
         where: dict[str, SafetensorsFile] = {}
@@ -88,12 +91,19 @@ def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, dev
                 if name in where:
                     duplicated.append(name)
                 where[name] = f
-        missing = sorted(n for n in wanted if n not in where)
-        unexpected = sorted(n for n in where if n not in wanted)
+        source = {n: (n if n in where or s.fallback not in where else s.fallback) for n, s in wanted.items()}
+        missing = sorted(n for n in wanted if source[n] not in where)
+        unexpected = sorted(n for n in where if n not in wanted and n not in redundant)
         wrong_shape, wrong_dtype = [], []
+        for extra, twin in redundant.items():
+            if extra in where and extra not in wanted and twin in where:
+                if where[extra].info(extra)[1] != where[twin].info(twin)[1] or not torch.equal(
+                        where[extra].tensor(extra), where[twin].tensor(twin)):
+                    wrong_shape.append(f"{extra}: the files hold it although the model shares {twin}, and it differs from that")
         for name, spec in wanted.items():
-            if name not in where:
+            if source[name] not in where:
                 continue
+            name = source[name]
             stored_dtype, shape = where[name].info(name)
             if tuple(shape) != tuple(spec.shape):
                 wrong_shape.append(f"{name}: file has {list(shape)}, model wants {list(spec.shape)}")
@@ -116,8 +126,12 @@ def load_weights(model_dir, specs: Iterable[TensorSpec], dtype: torch.dtype, dev
             raise WeightsError("\n".join(lines), missing, unexpected, wrong_shape, wrong_dtype, duplicated)
         out = {}
         for name, spec in wanted.items():
-            stored_dtype, _ = where[name].info(name)
-            out[name] = where[name].tensor(name).to(device=device, dtype=kept_dtype(spec, stored_dtype, dtype))
+            held = source[name]
+            if held != name and held in out:
+                out[name] = out[held]      # the stand-in is wanted under its own name too: one tensor on the device
+                continue
+            stored_dtype, _ = where[held].info(held)
+            out[name] = where[held].tensor(held).to(device=device, dtype=kept_dtype(spec, stored_dtype, dtype))
         return out
     finally:
         for f in files:

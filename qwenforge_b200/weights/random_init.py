@@ -35,6 +35,29 @@ def random_state(specs, seed: int, store_dtype: torch.dtype = torch.bfloat16) ->
     return {name: draw_tensor(spec, generator, store_dtype) for name, spec in merge_specs(specs).items()}
 
 
+def random_state_on_device(specs, seed: int, dtype: torch.dtype, device) -> dict[str, torch.Tensor]:
+    """The same distributions drawn on `device` by its own generator, tensor by tensor, straight into the kept
+    dtype: for measurements at sizes whose model file would take minutes to write and read (tens of GB). The values
+    are NOT those of `random_state` with the same seed; nothing that is compared with a model folder uses this."""
+    generator = torch.Generator(device=device).manual_seed(int(seed))
+    out = {}
+    for name, spec in merge_specs(specs).items():
+        if spec.keep == "int32":
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            continue
+        if spec.init not in ("norm", "matrix", "bias"):
+            raise ValueError(f"tensor {spec.name!r}: unknown init {spec.init!r}")
+        kept = torch.float32 if spec.keep == "stored" else dtype
+        value = torch.empty(spec.shape, dtype=kept, device=device)
+        flat = value.view(-1)
+        for begin in range(0, flat.numel(), 1 << 27):  # float32 draws of at most 512 MB at a time
+            noise = torch.randn(min(1 << 27, flat.numel() - begin), generator=generator, dtype=torch.float32, device=device)
+            noise = 1.0 + 0.1 * noise if spec.init == "norm" else 0.02 * noise
+            flat[begin:begin + noise.numel()] = noise.to(kept)
+        out[name] = value
+    return out
+
+
 def write_random_model(config: ModelConfig, seed: int, out_dir, store_dtype: torch.dtype = torch.bfloat16) -> Path:
     """Write `<out_dir>/config.json` and `<out_dir>/model.safetensors`; returns out_dir."""
     from ..engine.model import Model  # late import: the model needs the weights package

@@ -75,8 +75,8 @@ def test_load_config_from_folder(tmp_path):
 def test_spec_is_data():
     spec = config_from_dict(TINY_W).model_spec()
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    assert [layer.mixer.params["window"] for layer in spec.layers] == [0, 37, 37]
-    assert spec.layers[0].mixer.params["position"].params["theta"] == 50000.0
+    assert [layer.part("mixer").params["window"] for layer in spec.layers] == [0, 37, 37]
+    assert spec.layers[0].part("mixer").params["position"].params["theta"] == 50000.0
     assert spec.head.tensors["weight"] == "lm_head.weight"
     tied = config_from_dict(TINY_A).model_spec()
     assert tied.head.tensors["weight"] == tied.embedding.tensors["weight"]
@@ -94,7 +94,8 @@ def test_presets_cover_the_measured_sizes():
 def test_dtype_names():
     assert resolve_dtype("bf16") == torch.bfloat16 and resolve_dtype("float32") == torch.float32
     assert resolve_dtype("auto", "float32") == torch.float32 and resolve_dtype("auto", "float16") == torch.bfloat16
-    with pytest.raises(ValueError, match="float16"):
-        resolve_dtype("float16")
+    with pytest.warns(UserWarning, match="bfloat16"):   # the reference's default name is served by the 16-bit path there is
+        assert resolve_dtype("float16") == torch.bfloat16
+    assert resolve_dtype("auto", "float16") == torch.bfloat16
     with pytest.raises(ValueError, match="Unsupported dtype"):
         resolve_dtype("int8")

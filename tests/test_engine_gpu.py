@@ -213,6 +213,71 @@ def test_far_key_among_hundreds(folders, dtype, tmp_path):
     assert_logits_close(torch.cat(got), ref, dtype, "sharp attention over far keys")
 
 
+SMALL_64W = dict(SMALL_64, use_sliding_window=True, sliding_window=100, max_window_layers=1)
+# configuration, seed of the weights, seed of the tokens: chosen so that one token far back (or near the window's far
+# edge) moves the last logits by several times the tolerance once queries and keys are scaled by 3
+SHARP_CASES = {"small_64": (SMALL_64, 3, 18), "small_128": (SMALL_128, 4, 21), "small_64w": (SMALL_64W, 3, 22)}
+
+
+@pytest.mark.parametrize("tcgen05", [False, True], ids=["mma", "tcgen05"])
+@pytest.mark.parametrize("case", list(SHARP_CASES))
+def test_far_key_through_the_tensor_core_kernels(case, tcgen05, tmp_path, monkeypatch):
+    """The sharp-softmax test at the head sizes of the real models, in bfloat16: a 300-token prompt through the
+    tensor-core prefill attention (mma.sync, or tcgen05 when forced), continuations of 2 and of 60 tokens across a page
+    end (and, windowed, across the window's edge), single tokens through the fused decode kernels, and the last 20
+    from a captured decode graph over a cache whose windowed pages are given back meanwhile."""
+    import json
+
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.engine.graphs import DecodeGraph
+    from qwenforge_b200.parts import attention
+    from qwenforge_b200.sampling import Sampler
+    from qwenforge_b200.weights import save_safetensors
+    config, weight_seed, token_seed = SHARP_CASES[case]
+    weights = plain.random_weights(config, weight_seed)
+    for key in weights:
+        if "q_proj" in key or "k_proj" in key:
+            weights[key] = weights[key] * 3.0
+    n = 420
+    tokens = random_tokens(config["vocab_size"], n, token_seed)
+    ref = plain.forward_logits(config, weights, tokens)
+    bound = 2e-2 + 4e-2 * float(ref.abs().max())
+    first = n - 100 if config.get("use_sliding_window") else 0
+    sensitivity = 0.0
+    for far in range(first, first + 64, 2):
+        moved = list(tokens)
+        moved[far] = (moved[far] + 1) % config["vocab_size"]
+        sensitivity = max(sensitivity, float((plain.forward_logits(config, weights, moved)[-1] - ref[-1]).abs().max()))
+    assert sensitivity > 2.5 * bound, f"no far key matters enough ({sensitivity:.3e} vs {bound:.3e}) for this test to see a fault"
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    save_safetensors(tmp_path / "model.safetensors", weights)
+    if tcgen05:
+        monkeypatch.setattr(attention, "TC_PREFILL_MIN_TOKENS", {64: 1, 128: 1})
+    model = Model.from_dir(tmp_path, torch.bfloat16, "cuda")
+    cache = model.new_cache(1024, 2)
+    slot = cache.open()
+    cache.reserve([(slot, n)])
+    got = [model.step(cache, [(slot, tokens[:300])], want=[list(range(300))]),
+           model.step(cache, [(slot, tokens[300:302])], want=[[0, 1]]),
+           model.step(cache, [(slot, tokens[302:362])], want=[list(range(60))])]
+    for t in range(362, 400):
+        got.append(model.step(cache, [(slot, [tokens[t]])]))
+    graph = DecodeGraph(model, cache, 1, 512, Sampler())
+    cache.flush()
+    graph.capture()
+    for t in range(400, n):
+        cache.flush()   # a windowed group gave pages back at the last advance
+        graph.load([slot], [tokens[t]], [t], [1], [1 << 30], [0], [])
+        graph.run(1)
+        got.append(graph.last_logits.clone())
+        cache.advance(slot, 1)
+    model.raise_on_kernel_error()
+    if config.get("use_sliding_window"):
+        group = [g for g in cache.kv_groups if g.need.window > 0][0]
+        assert group.pages_held(slot) <= (100 + 63) // 64 + 1
+    assert_logits_close(torch.cat(got), ref, torch.bfloat16, f"{case}: sharp attention over far keys")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_greedy_generation_through_entry_point(folders, name, dtype):

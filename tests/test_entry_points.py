@@ -29,8 +29,9 @@ def test_cli_options_follow_the_reference():
     assert args.random_weights == "tiny-a" and args.timed_repeats == 3 and args.temperature == 0.7
     with pytest.raises(SystemExit):
         parse_args([])                       # neither --model nor --random-weights
-    with pytest.raises(SystemExit):
-        parse_args(["--model", "d", "--dtype", "float16"])
+    assert parse_args(["--model", "d", "--dtype", "float16"]).dtype == "float16"   # the reference's default name is taken
+    args = parse_args(["--model", "d", "--context", "4096", "--prompt-len-range", "64,2048", "--time-kernels"])
+    assert args.context == 4096 and args.prompt_len_range == "64,2048" and args.time_kernels
 
 
 def test_trace_run_arguments():

@@ -322,7 +322,8 @@ def register_toy_parts():
                                      {"q_weight": p + "q", "k_weight": p + "k", "v_weight": p + "v", "o_weight": p + "o"})
                 ffn = PartSpec("swiglu", {"hidden_size": self.width, "intermediate_size": 2 * self.width},
                                {"gate_weight": p + "ff.g", "up_weight": p + "ff.u", "down_weight": p + "ff.d"})
-                layers.append(LayerSpec("pre_norm", norm(p + "n1"), mixer, norm(p + "n2"), ffn))
+                layers.append(LayerSpec("pre_norm", {"mixer_norm": norm(p + "n1"), "mixer": mixer,
+                                                    "feed_forward_norm": norm(p + "n2"), "feed_forward": ffn}))
             return ModelSpec("ToyMixedForCausalLM", self.vocab_size, self.width, 4096,
                              PartSpec("token_embedding", {"vocab_size": self.vocab_size, "width": self.width}, {"weight": "emb"}),
                              tuple(layers), tuple(ScheduleEntry(i) for i in range(self.n_layers)), norm("final"),

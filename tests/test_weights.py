@@ -80,6 +80,31 @@ def test_tied_and_untied_heads(tmp_path):
         load_weights(folder_b, specs_of(TINY_B), torch.float32, "cpu")
 
 
+def test_a_stored_copy_of_a_tied_head_and_files_that_do_not_say(tmp_path):
+    """The reference takes lm_head.weight if the files hold it and the embedding table otherwise, whatever config.json
+    says (student_engine.py:359). Here a tied model accepts a stored head that IS the embedding table and refuses
+    one that differs; and a config.json without `tie_word_embeddings` lets the files decide."""
+    spec = config_from_dict(TINY_A).model_spec()
+    folder, weights = make_model_dir(TINY_A, 0, tmp_path)
+    save_safetensors(folder / "model.safetensors", dict(weights, **{"lm_head.weight": weights["model.embed_tokens.weight"].clone()}))
+    got = load_weights(folder, specs_of(TINY_A), torch.float32, "cpu", spec.redundant_tensors)
+    assert "lm_head.weight" not in got and torch.equal(got["model.embed_tokens.weight"], weights["model.embed_tokens.weight"])
+    save_safetensors(folder / "model.safetensors", dict(weights, **{"lm_head.weight": torch.zeros(256, 64)}))
+    with pytest.raises(WeightsError, match="lm_head.weight.*differs"):
+        load_weights(folder, specs_of(TINY_A), torch.float32, "cpu", spec.redundant_tensors)
+    # no tie_word_embeddings key at all
+    silent = {k: v for k, v in TINY_B.items() if k != "tie_word_embeddings"}
+    assert config_from_dict(silent).tie_word_embeddings is None
+    folder_b, weights_b = make_model_dir(silent, 1, tmp_path / "b")
+    with_head = load_weights(folder_b, specs_of(silent), torch.float32, "cpu")
+    assert torch.equal(with_head["lm_head.weight"], weights_b["lm_head.weight"])
+    del weights_b["lm_head.weight"]
+    save_safetensors(folder_b / "model.safetensors", weights_b)
+    without = load_weights(folder_b, specs_of(silent), torch.float32, "cpu")
+    assert torch.equal(without["lm_head.weight"], weights_b["model.embed_tokens.weight"])
+    assert without["lm_head.weight"] is without["model.embed_tokens.weight"]     # one tensor, not a second copy
+
+
 def test_shards_index_and_duplicates(tmp_path):
     _, weights = make_model_dir(TINY_A, 0, tmp_path / "whole")
     names = sorted(weights)
