@@ -41,6 +41,10 @@ class Model:
         self.err = None
         self.decode_scratch = None
         self.prefill_graphs = None  # engine.graphs.PrefillGraphs once enabled
+        # a callable (index, hidden, delta) that is shown the float32 residual stream after the embedding (index 0) and
+        # after every schedule entry (index k + 1); the stream's value there is hidden + delta when delta is pending.
+        # For diagnosis (trace_run --dump-layers); it reads, it must not write.
+        self.observer = None
         self._bound = False
 
     # ------------------------------------------------------------------ structure
@@ -116,10 +120,14 @@ class Model:
         """Run the schedule over the context's tokens; logits of ctx.want_rows (None if nothing is wanted)."""
         hidden = self.embedding.forward(ctx.token_ids, ctx)
         delta = None
+        if self.observer is not None:
+            self.observer(0, hidden, None)
         for index, entry in enumerate(self.spec.schedule):
             own = entry.cache_from is None
             site = cache.site(index if own else entry.cache_from)
             delta = self.blocks[entry.layer].forward(hidden, delta, ctx, site, own)
+            if self.observer is not None:
+                self.observer(index + 1, hidden, delta)
         if ctx.want_rows is None:
             return None
         rows = torch.empty((ctx.want_rows.numel(), hidden.shape[1]), dtype=torch.float32, device=hidden.device)

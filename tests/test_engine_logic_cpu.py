@@ -104,8 +104,21 @@ def test_replay_in_process(reference_kernels, tmp_path):
     out = tmp_path / "o"
     out.mkdir()
     said = []
-    replay(model, cache, io.StringIO("".join(json.dumps(s) + "\n" for s in steps)), out, report=said.append)
+    dumps = tmp_path / "layers"
+    dumps.mkdir()
+    replay(model, cache, io.StringIO("".join(json.dumps(s) + "\n" for s in steps)), out, report=said.append, dump_dir=dumps)
+    model.observer = None
     assert said == ["done 0", "done 1", "done 2"]
+    # the dumped residual stream of the last step (request c, whole): the embedding, then every layer's output
+    sizes = plain.read_sizes(config)
+    w64 = {k: v.double() for k, v in weights.items()}
+    h = w64["model.embed_tokens.weight"][torch.tensor(b)]
+    cos, sin = plain.rope_cos_sin(torch.arange(len(b)), sizes["head_dim"], sizes["theta"], torch.float64)
+    for k in range(sizes["layers"] + 1):
+        dumped = torch.from_numpy(np.fromfile(dumps / f"2.layer{k}.f32", dtype="<f4").reshape(len(b), -1).copy())
+        assert max_err(dumped, h) < 2e-6, f"residual stream after {k} layers"
+        if k < sizes["layers"]:
+            h = plain.decoder_layer(h, w64, k, sizes, cos, sin)
     ra, rb = plain.forward_logits(config, weights, a), plain.forward_logits(config, weights, b)
     read = lambda n: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 256).copy())
     assert max_err(read(0), ra[[0, 18]]) < 2e-6

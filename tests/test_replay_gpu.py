@@ -113,3 +113,47 @@ def test_command_line_runs_a_small_suite(tmp_path):
     rows = summary["results"]
     assert [r["suite"] for r in rows] == ["decode_throughput", "decode_throughput", "ttft_prefill"]
     assert rows[1]["batch_size"] == 3 and rows[1]["new_tokens"] == 3 * 12 and all(r["tokens_per_s"] > 0 for r in rows)
+
+
+def test_command_line_context_length_range_and_kernel_times(tmp_path):
+    peaks = tmp_path / "peaks.json"
+    peaks.write_text(json.dumps({"hbm_gbs": 6500.0}))
+    done = subprocess.run([sys.executable, "-m", "qwenforge_b200.cli", "--random-weights", "tiny-a", "--dtype", "bfloat16",
+                           "--suites", "decode_throughput", "--decode-batch-sizes", "4", "--prompt-len-range", "5,30",
+                           "--context", "48", "--time-kernels", "--peaks", str(peaks), "--output-dir", str(tmp_path / "out")],
+                          capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert done.returncode == 0, done.stderr[-2000:]
+    summary = json.loads((tmp_path / "out" / "summary.json").read_text())
+    row = summary["results"][0]
+    assert row["requests"] == 4 and 4 * (48 - 30) <= row["new_tokens"] <= 4 * (48 - 5)   # every request decoded to 48 tokens
+    assert row["bytes_per_step"] > 0 and row["decode_gbs"] > 0 and 0 < row["decode_roofline_frac"] < 1
+    assert row["peak_memory_bytes"] > 0
+    kernels = {k["kernel"] for k in summary["kernels"]}
+    assert any(k.startswith("linear[") for k in kernels) and "embed_gather" in kernels and "sample" in kernels
+    assert "kernel" in done.stdout and "us/call" in done.stdout
+
+
+def test_validate_program(tmp_path):
+    done = subprocess.run([sys.executable, "-m", "qwenforge_b200.validate", "--random-weights", "tiny-b", "--dtype", "float32"],
+                          capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert "Signature check passed." in done.stdout and "Runtime interface check passed." in done.stdout
+
+
+def test_dump_layers_of_trace_run(tmp_path):
+    folder, weights = make_model_dir(TINY_B, 2, tmp_path / "model")
+    tokens = random_tokens(TINY_B["vocab_size"], 9, 5)
+    text = json.dumps(dict(step=0, entries=[dict(id="a", tokens=tokens, want=[8])], end=["a"])) + "\n"
+    done = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32",
+                           "--out", str(tmp_path / "o"), "--max-tokens", "64", "--dump-layers", str(tmp_path / "layers")],
+                          input=text, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    sizes = plain.read_sizes(TINY_B)
+    w64 = {k: v.double() for k, v in weights.items()}
+    h = w64["model.embed_tokens.weight"][torch.tensor(tokens)]
+    cos, sin = plain.rope_cos_sin(torch.arange(len(tokens)), sizes["head_dim"], sizes["theta"], torch.float64)
+    for k in range(sizes["layers"] + 1):
+        data = np.fromfile(tmp_path / "layers" / f"0.layer{k}.f32", dtype="<f4").reshape(len(tokens), -1)
+        assert float((torch.from_numpy(data.copy()).double() - h).abs().max()) <= 2e-5 * max(1.0, float(h.abs().max()))
+        if k < sizes["layers"]:
+            h = plain.decoder_layer(h, w64, k, sizes, cos, sin)
