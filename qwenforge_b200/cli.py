@@ -123,9 +123,9 @@ def run_suite(engine, name, prompt_lens, batch_sizes, max_new, args, vocab, peak
             middle = [len(p) + len(t) / 2 for p, t in zip(prompts, out)]
             step_bytes = engine.model.step_weight_bytes() + engine.cache.read_bytes(middle) * live / len(prompts)
             gbs = step_bytes * loop.steps_run / loop.decode_seconds / 1e9
-            row.update(decode_steps=loop.steps_run, bytes_per_step=int(step_bytes), decode_gbs=round(gbs, 1))
+            row.update(decode_steps=loop.steps_run, bytes_per_step=int(step_bytes), decode_gbs=round(gbs, 3))
             if peaks and peaks.get("hbm_gbs"):
-                row["decode_roofline_frac"] = round(gbs / float(peaks["hbm_gbs"]), 4)
+                row["decode_roofline_frac"] = round(gbs / float(peaks["hbm_gbs"]), 6)
         rows.append(row)
         if args.verbose_batches or not args.output_dir:
             print(json.dumps(row), flush=True)
