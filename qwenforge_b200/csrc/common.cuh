@@ -18,6 +18,7 @@ typedef __nv_bfloat16 bf16;
 #define QF_ERR_NO_PAGE 2       // a position whose cache page is not allocated
 #define QF_ERR_ROW_RANGE 4     // a gathered row index outside the activations
 #define QF_ERR_COPY_TIMEOUT 8  // a bulk copy did not complete within the wait limit
+#define QF_ERR_BARRIER_TIMEOUT 16  // a barrier over the blocks of a persistent kernel was not reached within the wait limit
 
 template <typename T> struct Num;
 template <> struct Num<float> {

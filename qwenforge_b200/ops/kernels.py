@@ -24,12 +24,14 @@ ERR_TOKEN_RANGE = 1
 ERR_NO_PAGE = 2
 ERR_ROW_RANGE = 4
 ERR_COPY_TIMEOUT = 8
+ERR_BARRIER_TIMEOUT = 16
 
 _ERROR_TEXT = {
     ERR_TOKEN_RANGE: "a token id lies outside the embedding table",
     ERR_NO_PAGE: "a position was read or written whose cache page is not held by its sequence",
     ERR_ROW_RANGE: "a wanted row lies outside the step's tokens",
     ERR_COPY_TIMEOUT: "a bulk copy into shared memory did not complete within its wait limit",
+    ERR_BARRIER_TIMEOUT: "the blocks of a persistent kernel did not all reach a barrier within its wait limit",
 }
 
 
@@ -449,14 +451,12 @@ def skinny_gemm_takes(m: int, weight: torch.Tensor, epilogue: int = EPI_PLAIN, n
     return answer
 
 
-def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,
-                hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
-                bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None,
-                err: Optional[torch.Tensor] = None) -> None:
-    """One fused product for up to 16 token rows. Input rows are either `x` [m, K] bf16, or the float32 residual
-    stream `hidden` [m, K] normalised on the fly with `norm_weight`, `eps`. See csrc/skinny_gemm.cu for the epilogues.
-    qkv (EPI_QKV): dict(n_heads, site=KvSiteArgs, inv_freq, rot_dim, tok_pos, tok_seq, slots, q_out, write_cache, err)."""
+def _skinny_args(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,
+                 hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None, qkv: Optional[dict] = None,
+                 err: Optional[torch.Tensor] = None):
+    """Checks one fused product's tensors and fills the kernels' argument block; returns (block, norm flag)."""
     _dev("weight", weight, torch.bfloat16, contiguous=False)
     a = _SkinnyArgs()
     a.w, a.n, a.k, a.ldw = weight.data_ptr(), weight.shape[0], weight.shape[1], weight.stride(0)
@@ -507,11 +507,77 @@ def skinny_gemm(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor
         raise KernelError(f"skinny_gemm: unknown epilogue {epilogue}")
     if not a.err:
         a.err = (err if err is not None else _err_word_for(weight.device)).data_ptr()
+    return a, norm
+
+
+def skinny_gemm(epilogue: int, weight: torch.Tensor, **tensors) -> None:
+    """One fused product for up to 16 token rows. Input rows are either `x` [m, K] bf16, or the float32 residual
+    stream `hidden` [m, K] normalised on the fly with `norm_weight`, `eps`. Keywords: x | hidden, norm_weight, eps;
+    bias; out (PLAIN, SWIGLU); residual (RESIDUAL); err; see csrc/skinny_gemm.cu for the epilogues.
+    qkv (EPI_QKV): dict(n_heads, site=KvSiteArgs, inv_freq, rot_dim, tok_pos, tok_seq, slots, q_out, write_cache, err)."""
+    a, norm = _skinny_args(epilogue, weight, **tensors)
     code = library("skinny_gemm").qf_skinny_gemm(_I(epilogue), _I(int(norm)), ctypes.byref(a), _stream())
     if code == 1:  # cudaErrorInvalidValue: a shape the kernel does not take
         raise KernelError(f"skinny_gemm: shape m={a.m} n={a.n} k={a.k} (epilogue {epilogue}) is not supported; "
                           "use the unfused kernels")
     _check(code, "skinny_gemm")
+
+
+class FusedProduct:
+    """One fused product, described but not run: the epilogue, the weight and the keywords of `skinny_gemm`. Parts hand
+    these out so that whoever arranges them can run several as one chain (`skinny_chain`) or each alone (`run`)."""
+    __slots__ = ("epilogue", "weight", "tensors")
+
+    def __init__(self, epilogue: int, weight: torch.Tensor, **tensors):
+        self.epilogue, self.weight, self.tensors = epilogue, weight, tensors
+
+    def run(self) -> None:
+        skinny_gemm(self.epilogue, self.weight, **self.tensors)
+
+
+class _ChainProduct(ctypes.Structure):
+    _fields_ = [("epilogue", _I), ("norm", _I), ("a", _SkinnyArgs)]
+
+
+CHAIN_MAX_PRODUCTS = 4
+_chain_answers: dict = {}
+
+
+def _chain_array(products):
+    array = (_ChainProduct * len(products))()
+    for i, product in enumerate(products):
+        a, norm = _skinny_args(product.epilogue, product.weight, **product.tensors)
+        array[i].epilogue, array[i].norm, array[i].a = product.epilogue, int(norm), a
+    return array
+
+
+def skinny_chain_takes(products) -> bool:
+    """Whether `skinny_chain` runs these products as ONE persistent kernel (the library's own planning, launching nothing)."""
+    if not 1 <= len(products) <= CHAIN_MAX_PRODUCTS:
+        return False
+    key = tuple((p.epilogue, p.weight.shape, p.weight.stride(0), "hidden" in p.tensors,
+                 (p.tensors.get("hidden") if "hidden" in p.tensors else p.tensors["x"]).shape[0],
+                 p.tensors["x"].stride(0) if "x" in p.tensors else 0) for p in products) + (products[0].weight.device.index,)
+    answer = _chain_answers.get(key)
+    if answer is None:
+        with torch.cuda.device(products[0].weight.device):
+            answer = library("skinny_chain").qf_skinny_chain_takes(_I(len(products)), _chain_array(products)) != 0
+        _chain_answers[key] = answer
+    return answer
+
+
+def skinny_chain(products, sync: torch.Tensor, err: torch.Tensor) -> None:
+    """Runs up to four fused products, each reading what the one before wrote, as one persistent kernel whose blocks
+    stream the weights of all of them without a pause (csrc/skinny_chain.cu). `sync`: two int32 words, zero when first
+    used, that belong to this stream's chains."""
+    _dev("sync", sync, torch.int32)
+    _dev("err", err, torch.int32)
+    if sync.numel() < 2:
+        raise KernelError("skinny_chain: sync must hold two words")
+    code = library("skinny_chain").qf_skinny_chain(_I(len(products)), _chain_array(products), _ptr(sync), _ptr(err), _stream())
+    if code == 1:
+        raise KernelError("skinny_chain: these products do not fit the chain kernel; run them one by one")
+    _check(code, "skinny_chain")
 
 
 def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:

@@ -554,6 +554,87 @@ def test_skinny_gemm_refuses_what_it_does_not_take(ops):
     assert not ops.skinny_gemm_takes(17, torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV))
 
 
+def _layer_tail(ops, m, hidden_w, inter, nh, kvh, d, seed=50):
+    """The four products that follow a decode step's attention, as descriptions: output projection into the stream,
+    norm + gate/up + SwiGLU, down into the stream, norm + the next layer's QKV with rotation and cache write.
+    Returns (products, state) where state holds every tensor that a run changes."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *shape, scale=1.0: (torch.randn(*shape, generator=g) * scale)
+    stream = rnd(m, hidden_w).to(DEV)
+    attended = rnd(m, nh * d).to(torch.bfloat16).to(DEV)
+    o_w = rnd(hidden_w, nh * d, scale=0.05).to(torch.bfloat16).to(DEV)
+    gu_w = rnd(2 * inter, hidden_w, scale=0.05).to(torch.bfloat16).to(DEV)
+    down_w = rnd(hidden_w, inter, scale=0.05).to(torch.bfloat16).to(DEV)
+    qkv_w = rnd((nh + 2 * kvh) * d, hidden_w, scale=0.05).to(torch.bfloat16).to(DEV)
+    qkv_b = rnd((nh + 2 * kvh) * d).to(torch.bfloat16).to(DEV)
+    n1 = (1 + 0.1 * rnd(hidden_w)).to(torch.bfloat16).to(DEV)
+    n2 = (1 + 0.1 * rnd(hidden_w)).to(torch.bfloat16).to(DEV)
+    site = FakeSite(m, 400, kvh, d, torch.bfloat16)
+    act = torch.zeros(m, inter, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.zeros(m, nh * d, dtype=torch.bfloat16, device=DEV)
+    tok_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([(37 * i + 63) % 390 for i in range(m)], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([(m - 1 - i) if i != 1 else -1 for i in range(m)], dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    e = err_word()
+    products = [
+        ops.FusedProduct(ops.EPI_RESIDUAL, o_w, x=attended, residual=stream),
+        ops.FusedProduct(ops.EPI_SWIGLU, gu_w, hidden=stream, norm_weight=n1, eps=1e-6, out=act),
+        ops.FusedProduct(ops.EPI_RESIDUAL, down_w, x=act, residual=stream),
+        ops.FusedProduct(ops.EPI_QKV, qkv_w, hidden=stream, norm_weight=n2, eps=1e-6, bias=qkv_b,
+                         qkv=dict(n_heads=nh, site=ops.KvSiteArgs(site.storage, site.table, kvh, d), inv_freq=inv_freq,
+                                  rot_dim=d, tok_pos=tok_pos, tok_seq=tok_seq, slots=slots, q_out=q_out, write_cache=True, err=e)),
+    ]
+    return products, dict(stream=stream, act=act, q_out=q_out, cache=site.storage, err=e)
+
+
+@pytest.mark.parametrize("m,hidden_w,inter,nh,kvh,d", [(8, 896, 4864, 14, 2, 64), (1, 896, 4864, 14, 2, 64),
+                                                      (3, 448, 608, 7, 1, 64), (5, 512, 736, 4, 2, 128),
+                                                      (12, 448, 608, 7, 1, 64), (8, 2048, 11008, 16, 2, 128)])
+def test_skinny_chain_equals_the_products_one_by_one(ops, m, hidden_w, inter, nh, kvh, d):
+    """A decoder layer's products after attention as ONE persistent kernel against the same four run as separate
+    kernels: the residual stream, the activations, the rotated queries and the cache pages. Twice over the same
+    barrier words, bit for bit the same."""
+    products, state = _layer_tail(ops, m, hidden_w, inter, nh, kvh, d)
+    start = {k: v.clone() for k, v in state.items()}
+    if not ops.skinny_chain_takes(products):
+        assert m > 8 or hidden_w > 1024, "the chain kernel must take the small shapes"
+        with pytest.raises(ops.KernelError, match="one by one"):
+            ops.skinny_chain(products, torch.zeros(2, dtype=torch.int32, device=DEV), state["err"])
+        return
+    for product in products:
+        product.run()
+    want = {k: v.clone() for k, v in state.items()}
+    assert int(state["err"]) == 0
+    sync = torch.zeros(2, dtype=torch.int32, device=DEV)
+    results = []
+    for _ in range(2):
+        for k, v in state.items():
+            v.copy_(start[k])
+        ops.skinny_chain(products, sync, state["err"])
+        torch.cuda.synchronize()
+        assert int(state["err"]) == 0
+        results.append({k: v.clone() for k, v in state.items()})
+    assert sync.tolist() == [0, 6]   # three barriers per launch, the arrival count back at zero
+    for k in ("stream", "act", "q_out", "cache"):
+        assert torch.equal(results[0][k], results[1][k]), k
+        scale = max(1.0, float(want[k].float().abs().max()))
+        assert max_err(results[0][k], want[k]) <= (2e-2 if want[k].dtype == torch.bfloat16 else 2e-3) * scale, k
+    assert float(results[0]["cache"].float().abs().sum()) > 0
+    # chains of one, two and three products
+    for n in (1, 2, 3):
+        for k, v in state.items():
+            v.copy_(start[k])
+        for product in products[:n]:
+            product.run()
+        want_n = state["stream"].clone(), state["act"].clone()
+        for k, v in state.items():
+            v.copy_(start[k])
+        ops.skinny_chain(products[:n], sync, state["err"])
+        assert max_err(state["stream"], want_n[0]) <= 2e-3 * max(1.0, float(want_n[0].abs().max()))
+        assert max_err(state["act"], want_n[1]) <= 2e-2 * max(1.0, float(want_n[1].float().abs().max()))
+
+
 def test_residual_add(ops):
     g = torch.Generator().manual_seed(23)
     h = torch.randn(5, 77, generator=g).to(DEV)
