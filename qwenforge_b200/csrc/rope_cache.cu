@@ -6,6 +6,11 @@
 // inv_freq == nullptr means no rotation at all (another position encoding did its work before).
 #include "common.cuh"
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <typename T>
 __global__ void rope_cache_kernel(const T* __restrict__ qkv, const T* __restrict__ bias, int qkv_stride, const int* __restrict__ tok_seq,
                                   const int* __restrict__ tok_pos, const int* __restrict__ slots,
@@ -78,6 +83,111 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, const T* __restrict
     }
 }
 
+// The same for bfloat16 with rows that 16-byte accesses can address (head size, rotated part and row stride
+// multiples of 8 elements when halved): a block takes RC_TOKENS tokens, a thread eight components at a time.
+#define RC_TOKENS 4
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bias, int qkv_stride, const int* __restrict__ tok_seq,
+                      const int* __restrict__ tok_pos, const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                      int rot_dim, int n_heads, bf16* __restrict__ q_out, KvSite<bf16> site, int write_cache, int n_tokens,
+                      int* err) {
+    const int D = site.head_dim, KVH = site.kv_heads;
+    const int half = rot_dim / 2, pass = D - rot_dim;
+    const int q_width = n_heads * D, kv_width = KVH * D;
+    const int t0 = blockIdx.x * RC_TOKENS, n_here = min(RC_TOKENS, n_tokens - t0);
+    __shared__ float sin_s[RC_TOKENS][128], cos_s[RC_TOKENS][128];
+    __shared__ int pos_s[RC_TOKENS];
+    __shared__ long long page_s[RC_TOKENS];  // element offset of the token's page in the cache, -1: nothing to write
+    if (threadIdx.x < n_here) {
+        const int t = t0 + threadIdx.x, pos = tok_pos[t], slot = slots[tok_seq[t]];
+        pos_s[threadIdx.x] = pos;
+        long long offset = -1;
+        if (write_cache && slot >= 0) {
+            const int page = site.table[(long long)slot * site.table_stride + pos / QF_PAGE];
+            if (page < 0) atomicOr(err, QF_ERR_NO_PAGE);
+            else offset = (long long)page * site.page_elems + (long long)(pos % QF_PAGE) * D;
+        }
+        page_s[threadIdx.x] = offset;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_here * half; i += blockDim.x) {
+        const int k = i / half, j = i % half;
+        sincosf((float)pos_s[k] * inv_freq[j], &sin_s[k][j], &cos_s[k][j]);
+    }
+    __syncthreads();
+    auto load8 = [&](const bf16* p, const bf16* b, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            v[2 * e] = f.x;
+            v[2 * e + 1] = f.y;
+        }
+        if (b) {
+            const uint4 braw = *reinterpret_cast<const uint4*>(b);
+            const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&braw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(bh[e]);
+                v[2 * e] += f.x;
+                v[2 * e + 1] += f.y;
+            }
+        }
+    };
+    auto store8 = [&](bf16* p, const float (&v)[8]) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+    };
+    // work items per token: groups of eight rotation pairs of q and k heads, then groups of eight components that pass
+    // through (the unrotated tail of q and k heads, and the values)
+    const int rot_groups = (n_heads + KVH) * (half / 8);
+    const int pass_groups = (n_heads + KVH) * (pass / 8) + kv_width / 8;
+    const int per_token = rot_groups + pass_groups;
+    for (int i = threadIdx.x; i < n_here * per_token; i += blockDim.x) {
+        const int k = i / per_token, item = i % per_token, t = t0 + k;
+        const bf16* row = qkv + (size_t)t * qkv_stride;
+        const long long cache_off = page_s[k];
+        if (item < rot_groups) {
+            const int head = item / (half / 8), j = (item % (half / 8)) * 8;
+            const bool is_q = head < n_heads;
+            const int src = is_q ? head * D : q_width + (head - n_heads) * D;
+            float x1[8], x2[8], o1[8], o2[8];
+            load8(row + src + j, bias ? bias + src + j : nullptr, x1);
+            load8(row + src + j + half, bias ? bias + src + j + half : nullptr, x2);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float s = sin_s[k][j + e], c = cos_s[k][j + e];
+                o1[e] = x1[e] * c - x2[e] * s;
+                o2[e] = x2[e] * c + x1[e] * s;
+            }
+            bf16* dst = nullptr;
+            if (is_q) dst = q_out + (size_t)t * q_width + head * D;
+            else if (cache_off >= 0) dst = site.base + cache_off + (long long)(head - n_heads) * QF_PAGE * D;
+            if (dst) {
+                store8(dst + j, o1);
+                store8(dst + j + half, o2);
+            }
+        } else {
+            int rest = item - rot_groups;
+            const int head_groups = (n_heads + KVH) * (pass / 8);
+            float v[8];
+            if (rest < head_groups) {
+                const int head = rest / (pass / 8), j = rot_dim + (rest % (pass / 8)) * 8;
+                const bool is_q = head < n_heads;
+                const int src = is_q ? head * D : q_width + (head - n_heads) * D;
+                load8(row + src + j, bias ? bias + src + j : nullptr, v);
+                if (is_q) store8(q_out + (size_t)t * q_width + head * D + j, v);
+                else if (cache_off >= 0) store8(site.base + cache_off + (long long)(head - n_heads) * QF_PAGE * D + j, v);
+            } else if (cache_off >= 0) {
+                rest -= head_groups;
+                const int c = rest * 8, src = q_width + kv_width + c;  // value component c of the token: head c / D
+                load8(row + src, bias ? bias + src : nullptr, v);
+                store8(site.base + cache_off + (long long)(KVH + c / D) * QF_PAGE * D + c % D, v);
+            }
+        }
+    }
+}
+
 template <typename T>
 static int launch(const void* qkv, const void* bias, int qkv_stride, const int* tok_seq, const int* tok_pos, const int* slots,
                   const float* inv_freq, int rot_dim, int n_heads, void* q_out, void* base, const int* table,
@@ -86,6 +196,13 @@ static int launch(const void* qkv, const void* bias, int qkv_stride, const int* 
     if (n_tokens <= 0) return 0;
     KvSite<T> site{(T*)base, table, page_elems, table_stride, kv_heads, head_dim};
     if (!inv_freq) rot_dim = 0;
+    if (sizeof(T) == 2 && head_dim % 16 == 0 && rot_dim % 16 == 0 && qkv_stride % 8 == 0 && head_dim <= 256 &&
+        ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)base | (uintptr_t)bias) % 16 == 0 && page_elems % 8 == 0) {
+        rope_cache_vec_kernel<<<(n_tokens + RC_TOKENS - 1) / RC_TOKENS, 256, 0, stream>>>(
+            (const bf16*)qkv, (const bf16*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
+            KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, n_tokens, err);
+        return (int)cudaGetLastError();
+    }
     rope_cache_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)qkv, (const T*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq,
                                                        rot_dim, n_heads, (T*)q_out, site, write_cache, err);
     return (int)cudaGetLastError();

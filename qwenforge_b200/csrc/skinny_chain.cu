@@ -38,7 +38,9 @@ struct ChainPhase {
 };
 
 struct ChainArgs {  // a kernel parameter: at most 4 KB
-    int n_phases, stages, x_bytes, pad;
+    int n_phases, stages, x_bytes;
+    int repeats;  // the products are run this many times over (weights, biases and norm weights advance by the strides below)
+    long long w_step[CH_MAX_PHASES], bias_step[CH_MAX_PHASES], norm_step[CH_MAX_PHASES];  // elements per repeat
     unsigned* sync;  // [0] arrivals at the running barrier, [1] generation (barriers completed since the words were zeroed)
     int* err;
     ChainPhase phase[CH_MAX_PHASES];
@@ -116,8 +118,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
         // ---- the fetching warp: every weight chunk this block will multiply, in the order in which it will; weights
         // are nobody's output, so nothing here waits for another kernel or another block
         int idx = 0;
+        for (int rep = 0; rep < c.repeats; ++rep)
         for (int p = 0; p < c.n_phases; ++p) {
             const ChainPhase& ph = c.phase[p];
+            const bf16* w_rep = ph.a.w + (size_t)rep * c.w_step[p];
             const int t0 = c.begin[p][block], n_mine = c.count[p][block];
             for (int tile = t0; tile < t0 + n_mine; ++tile) {
                 int ra, rb;
@@ -135,7 +139,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
                     if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * __popc(rows_mask));
                     __syncwarp();
                     if (grow >= 0)
-                        bulk_copy_g2s(stage + (size_t)lane * SK_STAGE_STRIDE, ph.a.w + (size_t)grow * ph.a.ldw + (size_t)ch * SK_CHUNK,
+                        bulk_copy_g2s(stage + (size_t)lane * SK_STAGE_STRIDE, w_rep + (size_t)grow * ph.a.ldw + (size_t)ch * SK_CHUNK,
                                       bytes, &full_bar[s]);
                 }
             }
@@ -150,17 +154,22 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
     const unsigned gen0 = gen_s;
     int idx = 0;
     bool dead = false;  // a wait ran out: reported; from then on nothing waits, so that the kernel still ends
+    for (int rep = 0; rep < c.repeats; ++rep)
     for (int p = 0; p < c.n_phases; ++p) {
         const ChainPhase& ph = c.phase[p];
-        const SkinnyArgs& a = ph.a;
+        SkinnyArgs a = ph.a;
+        a.w += (size_t)rep * c.w_step[p];
+        if (a.bias) a.bias += (size_t)rep * c.bias_step[p];
+        if (a.norm_w) a.norm_w += (size_t)rep * c.norm_step[p];
         const int t0 = c.begin[p][block], n_mine = c.count[p][block];
         if (n_mine == 0) continue;
-        if (p > 0) {
-            // everything the earlier products wrote: the barrier after product p - 1 is generation gen0 + p
+        const int ordinal = rep * c.n_phases + p;  // products run before this one
+        if (ordinal > 0) {
+            // everything the earlier products wrote: the barrier after the one before is generation gen0 + ordinal
             if (threadIdx.x == 0 && !dead) {
                 bool ok = false;
                 for (int i = 0; i < CH_BARRIER_TRIES; ++i) {
-                    if ((int)(load_acquire(c.sync + 1) - (gen0 + (unsigned)p)) >= 0) {
+                    if ((int)(load_acquire(c.sync + 1) - (gen0 + (unsigned)ordinal)) >= 0) {
                         ok = true;
                         break;
                     }
@@ -213,12 +222,22 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
                 if (lane == 0) ss_s[m] = ss;
             }
         } else {
-            const int pieces = a.k / 8;
-            for (int i = threadIdx.x; i < MP * pieces; i += SK_THREADS) {
-                const int m = i / pieces, col = (i % pieces) * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (m < a.m) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + col));
-                *reinterpret_cast<uint4*>(x_s + (size_t)m * stride_x + col * 2) = v;
+            // eight independent 16-byte loads per thread at a time: the rows come from L2, a round trip each
+            const int pieces = a.k / 8, total = MP * pieces;
+            for (int base = 0; base < total; base += SK_THREADS * 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = base + u * SK_THREADS + threadIdx.x;
+                    const int m = i / pieces, col = (i % pieces) * 8;
+                    v[u] = (i < total && m < a.m) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + col))
+                                                   : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = base + u * SK_THREADS + threadIdx.x;
+                    if (i < total) *reinterpret_cast<uint4*>(x_s + (size_t)(i / pieces) * stride_x + (i % pieces) * 16) = v[u];
+                }
             }
         }
         if (ph.epilogue == EPI_QKV && threadIdx.x < 16) {
@@ -268,20 +287,9 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
                 if (mine) {
                     const unsigned char* stage = ring + (size_t)s * CH_STAGE_BYTES;
                     const unsigned char* a_addr = stage + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * SK_STAGE_STRIDE + (lane >> 4) * 16;
-                    const unsigned char* x_base = x_s + (size_t)ch * SK_CHUNK * 2;
+                    const unsigned char* x_lane = x_lane_address(x_s + (size_t)ch * SK_CHUNK * 2, stride_x, lane, NT > 1);
                     const int kbs = min(SK_CHUNK / 32, n_kb - ch * (SK_CHUNK / 32));
-                    for (int kb = sub; kb < kbs; kb += gw) {
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {
-                            uint32_t af[4];
-                            ldmatrix_x4(af, a_addr + (kb * 32 + ks * 16) * 2);
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                const unsigned char* xr = x_base + (size_t)(8 * nt + g) * stride_x + (kb * 32 + ks * 16 + 2 * t) * 2;
-                                mma_bf16_16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(xr), *reinterpret_cast<const uint32_t*>(xr + 16));
-                            }
-                        }
-                    }
+                    for (int kb = sub; kb < kbs; kb += gw) mma_k_block<NT>(acc, a_addr, x_lane, stride_x, kb * 32);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -321,7 +329,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) skinny_chain_kernel(const __gri
             }
         }
         // ---- this block's part of product p is written: count it in (the last product has nobody waiting)
-        if (p + 1 < c.n_phases) {
+        if (ordinal + 1 < c.repeats * c.n_phases) {
             consumer_barrier();  // also keeps the token rows until every warp is done with them
             if (threadIdx.x == 0) {
                 __threadfence();
@@ -390,6 +398,8 @@ static bool plan_chain(const ChainProduct* products, int n, int sms, ChainArgs& 
     size_t stages = (most - x_bytes - red) / CH_STAGE_BYTES;
     if (stages > CH_MAX_STAGES) stages = CH_MAX_STAGES;
     c.n_phases = n;
+    c.repeats = 1;
+    for (int p = 0; p < CH_MAX_PHASES; ++p) c.w_step[p] = c.bias_step[p] = c.norm_step[p] = 0;
     c.stages = (int)stages;
     c.x_bytes = (int)x_bytes;
     smem = stages * CH_STAGE_BYTES + x_bytes + red;
@@ -450,6 +460,28 @@ QF_EXPORT int qf_skinny_chain(int n, const ChainProduct* products, unsigned* syn
     size_t smem = 0;
     const int sms = qf_sm_count();
     if (!plan_chain(products, n, sms, c, nt, smem)) return (int)cudaErrorInvalidValue;
+    c.sync = sync;
+    c.err = err;
+    const int blocks = sms < CH_MAX_BLOCKS ? sms : CH_MAX_BLOCKS;
+    return nt == 1 ? launch_chain<1>(c, blocks, smem, stream) : launch_chain<2>(c, blocks, smem, stream);
+}
+
+// The same chain run `repeats` times over in one launch, product p's weight, bias and norm weight advancing by
+// steps[p], steps[4 + p], steps[8 + p] elements per repeat (stacked tensors); every other tensor is shared by the
+// repeats. A measuring aid: how fast products follow one another once the blocks are resident and streaming.
+QF_EXPORT int qf_skinny_chain_repeated(int n, const ChainProduct* products, int repeats, const long long* steps, unsigned* sync,
+                                       int* err, cudaStream_t stream) {
+    static ChainArgs c;
+    int nt = 1;
+    size_t smem = 0;
+    const int sms = qf_sm_count();
+    if (repeats < 1 || !plan_chain(products, n, sms, c, nt, smem)) return (int)cudaErrorInvalidValue;
+    c.repeats = repeats;
+    for (int p = 0; p < n; ++p) {
+        c.w_step[p] = steps[p];
+        c.bias_step[p] = steps[4 + p];
+        c.norm_step[p] = steps[8 + p];
+    }
     c.sync = sync;
     c.err = err;
     const int blocks = sms < CH_MAX_BLOCKS ? sms : CH_MAX_BLOCKS;

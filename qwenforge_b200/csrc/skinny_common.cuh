@@ -89,13 +89,15 @@ __device__ __forceinline__ void skinny_epilogue_prefetch(const SkinnyArgs& a, in
 template <int NT, int EPI, bool NORM>
 __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, int tile, int g, int t, const float (&acc)[NT][4],
                                                 const EpiloguePre<NT>& pre, const float* ss_s, const float (*ss_part)[16],
-                                                int ksplit, const int* pos_s, const long long* dst_s) {
+                                                int ksplit, const int* pos_s, const long long* dst_s, int only_nt = -1) {
     int ra, rb;
     tile_rows<EPI>(a, tile, g, ra, rb);
     const float bias_a = pre.bias_a, bias_b = pre.bias_b, freq = pre.freq;
     // this lane holds, for token rows m = 8 nt + 2t + {0, 1}: acc[nt][0..1] of weight row ra, acc[nt][2..3] of row rb
+    // (`only_nt` >= 0: the caller holds the sums of that n-tile alone)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
+        if (only_nt >= 0 && nt != only_nt) continue;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int m = 8 * nt + 2 * t + e;
@@ -149,6 +151,39 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, int tile, i
     }
 }
 
+
+// One k-block (32 columns) of a 16-row weight tile against NT n-tiles of 8 token rows, both in shared memory with rows
+// a multiple of 128 bytes plus 16 apart (conflict-free ldmatrix). `a_lane` is this lane's ldmatrix address in the weight
+// tile at column 0: row (lane & 7) + 8 * ((lane >> 3) & 1), plus 16 bytes for lanes 16..31. `x_lane` is this lane's
+// address in the token rows at column 0 (`x_lane_address`): the token rows are read with ldmatrix as well, four 8 x 8
+// blocks (two n-tiles, two halves of k) per instruction.
+__device__ __forceinline__ const unsigned char* x_lane_address(const unsigned char* x_s, int x_stride, int lane, bool two_tiles) {
+    const int row = (lane & 7) + (two_tiles ? ((lane >> 4) << 3) : 0);
+    return x_s + (size_t)row * x_stride + ((lane >> 3) & 1) * 16;
+}
+
+template <int NT>
+__device__ __forceinline__ void mma_k_block(float (&acc)[NT][4], const unsigned char* a_lane, const unsigned char* x_lane,
+                                            int x_stride, int col) {
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        uint32_t af[4];
+        ldmatrix_x4(af, a_lane + (col + ks * 16) * 2);
+        if (NT == 1) {
+            uint32_t b[2];
+            ldmatrix_x2(b, x_lane + (col + ks * 16) * 2);
+            mma_bf16_16816(acc[0], af, b[0], b[1]);
+        } else {
+#pragma unroll
+            for (int p = 0; p < NT / 2; ++p) {
+                uint32_t b[4];
+                ldmatrix_x4(b, x_lane + (size_t)p * 16 * x_stride + (col + ks * 16) * 2);
+                mma_bf16_16816(acc[2 * p], af, b[0], b[1]);
+                mma_bf16_16816(acc[2 * p + 1], af, b[2], b[3]);
+            }
+        }
+    }
+}
 
 // The streaming kernels move K in chunks of SK_CHUNK columns through a ring of shared-memory stages.
 #define SK_CHUNK 1024  // columns of a chunk: one bulk copy per row and chunk (2 KB); smaller copies are bound by their issue

@@ -191,18 +191,8 @@ __global__ void __launch_bounds__(SK_THREADS, 3) skinny_gemm_kernel(const Skinny
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
     const unsigned char* w_tile = w_s + (size_t)tile_local * 16 * plan.stride_w;
     const unsigned char* a_addr = w_tile + (size_t)((lane & 7) + ((lane >> 3) & 1) * 8) * plan.stride_w + (lane >> 4) * 16;
-    for (int kb = sub; kb < kb_count; kb += wpt) {
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            uint32_t af[4];
-            ldmatrix_x4(af, a_addr + (kb * 32 + ks * 16) * 2);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const unsigned char* xr = x_s + (size_t)(8 * nt + g) * plan.stride_x + (kb * 32 + ks * 16 + 2 * t) * 2;
-                mma_bf16_16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(xr), *reinterpret_cast<const uint32_t*>(xr + 16));
-            }
-        }
-    }
+    const unsigned char* x_lane = x_lane_address(x_s, plan.stride_x, lane, NT > 1);
+    for (int kb = sub; kb < kb_count; kb += wpt) mma_k_block<NT>(acc, a_addr, x_lane, plan.stride_x, kb * 32);
     // ---- sum the warps of each tile in a fixed order, then the blocks of the cluster in rank order
     __syncthreads();  // every warp is done with this buffer's weights
 #pragma unroll
@@ -394,7 +384,7 @@ __global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(con
     bool dead = false;  // a wait ran out: reported; the warp goes on without waiting, so that every barrier is still met
     for (int tile = blockIdx.x; tile < tiles; tile += plan.nblk) {
         EpiloguePre<NT> pre;
-        if (warp == 0) skinny_epilogue_prefetch<NT, EPI>(a, tile, g, t, pre);
+        if (warp < NT) skinny_epilogue_prefetch<NT, EPI>(a, tile, g, t, pre);
         float acc[NT][4];
 #pragma unroll
         for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -409,30 +399,20 @@ __global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(con
             const unsigned char* x_base = XS ? stage + (size_t)16 * SK_STAGE_STRIDE : x_s + (size_t)c * SK_CHUNK * 2;
             const int x_stride = XS ? SK_STAGE_STRIDE : plan.stride_x;
             const int kbs = min(SK_CHUNK / 32, n_kb - c * (SK_CHUNK / 32));
-            for (int kb = warp; kb < kbs; kb += SK_WARPS) {
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks) {
-                    uint32_t af[4];
-                    ldmatrix_x4(af, a_addr + (kb * 32 + ks * 16) * 2);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const unsigned char* xr = x_base + (size_t)(8 * nt + g) * x_stride + (kb * 32 + ks * 16 + 2 * t) * 2;
-                        mma_bf16_16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(xr), *reinterpret_cast<const uint32_t*>(xr + 16));
-                    }
-                }
-            }
+            const unsigned char* x_lane = x_lane_address(x_base, x_stride, lane, NT > 1);
+            for (int kb = warp; kb < kbs; kb += SK_WARPS) mma_k_block<NT>(acc, a_addr, x_lane, x_stride, kb * 32);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);  // this warp is done with the stage
         }
-        // ---- the tile's sums: the warps' parts are added in warp order, then the first warp runs the epilogue
+        // ---- the tile's sums: warp w adds up the parts of n-tile w in warp order and runs that n-tile's epilogue
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) red[((size_t)warp * NT * 4 + nt * 4 + e) * 32 + lane] = acc[nt][e];
         consumer_barrier();
-        if (warp == 0) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
+            if (warp == nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float sum = 0.f;
@@ -440,9 +420,9 @@ __global__ void __launch_bounds__(SK_STREAM_THREADS, 1) skinny_stream_kernel(con
                     for (int w = 0; w < SK_WARPS; ++w) sum += red[((size_t)w * NT * 4 + nt * 4 + e) * 32 + lane];
                     acc[nt][e] = sum;
                 }
-        }
+            }
         consumer_barrier();  // the parts have been read: the next tile may overwrite them
-        if (warp == 0) skinny_epilogue<NT, EPI, NORM>(a, tile, g, t, acc, pre, ss_s, nullptr, 1, pos_s, dst_s);
+        if (warp < NT) skinny_epilogue<NT, EPI, NORM>(a, tile, g, t, acc, pre, ss_s, nullptr, 1, pos_s, dst_s, warp);
     }
 }
 

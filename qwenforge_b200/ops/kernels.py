@@ -580,6 +580,20 @@ def skinny_chain(products, sync: torch.Tensor, err: torch.Tensor) -> None:
     _check(code, "skinny_chain")
 
 
+def skinny_chain_repeated(products, repeats: int, steps, sync: torch.Tensor, err: torch.Tensor) -> None:
+    """A measuring aid: the chain run `repeats` times over inside ONE launch. steps: per product the elements by which
+    its weight, its bias and its norm weight advance per repeat (three lists; stacked tensors); all else is shared."""
+    flat = (ctypes.c_longlong * 12)(*([0] * 12))
+    for kind, values in enumerate(steps):
+        for i, value in enumerate(values):
+            flat[4 * kind + i] = int(value)
+    code = library("skinny_chain").qf_skinny_chain_repeated(_I(len(products)), _chain_array(products), _I(repeats), flat,
+                                                            _ptr(sync), _ptr(err), _stream())
+    if code == 1:
+        raise KernelError("skinny_chain: these products do not fit the chain kernel; run them one by one")
+    _check(code, "skinny_chain_repeated")
+
+
 def residual_add(hidden: torch.Tensor, delta: torch.Tensor) -> None:
     """hidden (float32) += delta, in place."""
     _dev("hidden", hidden, torch.float32)

@@ -16,6 +16,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 DTYPES = [torch.float32, torch.bfloat16]
 HEADS, KV_HEADS, HEAD_DIM = 4, 2, 16
+WEIGHT_SEED = 7   # of seeds 1..59 the one whose router decisions stay furthest from a tie (3.8e-3), found once on the CPU
 
 
 def register_toys():
@@ -172,9 +173,12 @@ def plain_two_axis(t, axes, theta):
 
 
 def plain_toy(cfg, w, tokens, axes, dtype):
+    """Logits [n, vocab] in float64 from `dtype`-rounded weights, and the smallest gap between the second and the third
+    router logit of any token (how far the choice of experts is from a tie)."""
     w = {k: (v if k.endswith("router") else v.to(dtype)).double() for k, v in w.items()}
     n = len(tokens)
     h = w["emb"][torch.tensor(tokens)]
+    closest = float("inf")
 
     def attend(x, p):
         q = plain_two_axis((x @ w[p + "q"].T).view(n, HEADS, HEAD_DIM).transpose(0, 1), axes, cfg.theta)
@@ -186,6 +190,8 @@ def plain_toy(cfg, w, tokens, axes, dtype):
         p = f"l{i}."
         if i % 2 == 0:
             x = plain.rms_norm(h, w[p + "n"], cfg.eps)
+            ranked = torch.sort(x @ w[p + "router"].T, dim=-1, descending=True).values
+            closest = min(closest, float((ranked[:, 1] - ranked[:, 2]).min()))
             top, chosen = torch.topk(x @ w[p + "router"].T, 2, dim=-1)
             gates = torch.softmax(top, dim=-1)
             routed = torch.zeros_like(h)
@@ -200,7 +206,7 @@ def plain_toy(cfg, w, tokens, axes, dtype):
             x = plain.rms_norm(h, w[p + "n2"], cfg.eps)
             g, u = x @ w[p + "g"].T, x @ w[p + "u"].T
             h = h + (g * torch.sigmoid(g) * u) @ w[p + "d"].T
-    return plain.rms_norm(h, w["final"], cfg.eps) @ w["head"].T
+    return plain.rms_norm(h, w["final"], cfg.eps) @ w["head"].T, closest
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -210,13 +216,9 @@ def test_routed_feed_forward_two_axis_positions_and_a_parallel_block(dtype, tmp_
     from qwenforge_b200.weights import SafetensorsFile, write_random_model
     ToyRoutedConfig = register_toys()
     cfg = ToyRoutedConfig(vocab_size=101, width=64, inner=24, experts=4, eps=1e-5, theta=100.0, n_layers=3)
-    write_random_model(cfg, 6, tmp_path, torch.float32)
+    write_random_model(cfg, WEIGHT_SEED, tmp_path, torch.float32)
     with SafetensorsFile(tmp_path / "model.safetensors") as f:
         weights = {n: f.tensor(n) for n in f.names()}
-    for i in (0, 2):   # routers that decide clearly: a near-tie between two experts would be a matter of rounding
-        weights[f"l{i}.router"] *= 40.0
-    from qwenforge_b200.weights import save_safetensors
-    save_safetensors(tmp_path / "model.safetensors", weights)
     assert weights["l0.router"].dtype == torch.float32 and "l0.e3.out" in weights and "l1.g" in weights
     model = Model.from_dir(tmp_path, dtype, DEV)
     assert not GraphDecoder.supported(model)   # the toys plan on the host: such a model steps, it does not replay graphs
@@ -224,7 +226,10 @@ def test_routed_feed_forward_two_axis_positions_and_a_parallel_block(dtype, tmp_
     g = torch.Generator().manual_seed(3)
     seqs = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (40, 7, 21)]
     axes = [torch.stack((torch.arange(len(s)) // 8, torch.arange(len(s)) % 8), dim=1).int() for s in seqs]   # rows of 8
-    refs = [plain_toy(cfg, weights, s, a, dtype) for s, a in zip(seqs, axes)]
+    refs, gaps = zip(*(plain_toy(cfg, weights, s, a, dtype) for s, a in zip(seqs, axes)))
+    # the seed is one under which no token's choice of experts is near a tie: which experts run is then not a matter of
+    # rounding, and the comparison sees the arithmetic
+    assert min(gaps) > 2e-3, f"a router decision is {min(gaps):.1e} from a tie: take another WEIGHT_SEED"
     bound = [(4e-5 if dtype == torch.float32 else 5e-2) * float(r.abs().max()) for r in refs]
     slots = [cache.open() for _ in seqs]
     logits = model.step(cache, list(zip(slots, seqs)), want=[list(range(len(s))) for s in seqs], extras={"axes": axes})
