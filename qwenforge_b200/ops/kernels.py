@@ -523,6 +523,47 @@ def skinny_gemm(epilogue: int, weight: torch.Tensor, **tensors) -> None:
     _check(code, "skinny_gemm")
 
 
+WIDE_MAX_ROWS = 64
+_wide_answers: dict = {}
+
+
+def wide_gemm_takes(epilogue: int, weight: torch.Tensor, **tensors) -> bool:
+    """Whether `wide_gemm` runs this product (up to 64 token rows `x`; the library's own planning, launching nothing)."""
+    x = tensors.get("x")
+    if x is None or not (weight.is_cuda and weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
+        return False
+    qkv = tensors.get("qkv") or {}
+    site = qkv.get("site")
+    key = (weight.device.index, epilogue, tuple(weight.shape), weight.stride(0), tuple(x.shape), x.stride(0),
+           weight.data_ptr() % 16, x.data_ptr() % 16, tensors.get("bias") is not None, qkv.get("n_heads"),
+           None if site is None else (site.kv_heads, site.head_dim), qkv.get("rot_dim"), qkv.get("inv_freq") is not None)
+    answer = _wide_answers.get(key)
+    if answer is None:
+        try:
+            a, _ = _skinny_args(epilogue, weight, **tensors)
+        except KernelError:
+            return False
+        with torch.cuda.device(weight.device):
+            answer = library("wide_gemm").qf_wide_gemm_takes(_I(epilogue), ctypes.byref(a)) != 0
+        _wide_answers[key] = answer
+    return answer
+
+
+def wide_gemm(epilogue: int, weight: torch.Tensor, **tensors) -> None:
+    """One fused product for up to 64 token rows on the tcgen05 tensor cores (csrc/wide_gemm.cu): the keywords of
+    `skinny_gemm`, with the input rows always given as `x` [m, K] bf16 (already normalised)."""
+    a, norm = _skinny_args(epilogue, weight, **tensors)
+    if norm:
+        raise KernelError("wide_gemm: the input rows must be given as x (normalise them first)")
+    code = library("wide_gemm").qf_wide_gemm(_I(epilogue), ctypes.byref(a), _stream())
+    if code == 1:
+        raise KernelError(f"wide_gemm: shape m={a.m} n={a.n} k={a.k} (epilogue {epilogue}) is not supported; "
+                          "use the unfused kernels")
+    if code == 801:
+        raise KernelError("wide_gemm: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
+    _check(code, "wide_gemm")
+
+
 class FusedProduct:
     """One fused product, described but not run: the epilogue, the weight and the keywords of `skinny_gemm`. Parts hand
     these out so that whoever arranges them can run several as one chain (`skinny_chain`) or each alone (`run`)."""

@@ -635,6 +635,101 @@ def test_skinny_chain_equals_the_products_one_by_one(ops, m, hidden_w, inter, nh
         assert max_err(state["act"], want_n[1]) <= 2e-2 * max(1.0, float(want_n[1].float().abs().max()))
 
 
+# ------------------------------------------------------------------------------------------------ wide fused products
+
+@pytest.mark.parametrize("m", [1, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(896, 896), (200, 72), (896, 4864), (1152, 2048), (130, 8)])
+def test_wide_gemm_plain_and_residual(ops, m, n, k):
+    """Up to 64 token rows against the weights on tcgen05: plain (bf16 and float32, with a bias) and into the residual
+    stream; K = 4864 against few tiles is split over a cluster."""
+    g = torch.Generator().manual_seed(60)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV)
+    want = x.double() @ w.double().T
+    scale = max(1.0, float(want.abs().max()))
+    e = err_word()
+    assert ops.wide_gemm_takes(ops.EPI_PLAIN, w, x=x, out=torch.empty(m, n, dtype=torch.float32, device=DEV))
+    for dtype, tolerance in ((torch.float32, 2e-3), (torch.bfloat16, 2e-2)):
+        out = torch.full((m, n), 7.0, dtype=dtype, device=DEV)
+        ops.wide_gemm(ops.EPI_PLAIN, w, x=x, bias=b, out=out, err=e)
+        assert int(e) == 0 and max_err(out, want + b.double()) <= tolerance * scale
+    hidden = torch.randn(m, n, generator=g).to(DEV)
+    before = hidden.clone()
+    ops.wide_gemm(ops.EPI_RESIDUAL, w, x=x, residual=hidden, err=e)
+    first = hidden.clone()
+    assert int(e) == 0 and max_err(hidden, before.double() + want) <= 2e-3 * scale
+    hidden.copy_(before)
+    ops.wide_gemm(ops.EPI_RESIDUAL, w, x=x, residual=hidden, err=e)
+    assert torch.equal(hidden, first)                       # the same sums in the same order, run after run
+    if m > 1:                                               # and a row's result does not depend on the rows beside it
+        alone = before[m - 1:].clone()
+        ops.wide_gemm(ops.EPI_RESIDUAL, w, x=x[m - 1:], residual=alone, err=e)
+        assert torch.equal(alone[0], first[m - 1])
+
+
+@pytest.mark.parametrize("m,inter,k", [(64, 4864, 896), (17, 200, 120), (40, 64, 64), (33, 11008, 2048)])
+def test_wide_gemm_swiglu(ops, m, inter, k):
+    g = torch.Generator().manual_seed(61)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * inter, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    out = torch.full((m, inter), 7.0, dtype=torch.bfloat16, device=DEV)
+    e = err_word()
+    ops.wide_gemm(ops.EPI_SWIGLU, w, x=x, out=out, err=e)
+    gu = x.double() @ w.double().T
+    want = gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]
+    assert int(e) == 0 and max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("m,nh,kvh,d,rotary,k", [(64, 14, 2, 64, True, 896), (17, 4, 4, 32, True, 248), (33, 8, 1, 128, False, 248),
+                                                 (20, 6, 3, 16, True, 96), (48, 28, 4, 128, True, 3584)])
+def test_wide_gemm_qkv(ops, m, nh, kvh, d, rotary, k):
+    """The fused projection + bias + rotation + cache write for up to 64 tokens against the unfused references."""
+    g = torch.Generator().manual_seed(62)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    n = (nh + 2 * kvh) * d
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    b = torch.randn(n, generator=g).to(torch.bfloat16).to(DEV)
+    site_a, site_b = FakeSite(m, 400, kvh, d, torch.bfloat16), FakeSite(m, 400, kvh, d, torch.bfloat16)
+    site_b.table = site_a.table
+    positions = [(37 * i + 63) % 390 for i in range(m)]
+    slots = [(m - 1 - i) if i != 1 else -1 for i in range(m)]
+    tok_seq = torch.arange(m, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV) if rotary else None
+    q1 = torch.full((m, nh * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    e = err_word()
+    ops.wide_gemm(ops.EPI_QKV, w, x=x, bias=b,
+                  qkv=dict(n_heads=nh, site=ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d), inv_freq=inv_freq,
+                           rot_dim=d if rotary else 0, tok_pos=tok_pos, tok_seq=tok_seq, slots=slots_t, q_out=q1,
+                           write_cache=True, err=e))
+    qkv = (x.double() @ w.double().T + b.double()).to(torch.float32)
+    q2 = torch.empty(m, nh * d, dtype=torch.float32, device=DEV)
+    site_b.storage = site_b.storage.float()
+    ref.rope_cache_write(qkv, tok_seq, tok_pos, slots_t, inv_freq, d if rotary else 0, nh, q2, site_b, True, None)
+    assert int(e) == 0
+    assert max_err(q1, q2) <= 3e-2 * max(1.0, float(q2.abs().max()))
+    assert max_err(site_a.storage, site_b.storage) <= 3e-2 * max(1.0, float(site_b.storage.abs().max()))
+    assert float(site_a.storage.float().abs().sum()) > 0
+
+
+def test_wide_gemm_refuses_what_it_does_not_take(ops):
+    w = torch.zeros(256, 64, dtype=torch.bfloat16, device=DEV)
+    x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)     # more than 64 token rows
+    out = torch.empty(65, 256, dtype=torch.bfloat16, device=DEV)
+    assert not ops.wide_gemm_takes(ops.EPI_PLAIN, w, x=x, out=out)
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.wide_gemm(ops.EPI_PLAIN, w, x=x, out=out)
+    w96 = torch.zeros(5 * 96, 64, dtype=torch.bfloat16, device=DEV)   # a head size that does not divide 128
+    site = FakeSite(4, 64, 1, 96, torch.bfloat16)
+    args = dict(x=x[:4], qkv=dict(n_heads=3, site=ops.KvSiteArgs(site.storage, site.table, 1, 96), inv_freq=None, rot_dim=0,
+                                  tok_pos=torch.zeros(4, dtype=torch.int32, device=DEV), tok_seq=torch.zeros(4, dtype=torch.int32, device=DEV),
+                                  slots=torch.zeros(1, dtype=torch.int32, device=DEV),
+                                  q_out=torch.empty(4, 3 * 96, dtype=torch.bfloat16, device=DEV), write_cache=False, err=err_word()))
+    assert not ops.wide_gemm_takes(ops.EPI_QKV, w96, **args)
+
+
 def test_residual_add(ops):
     g = torch.Generator().manual_seed(23)
     h = torch.randn(5, 77, generator=g).to(DEV)
