@@ -44,6 +44,8 @@ struct WideGeometry {
     int ksplit;      // blocks of a cluster sharing a tile
     int slabs;       // 64-column slabs of K
     int stage_bytes; // weights + token rows of one stage
+    int stages;      // depth of the ring
+    int pair_shift;  // log2 of the distance between the two tile rows an epilogue needs together
 };
 
 __device__ __forceinline__ void row_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(WG_ROW_THREADS) : "memory"); }
@@ -67,10 +69,10 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     // after the ring: what the epilogue exchanges (see below); the ring itself is free by then, but the partial sums of
     // other blocks of the cluster arrive while this block may still be multiplying, so they get room of their own
     unsigned char* ring = smem;
-    float* extra = reinterpret_cast<float*>(ring + (size_t)WG_STAGES * geo.stage_bytes);
+    float* extra = reinterpret_cast<float*>(ring + (size_t)geo.stages * geo.stage_bytes);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < WG_STAGES; ++s) {
+        for (int s = 0; s < geo.stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -88,7 +90,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     bool timed_out = false;
     float v[WG_MAX_TOK];  // row threads: this lane's sums, one per token row
     const int D = a.head_dim;
-    float* cs = extra;    // QKV: [tokens][D / 2] pairs (cos, sin) of every token's angles
+    float* sums = extra;                                        // [ksplit][ntok][rows owned]: the (partial) sums, token-major
+    float* cs = extra + (size_t)WG_BM * ntok;                   // QKV: [tokens][D / 2] pairs (cos, sin) of every token's angles
 
     // first weight row of the tile's two boxes of 64 rows
     int row0 = tile * WG_BM, row1 = row0 + 64;
@@ -109,7 +112,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             tma_load_2d(ring + (size_t)s * geo.stage_bytes + WG_W_BYTES, &x_map, kb * WG_BK, 0, &full_bar[s]);
         };
         // weights are nobody's output: those of the first stages are on their way before the kernel before this one ends
-        const int early = min(n_kb, WG_STAGES);
+        const int stages = geo.stages;
+        const int early = min(n_kb, stages);
         if (leader)
             for (int i = 0; i < early; ++i) {
                 mbar_expect_tx(&full_bar[i], (uint32_t)geo.stage_bytes);
@@ -121,8 +125,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             for (int i = 0; i < early; ++i) load_x(kb_begin + i, i);
         __syncwarp();
         for (int i = early; i < n_kb; ++i) {
-            const int s = i % WG_STAGES;
-            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / WG_STAGES) - 1) & 1))) {
+            const int s = i % stages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1))) {
                 timed_out = true;
                 break;
             }
@@ -138,8 +142,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         const bool leader = elect_one();
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ntok >> 3) << 17) | ((uint32_t)(WG_BM >> 4) << 24);
         for (int i = 0; i < n_kb; ++i) {
-            const int s = i % WG_STAGES;
-            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / WG_STAGES) & 1))) {
+            const int s = i % geo.stages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / geo.stages) & 1))) {
                 timed_out = true;
                 break;
             }
@@ -205,96 +209,96 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 for (int i = 0; i < 32; ++i) v[c0 + i] = 0.f;
             }
         }
-        if (EPI != EPI_QKV) grid_dependency_wait();  // the residual stream and the outputs belong to earlier kernels until now
-
-        if (ksplit > 1) {
-            // ---- K was split over the cluster (PLAIN and RESIDUAL only): block q owns rows [q * own, (q + 1) * own) of the
-            // tile; everyone sends it their partial sums of those rows
-            cg::cluster_group cluster = cg::this_cluster();
-            const int own = WG_BM / ksplit, q = r / own, r_local = r % own;
-            float* theirs = cluster.map_shared_rank(extra, q) + ((size_t)rank * own + r_local) * ntok;
+        // ---- every lane's sums go to the block that owns the lane's row (this block when K is not split), token-major,
+        // with the two rows of a pair side by side: tile row r -> pair index (r without its bit `pair_shift`), half
+        // (that bit). A pair is what an epilogue needs together: gate and up row, component j and j + D/2 of a head.
+        const int lp = geo.pair_shift, P = 1 << lp;
+        const int low = ((r >> (lp + 1)) << lp) | (r & (P - 1)), hi = (r >> lp) & 1;
+        const int pairs_per_rank = 64 / ksplit, own = 2 * pairs_per_rank;
+        const int q = low / pairs_per_rank, rl = 2 * (low % pairs_per_rank) + hi;
+        float* mine = (ksplit > 1 ? cg::this_cluster().map_shared_rank(sums, q) : sums) + ((size_t)rank * ntok) * own + rl;
 #pragma unroll
-            for (int m = 0; m < WG_MAX_TOK; ++m)
-                if (m < ntok) theirs[m] = v[m];
-        }
+        for (int m = 0; m < WG_MAX_TOK; ++m)
+            if (m < ntok) mine[(size_t)m * own] = v[m];
     }
-    if (ksplit > 1) cg::this_cluster().sync();  // every thread of every block of the cluster: the partial sums have arrived
+    if (ksplit > 1) cg::this_cluster().sync();  // every thread of every block of the cluster: all partial sums have arrived
+    else __syncthreads();
     if (warp < 4) {
-        const int r = threadIdx.x;
-        if (ksplit > 1) {
-            // the owner adds its rows' partial sums in rank order
-            const int own = WG_BM / ksplit;
-            for (int i = r; i < own * a.m; i += WG_ROW_THREADS) {
-                const int m = i / own, rl = i % own;
-                float sum = 0.f;
-                for (int src = 0; src < ksplit; ++src) sum += extra[((size_t)src * own + rl) * ntok + m];
-                const int n = tile * WG_BM + rank * own + rl;
-                if (n >= a.n) continue;
-                if (a.bias) sum += __bfloat162float(a.bias[n]);
-                if (EPI == EPI_RESIDUAL) a.residual[(size_t)m * a.n + n] += sum;
-                else if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n] = sum;
-                else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(sum);
-            }
-        } else if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL) {
-            const int n = tile * WG_BM + r;
-            if (n < a.n) {
-                const float bias = a.bias ? __bfloat162float(a.bias[n]) : 0.f;
+        // ---- the owner's epilogue: element (pair p, token m) per thread and turn, pairs fastest, so that the threads of a
+        // warp write neighbouring features of one token
+        if (EPI != EPI_QKV) grid_dependency_wait();  // the residual stream and the outputs belong to earlier kernels until now
+        const int lp = geo.pair_shift, P = 1 << lp;
+        const int pairs_per_rank = 64 / ksplit, own = 2 * pairs_per_rank;
+        const int total = pairs_per_rank * a.m;
+        constexpr int BATCH = 4;
+        for (int e0 = threadIdx.x; e0 < total; e0 += WG_ROW_THREADS * BATCH) {
+            float lo[BATCH], up[BATCH], res_lo[BATCH], res_hi[BATCH];
+            int n_lo[BATCH], tok[BATCH];
 #pragma unroll
-                for (int m = 0; m < WG_MAX_TOK; ++m) {
-                    if (m >= a.m) break;
-                    const float value = v[m] + bias;
-                    if (EPI == EPI_RESIDUAL) a.residual[(size_t)m * a.n + n] += value;
-                    else if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)m * a.ldo + n] = value;
-                    else reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(value);
+            for (int b = 0; b < BATCH; ++b) {
+                const int e = e0 + b * WG_ROW_THREADS;
+                const bool live = e < total;
+                const int p_local = live ? e % pairs_per_rank : 0, m = live ? e / pairs_per_rank : 0;
+                const int low = rank * pairs_per_rank + p_local;
+                const int r_lo = ((low >> lp) << (lp + 1)) | (low & (P - 1));  // the pair's first tile row; the second is P further
+                float x0 = 0.f, x1 = 0.f;
+                for (int src = 0; src < ksplit; ++src) {
+                    const float2 part = *reinterpret_cast<const float2*>(sums + ((size_t)src * ntok + m) * own + 2 * p_local);
+                    x0 += part.x;
+                    x1 += part.y;
+                }
+                lo[b] = x0;
+                up[b] = x1;
+                tok[b] = live ? m : -1;
+                n_lo[b] = EPI == EPI_SWIGLU ? tile * 64 + r_lo : tile * WG_BM + r_lo;  // SWIGLU: index into the intermediate width
+                if (EPI == EPI_RESIDUAL) {
+                    const bool in_lo = live && n_lo[b] < a.n, in_hi = live && n_lo[b] + P < a.n;
+                    res_lo[b] = in_lo ? __ldcg(a.residual + (size_t)m * a.n + n_lo[b]) : 0.f;
+                    res_hi[b] = in_hi ? __ldcg(a.residual + (size_t)m * a.n + n_lo[b] + P) : 0.f;
                 }
             }
-        } else if (EPI == EPI_SWIGLU) {
-            // lanes 64..127 hold the up rows: they pass their sums to the gate rows' threads
-            float* up = extra;  // [64][ntok + 1]
-            if (r >= 64) {
 #pragma unroll
-                for (int m = 0; m < WG_MAX_TOK; ++m)
-                    if (m < ntok) up[(size_t)(r - 64) * (ntok + 1) + m] = v[m];
-            }
-            row_barrier();
-            const int i = tile * 64 + r;
-            if (r < 64 && i < a.inter) {
-#pragma unroll
-                for (int m = 0; m < WG_MAX_TOK; ++m) {
-                    if (m >= a.m) break;
-                    const float gate = v[m], u = up[(size_t)r * (ntok + 1) + m];
-                    reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + i] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * u);
+            for (int b = 0; b < BATCH; ++b) {
+                const int m = tok[b], n0 = n_lo[b];
+                if (m < 0) continue;
+                if (EPI == EPI_SWIGLU) {
+                    if (n0 < a.inter)
+                        reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0] = __float2bfloat16_rn(lo[b] / (1.0f + expf(-lo[b])) * up[b]);
+                    continue;
                 }
-            }
-        } else {  // EPI_QKV
-            // row n of the projection is component j of head n / D; its rotation partner j +- D/2 lies in the same tile,
-            // D/2 lanes away: all sums (bias added) cross through shared memory
-            float* all = extra + 2 * (size_t)WG_MAX_TOK * (D / 2);  // [128][ntok + 1], behind the sines and cosines
-            const int n = tile * WG_BM + r;
-            const bool exists = n < a.n;
-            const float bias = (a.bias && exists) ? __bfloat162float(a.bias[n]) : 0.f;
-#pragma unroll
-            for (int m = 0; m < WG_MAX_TOK; ++m)
-                if (m < ntok) all[(size_t)r * (ntok + 1) + m] = v[m] + bias;
-            row_barrier();
-            if (exists) {
-                const int head = n / D, j = n % D, half = D / 2;
-                const bool rotated = a.inv_freq != nullptr && head < a.n_heads + a.kv_heads;
-                const bool low = j < half;
-                const float* partner = all + (size_t)(low ? r + half : r - half) * (ntok + 1);
-#pragma unroll
-                for (int m = 0; m < WG_MAX_TOK; ++m) {
-                    if (m >= a.m) break;
-                    float value = v[m] + bias;
-                    if (rotated) {
-                        const float c = cs[2 * (m * half + (low ? j : j - half))], s = cs[2 * (m * half + (low ? j : j - half)) + 1];
-                        const float other = partner[m];
-                        value = low ? value * c - other * s : value * c + other * s;
+                const int n1 = n0 + P;
+                float x0 = lo[b], x1 = up[b];
+                if (a.bias) {
+                    if (n0 < a.n) x0 += __bfloat162float(a.bias[n0]);
+                    if (n1 < a.n) x1 += __bfloat162float(a.bias[n1]);
+                }
+                if (EPI == EPI_RESIDUAL) {
+                    if (n0 < a.n) a.residual[(size_t)m * a.n + n0] = res_lo[b] + x0;
+                    if (n1 < a.n) a.residual[(size_t)m * a.n + n1] = res_hi[b] + x1;
+                } else if (EPI == EPI_PLAIN) {
+                    if (a.out_f32) {
+                        float* o = reinterpret_cast<float*>(a.out) + (size_t)m * a.ldo;
+                        if (n0 < a.n) o[n0] = x0;
+                        if (n1 < a.n) o[n1] = x1;
+                    } else {
+                        bf16* o = reinterpret_cast<bf16*>(a.out) + (size_t)m * a.ldo;
+                        if (n0 < a.n) o[n0] = __float2bfloat16_rn(x0);
+                        if (n1 < a.n) o[n1] = __float2bfloat16_rn(x1);
                     }
-                    if (head < a.n_heads) {
-                        a.q_out[(size_t)m * a.n_heads * D + (size_t)head * D + j] = __float2bfloat16_rn(value);
-                    } else if (dst_s[m] >= 0) {  // keys are heads n_heads .., values follow: [2][kv_heads] planes of a page
-                        a.kv_base[dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D + j] = __float2bfloat16_rn(value);
+                } else if (n0 < a.n) {  // EPI_QKV: n0 is component j < D/2 of head n0 / D, n1 its partner j + D/2
+                    const int head = n0 / D, j = n0 % D, half = D / 2;
+                    if (a.inv_freq != nullptr && head < a.n_heads + a.kv_heads) {
+                        const float c = cs[2 * (m * half + j)], sn = cs[2 * (m * half + j) + 1];
+                        const float r0 = x0 * c - x1 * sn, r1 = x1 * c + x0 * sn;
+                        x0 = r0;
+                        x1 = r1;
+                    }
+                    bf16* dst = nullptr;
+                    if (head < a.n_heads) dst = a.q_out + (size_t)m * a.n_heads * D + (size_t)head * D;
+                    else if (dst_s[m] >= 0) dst = a.kv_base + dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D;  // keys, then values
+                    if (dst) {
+                        dst[j] = __float2bfloat16_rn(x0);
+                        dst[j + half] = __float2bfloat16_rn(x1);
                     }
                 }
             }
@@ -336,18 +340,22 @@ static bool wide_plan(int epilogue, const SkinnyArgs& a, int sms, WideGeometry& 
     geo.ntok = (a.m + 15) / 16 * 16;
     geo.slabs = (a.k + WG_BK - 1) / WG_BK;
     geo.stage_bytes = WG_W_BYTES + geo.ntok * WG_BK * 2;
-    // K is split over a cluster when the tiles are few and heavy: a block should not stream much more than 256 KB,
-    // as long as that does not ask for more blocks than there are SMs
+    // the rows an epilogue needs together: gate and up row (64 apart in a tile), components j and j + D/2 of a head
+    int pair = 64;
+    if (epilogue == EPI_QKV) pair = a.head_dim / 2;
+    geo.pair_shift = 0;
+    while ((1 << geo.pair_shift) < pair) ++geo.pair_shift;
+    if ((1 << geo.pair_shift) != pair) return false;
+    // K is split over the blocks of a cluster as far as that puts more SMs to streaming, while every block still has
+    // two slabs or more to multiply
     geo.ksplit = 1;
-    if (epilogue == EPI_PLAIN || epilogue == EPI_RESIDUAL)
-        while (geo.ksplit < WG_MAX_SPLIT && geo.tiles * geo.ksplit * 2 <= sms &&
-               (size_t)WG_BM * a.k * 2 / geo.ksplit > 256 * 1024 && geo.slabs / (geo.ksplit * 2) >= 2)
-            geo.ksplit *= 2;
-    size_t extra = 0;
-    if (geo.ksplit > 1) extra = (size_t)WG_BM * geo.ntok * 4;                                  // [ksplit][128 / ksplit][ntok]
-    else if (epilogue == EPI_SWIGLU) extra = (size_t)64 * (geo.ntok + 1) * 4;
-    else if (epilogue == EPI_QKV) extra = 2 * (size_t)WG_MAX_TOK * (a.head_dim / 2) * 4 + (size_t)WG_BM * (geo.ntok + 1) * 4;
-    smem = (size_t)WG_STAGES * geo.stage_bytes + extra + 1024;
+    while (geo.ksplit < WG_MAX_SPLIT && geo.tiles * geo.ksplit * 2 <= sms && geo.slabs >= geo.ksplit * 4) geo.ksplit *= 2;
+    const int per = (geo.slabs + geo.ksplit - 1) / geo.ksplit;
+    size_t extra = (size_t)WG_BM * geo.ntok * 4;  // the (partial) sums on their way to the epilogue
+    if (epilogue == EPI_QKV) extra += 2 * (size_t)WG_MAX_TOK * (a.head_dim / 2) * 4;
+    geo.stages = per < WG_STAGES ? per : WG_STAGES;
+    if (geo.stages < 1) geo.stages = 1;
+    smem = (size_t)geo.stages * geo.stage_bytes + extra + 1024;
     return smem <= 224 * 1024;
 }
 
