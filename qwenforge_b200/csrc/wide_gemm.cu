@@ -43,7 +43,9 @@ struct WideGeometry {
     int tiles;       // tiles of 128 weight rows
     int ksplit;      // blocks of a cluster sharing a tile
     int slabs;       // 64-column slabs of K
-    int stage_bytes; // weights + token rows of one stage
+    int slab_bytes;  // weights + token rows of one slab
+    int group;       // slabs per stage of the ring
+    int stage_bytes; // group * slab_bytes
     int stages;      // depth of the ring
     int pair_shift;  // log2 of the distance between the two tile rows an epilogue needs together
 };
@@ -100,40 +102,51 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         row1 = a.inter + tile * 64;
     }
 
+    // A stage of the ring holds `group` consecutive slabs of K: its copies are issued together, slab after slab for the
+    // same weight rows, so that the memory sees runs of group x 128 contiguous bytes per row instead of lone 128-byte
+    // pieces a page apart (which it serves at a fraction of its bandwidth).
+    const int group = geo.group, stages = geo.stages, slab_bytes = geo.slab_bytes;
+    const int n_groups = (n_kb + group - 1) / group;
     if (warp == 4) {
         // ---- copies. All lanes run the loop; one issues.
         const bool leader = elect_one();
-        auto load_w = [&](int kb, int s) {
-            unsigned char* w_s = ring + (size_t)s * geo.stage_bytes;
-            tma_load_2d(w_s, &w_map, kb * WG_BK, row0, &full_bar[s]);
-            tma_load_2d(w_s + 64 * WG_BK * 2, &w_map, kb * WG_BK, row1, &full_bar[s]);
+        auto slabs_of = [&](int gi) { return min(group, n_kb - gi * group); };
+        auto load_w = [&](int gi, int s) {
+            unsigned char* base = ring + (size_t)s * geo.stage_bytes;
+            const int first = kb_begin + gi * group, count = slabs_of(gi);
+            for (int half = 0; half < 2; ++half)
+                for (int j = 0; j < count; ++j)
+                    tma_load_2d(base + (size_t)j * slab_bytes + half * 64 * WG_BK * 2, &w_map, (first + j) * WG_BK, half ? row1 : row0,
+                                &full_bar[s]);
         };
-        auto load_x = [&](int kb, int s) {
-            tma_load_2d(ring + (size_t)s * geo.stage_bytes + WG_W_BYTES, &x_map, kb * WG_BK, 0, &full_bar[s]);
+        auto load_x = [&](int gi, int s) {
+            unsigned char* base = ring + (size_t)s * geo.stage_bytes;
+            const int first = kb_begin + gi * group, count = slabs_of(gi);
+            for (int j = 0; j < count; ++j)
+                tma_load_2d(base + (size_t)j * slab_bytes + WG_W_BYTES, &x_map, (first + j) * WG_BK, 0, &full_bar[s]);
         };
         // weights are nobody's output: those of the first stages are on their way before the kernel before this one ends
-        const int stages = geo.stages;
-        const int early = min(n_kb, stages);
+        const int early = min(n_groups, stages);
         if (leader)
-            for (int i = 0; i < early; ++i) {
-                mbar_expect_tx(&full_bar[i], (uint32_t)geo.stage_bytes);
-                load_w(kb_begin + i, i);
+            for (int gi = 0; gi < early; ++gi) {
+                mbar_expect_tx(&full_bar[gi], (uint32_t)(slabs_of(gi) * slab_bytes));
+                load_w(gi, gi);
             }
         __syncwarp();
         grid_dependency_wait();
         if (leader)
-            for (int i = 0; i < early; ++i) load_x(kb_begin + i, i);
+            for (int gi = 0; gi < early; ++gi) load_x(gi, gi);
         __syncwarp();
-        for (int i = early; i < n_kb; ++i) {
-            const int s = i % stages;
-            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1))) {
+        for (int gi = early; gi < n_groups; ++gi) {
+            const int s = gi % stages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((gi / stages) - 1) & 1))) {
                 timed_out = true;
                 break;
             }
             if (leader) {
-                mbar_expect_tx(&full_bar[s], (uint32_t)geo.stage_bytes);
-                load_w(kb_begin + i, s);
-                load_x(kb_begin + i, s);
+                mbar_expect_tx(&full_bar[s], (uint32_t)(slabs_of(gi) * slab_bytes));
+                load_w(gi, s);
+                load_x(gi, s);
             }
             __syncwarp();
         }
@@ -141,18 +154,22 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         // ---- products
         const bool leader = elect_one();
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ntok >> 3) << 17) | ((uint32_t)(WG_BM >> 4) << 24);
-        for (int i = 0; i < n_kb; ++i) {
-            const int s = i % geo.stages;
-            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (i / geo.stages) & 1))) {
+        for (int gi = 0; gi < n_groups; ++gi) {
+            const int s = gi % stages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (gi / stages) & 1))) {
                 timed_out = true;
                 break;
             }
             tc_fence_after();
-            const unsigned char* w_s = ring + (size_t)s * geo.stage_bytes;
-            const uint64_t dw = smem_desc_sw128(w_s), dx = smem_desc_sw128(w_s + WG_W_BYTES);
+            const int count = min(group, n_kb - gi * group);
             if (leader) {
+                for (int j = 0; j < count; ++j) {
+                    const unsigned char* w_s = ring + (size_t)s * geo.stage_bytes + (size_t)j * slab_bytes;
+                    const uint64_t dw = smem_desc_sw128(w_s), dx = smem_desc_sw128(w_s + WG_W_BYTES);
 #pragma unroll
-                for (int k4 = 0; k4 < WG_BK / 16; ++k4) umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+                    for (int k4 = 0; k4 < WG_BK / 16; ++k4)
+                        umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, (gi > 0 || j > 0 || k4 > 0) ? 1u : 0u);
+                }
                 umma_commit(&empty_bar[s]);
             }
             __syncwarp();
@@ -339,7 +356,7 @@ static bool wide_plan(int epilogue, const SkinnyArgs& a, int sms, WideGeometry& 
     if (geo.tiles < 1) return false;
     geo.ntok = (a.m + 15) / 16 * 16;
     geo.slabs = (a.k + WG_BK - 1) / WG_BK;
-    geo.stage_bytes = WG_W_BYTES + geo.ntok * WG_BK * 2;
+    geo.slab_bytes = WG_W_BYTES + geo.ntok * WG_BK * 2;
     // the rows an epilogue needs together: gate and up row (64 apart in a tile), components j and j + D/2 of a head
     int pair = 64;
     if (epilogue == EPI_QKV) pair = a.head_dim / 2;
@@ -353,8 +370,17 @@ static bool wide_plan(int epilogue, const SkinnyArgs& a, int sms, WideGeometry& 
     const int per = (geo.slabs + geo.ksplit - 1) / geo.ksplit;
     size_t extra = (size_t)WG_BM * geo.ntok * 4;  // the (partial) sums on their way to the epilogue
     if (epilogue == EPI_QKV) extra += 2 * (size_t)WG_MAX_TOK * (a.head_dim / 2) * 4;
-    geo.stages = per < WG_STAGES ? per : WG_STAGES;
-    if (geo.stages < 1) geo.stages = 1;
+    // stages of four slabs (512 contiguous bytes per weight row and refill) while two of them fit, else of two, else one
+    for (geo.group = 4; geo.group >= 1; geo.group /= 2) {
+        geo.stage_bytes = geo.group * geo.slab_bytes;
+        const int wanted = (per + geo.group - 1) / geo.group;
+        const size_t room = 224 * 1024 - 1024 - extra;
+        int fit = (int)(room / geo.stage_bytes);
+        if (fit > WG_STAGES) fit = WG_STAGES;
+        geo.stages = wanted < fit ? wanted : fit;
+        if (geo.stages >= 2 || (geo.stages == 1 && wanted == 1)) break;
+    }
+    if (geo.group < 1 || geo.stages < 1) return false;
     smem = (size_t)geo.stages * geo.stage_bytes + extra + 1024;
     return smem <= 224 * 1024;
 }
