@@ -16,8 +16,8 @@
 // first stages are asked for before the kernel waits for the one before it (programmatic dependent launch). Warp 5
 // issues the products, four of K = 16 per stage, and `tcgen05.commit` hands the stage back. Warps 0 to 3 own the
 // accumulator's lanes: thread r reads the sums of weight row r for all token rows with `tcgen05.ld` and runs the
-// epilogue; where an epilogue pairs two weight rows (gate and up, component j and j + D/2 of a head) the partner's
-// values cross through shared memory. While the weights stream, those warps prepare what the epilogue needs
+// sums across shared memory, token-major and with the two rows an epilogue needs together side by side (gate and up,
+// component j and j + D/2 of a head); all six warps then run the epilogue, a thread per pair of rows. While the weights stream, those warps prepare what the epilogue needs
 // (sines and cosines of every token's position, where each token's key and value go).
 // Products of few tiles and a long K (a feed-forward's second product) are split along K over the blocks of a
 // thread-block cluster: every block sends each owner its rows' partial sums through distributed shared memory, and
@@ -200,13 +200,14 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             }
             row_barrier();
             if (a.inv_freq) {
-                const int half = D / 2;
-                for (int i = r; i < a.m * half; i += WG_ROW_THREADS) {
-                    const int m = i / half, j = i % half;
-                    float s, c;
-                    sincosf((float)pos_s[m] * a.inv_freq[j], &s, &c);
-                    cs[2 * i] = c;
-                    cs[2 * i + 1] = s;
+                // thread r takes frequency r % (D / 2) for every (128 / (D / 2))-th token: no division in the loop
+                const int half = D / 2, j = r & (half - 1), step = WG_ROW_THREADS / half;
+                const float freq = a.inv_freq[j];
+                for (int m = r / half; m < a.m; m += step) {
+                    float sn, c;
+                    sincosf((float)pos_s[m] * freq, &sn, &c);
+                    cs[2 * (m * half + j)] = c;
+                    cs[2 * (m * half + j) + 1] = sn;
                 }
             }
             row_barrier();
@@ -240,82 +241,78 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     }
     if (ksplit > 1) cg::this_cluster().sync();  // every thread of every block of the cluster: all partial sums have arrived
     else __syncthreads();
-    if (warp < 4) {
-        // ---- the owner's epilogue: element (pair p, token m) per thread and turn, pairs fastest, so that the threads of a
-        // warp write neighbouring features of one token
-        if (EPI != EPI_QKV) grid_dependency_wait();  // the residual stream and the outputs belong to earlier kernels until now
+    {
+        // ---- the owner's epilogue, by all six warps: a thread keeps one pair of rows (so that everything about the rows
+        // is computed once) and walks the tokens; the threads of a warp hold neighbouring pairs, so they write
+        // neighbouring features of one token
+        grid_dependency_wait();  // the residual stream and the outputs belong to earlier kernels until now
         const int lp = geo.pair_shift, P = 1 << lp;
-        const int pairs_per_rank = 64 / ksplit, own = 2 * pairs_per_rank;
-        const int total = pairs_per_rank * a.m;
-        constexpr int BATCH = 4;
-        for (int e0 = threadIdx.x; e0 < total; e0 += WG_ROW_THREADS * BATCH) {
-            float lo[BATCH], up[BATCH], res_lo[BATCH], res_hi[BATCH];
-            int n_lo[BATCH], tok[BATCH];
+        const int ppr = 64 / ksplit, own = 2 * ppr;                      // pairs this block owns; a power of two
+        const int p_local = threadIdx.x & (ppr - 1), m_first = threadIdx.x / ppr, m_step = WG_THREADS / ppr;
+        const int low = rank * ppr + p_local;
+        const int r_lo = ((low >> lp) << (lp + 1)) | (low & (P - 1));    // the pair's first tile row; the second is P further
+        const int n0 = (EPI == EPI_SWIGLU ? tile * 64 : tile * WG_BM) + r_lo, n1 = n0 + P;
+        const int width = EPI == EPI_SWIGLU ? a.inter : a.n;
+        const bool in0 = n0 < width, in1 = EPI != EPI_SWIGLU && n1 < width;
+        const float bias0 = (a.bias && in0) ? __bfloat162float(a.bias[n0]) : 0.f;
+        const float bias1 = (a.bias && in1) ? __bfloat162float(a.bias[n1]) : 0.f;
+        const float* pair_sums = sums + 2 * p_local;
+        // QKV: n0 is component j < D/2 of head n0 / D (D a power of two), n1 its partner j + D/2
+        const int d_shift = 31 - __clz(D > 0 ? D : 1), half = D / 2;
+        const int head = EPI == EPI_QKV ? n0 >> d_shift : 0, j = EPI == EPI_QKV ? n0 & (D - 1) : 0;
+        const bool rotated = EPI == EPI_QKV && a.inv_freq != nullptr && head < a.n_heads + a.kv_heads;
+        constexpr int BATCH = 8;
+        for (int mb = m_first; mb < a.m; mb += m_step * BATCH) {
+            float x0[BATCH], x1[BATCH], res0[BATCH], res1[BATCH];
 #pragma unroll
             for (int b = 0; b < BATCH; ++b) {
-                const int e = e0 + b * WG_ROW_THREADS;
-                const bool live = e < total;
-                const int p_local = live ? e % pairs_per_rank : 0, m = live ? e / pairs_per_rank : 0;
-                const int low = rank * pairs_per_rank + p_local;
-                const int r_lo = ((low >> lp) << (lp + 1)) | (low & (P - 1));  // the pair's first tile row; the second is P further
-                float x0 = 0.f, x1 = 0.f;
-                for (int src = 0; src < ksplit; ++src) {
-                    const float2 part = *reinterpret_cast<const float2*>(sums + ((size_t)src * ntok + m) * own + 2 * p_local);
-                    x0 += part.x;
-                    x1 += part.y;
-                }
-                lo[b] = x0;
-                up[b] = x1;
-                tok[b] = live ? m : -1;
-                n_lo[b] = EPI == EPI_SWIGLU ? tile * 64 + r_lo : tile * WG_BM + r_lo;  // SWIGLU: index into the intermediate width
-                if (EPI == EPI_RESIDUAL) {
-                    const bool in_lo = live && n_lo[b] < a.n, in_hi = live && n_lo[b] + P < a.n;
-                    res_lo[b] = in_lo ? __ldcg(a.residual + (size_t)m * a.n + n_lo[b]) : 0.f;
-                    res_hi[b] = in_hi ? __ldcg(a.residual + (size_t)m * a.n + n_lo[b] + P) : 0.f;
+                const int m = mb + b * m_step;
+                x0[b] = bias0;
+                x1[b] = bias1;
+                if (m < a.m) {
+                    for (int src = 0; src < ksplit; ++src) {
+                        const float2 part = *reinterpret_cast<const float2*>(pair_sums + ((size_t)src * ntok + m) * own);
+                        x0[b] += part.x;
+                        x1[b] += part.y;
+                    }
+                    if (EPI == EPI_RESIDUAL) {
+                        res0[b] = in0 ? __ldcg(a.residual + (size_t)m * a.n + n0) : 0.f;
+                        res1[b] = in1 ? __ldcg(a.residual + (size_t)m * a.n + n1) : 0.f;
+                    }
                 }
             }
 #pragma unroll
             for (int b = 0; b < BATCH; ++b) {
-                const int m = tok[b], n0 = n_lo[b];
-                if (m < 0) continue;
+                const int m = mb + b * m_step;
+                if (m >= a.m) break;
                 if (EPI == EPI_SWIGLU) {
-                    if (n0 < a.inter)
-                        reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0] = __float2bfloat16_rn(lo[b] / (1.0f + expf(-lo[b])) * up[b]);
-                    continue;
-                }
-                const int n1 = n0 + P;
-                float x0 = lo[b], x1 = up[b];
-                if (a.bias) {
-                    if (n0 < a.n) x0 += __bfloat162float(a.bias[n0]);
-                    if (n1 < a.n) x1 += __bfloat162float(a.bias[n1]);
-                }
-                if (EPI == EPI_RESIDUAL) {
-                    if (n0 < a.n) a.residual[(size_t)m * a.n + n0] = res_lo[b] + x0;
-                    if (n1 < a.n) a.residual[(size_t)m * a.n + n1] = res_hi[b] + x1;
+                    if (in0) reinterpret_cast<bf16*>(a.out)[(size_t)m * a.ldo + n0] = __float2bfloat16_rn(x0[b] / (1.0f + expf(-x0[b])) * x1[b]);
+                } else if (EPI == EPI_RESIDUAL) {
+                    if (in0) a.residual[(size_t)m * a.n + n0] = res0[b] + x0[b];
+                    if (in1) a.residual[(size_t)m * a.n + n1] = res1[b] + x1[b];
                 } else if (EPI == EPI_PLAIN) {
                     if (a.out_f32) {
                         float* o = reinterpret_cast<float*>(a.out) + (size_t)m * a.ldo;
-                        if (n0 < a.n) o[n0] = x0;
-                        if (n1 < a.n) o[n1] = x1;
+                        if (in0) o[n0] = x0[b];
+                        if (in1) o[n1] = x1[b];
                     } else {
                         bf16* o = reinterpret_cast<bf16*>(a.out) + (size_t)m * a.ldo;
-                        if (n0 < a.n) o[n0] = __float2bfloat16_rn(x0);
-                        if (n1 < a.n) o[n1] = __float2bfloat16_rn(x1);
+                        if (in0) o[n0] = __float2bfloat16_rn(x0[b]);
+                        if (in1) o[n1] = __float2bfloat16_rn(x1[b]);
                     }
-                } else if (n0 < a.n) {  // EPI_QKV: n0 is component j < D/2 of head n0 / D, n1 its partner j + D/2
-                    const int head = n0 / D, j = n0 % D, half = D / 2;
-                    if (a.inv_freq != nullptr && head < a.n_heads + a.kv_heads) {
+                } else if (in0) {  // EPI_QKV
+                    float y0 = x0[b], y1 = x1[b];
+                    if (rotated) {
                         const float c = cs[2 * (m * half + j)], sn = cs[2 * (m * half + j) + 1];
-                        const float r0 = x0 * c - x1 * sn, r1 = x1 * c + x0 * sn;
-                        x0 = r0;
-                        x1 = r1;
+                        y0 = x0[b] * c - x1[b] * sn;
+                        y1 = x1[b] * c + x0[b] * sn;
                     }
                     bf16* dst = nullptr;
-                    if (head < a.n_heads) dst = a.q_out + (size_t)m * a.n_heads * D + (size_t)head * D;
+                    if (head < a.n_heads) dst = a.q_out + ((size_t)m * a.n_heads + head) * D;
                     else if (dst_s[m] >= 0) dst = a.kv_base + dst_s[m] + (long long)(head - a.n_heads) * QF_PAGE * D;  // keys, then values
                     if (dst) {
-                        dst[j] = __float2bfloat16_rn(x0);
-                        dst[j + half] = __float2bfloat16_rn(x1);
+                        dst[j] = __float2bfloat16_rn(y0);
+                        dst[j + half] = __float2bfloat16_rn(y1);
                     }
                 }
             }
