@@ -48,7 +48,16 @@ struct WideGeometry {
     int stage_bytes; // group * slab_bytes
     int stages;      // depth of the ring
     int pair_shift;  // log2 of the distance between the two tile rows an epilogue needs together
+    unsigned long long* stamps;  // measuring aid: if not null, [blocks][8] nanosecond time stamps of a block's phases
 };
+
+__device__ __forceinline__ void stamp(const WideGeometry& geo, int slot) {
+    if (geo.stamps) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        geo.stamps[(size_t)blockIdx.x * 8 + slot] = now;
+    }
+}
 
 __device__ __forceinline__ void row_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(WG_ROW_THREADS) : "memory"); }
 
@@ -64,6 +73,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     __shared__ int pos_s[WG_MAX_TOK];
     __shared__ long long dst_s[WG_MAX_TOK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) stamp(geo, 0);  // entry
     const int ntok = geo.ntok, ksplit = geo.ksplit;
     const int tile = blockIdx.x / ksplit, rank = blockIdx.x % ksplit;
     const int per = (geo.slabs + ksplit - 1) / ksplit;
@@ -88,6 +98,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
     __syncthreads();
     tc_fence_after();
     grid_launch_dependents();
+    if (threadIdx.x == 0) stamp(geo, 1);  // barriers and tensor memory are set up
     const uint32_t tmem = tmem_base_s;
     bool timed_out = false;
     float v[WG_MAX_TOK];  // row threads: this lane's sums, one per token row
@@ -134,6 +145,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             }
         __syncwarp();
         grid_dependency_wait();
+        if (leader) stamp(geo, 2);  // the kernel before this one is done
         if (leader)
             for (int gi = 0; gi < early; ++gi) load_x(gi, gi);
         __syncwarp();
@@ -161,6 +173,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
                 break;
             }
             tc_fence_after();
+            if (leader && gi == 0) stamp(geo, 3);  // the first stage has arrived
             const int count = min(group, n_kb - gi * group);
             if (leader) {
                 for (int j = 0; j < count; ++j) {
@@ -214,6 +227,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         }
         if (!__all_sync(0xffffffffu, mbar_wait(&acc_bar, 0))) timed_out = true;
         tc_fence_after();
+        if (threadIdx.x == 0) stamp(geo, 4);  // every product is done
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
         for (int c0 = 0; c0 < WG_MAX_TOK; c0 += 32) {
@@ -239,8 +253,10 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
         for (int m = 0; m < WG_MAX_TOK; ++m)
             if (m < ntok) mine[(size_t)m * own] = v[m];
     }
+    if (threadIdx.x == 0) stamp(geo, 5);  // this block's sums are on their way
     if (ksplit > 1) cg::this_cluster().sync();  // every thread of every block of the cluster: all partial sums have arrived
     else __syncthreads();
+    if (threadIdx.x == 0) stamp(geo, 6);  // all sums have arrived
     {
         // ---- the owner's epilogue, by all six warps: a thread keeps one pair of rows (so that everything about the rows
         // is computed once) and walks the tokens; the threads of a warp hold neighbouring pairs, so they write
@@ -318,6 +334,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constan
             }
         }
     }
+    if (threadIdx.x == 0) stamp(geo, 7);  // the epilogue is done
     if (timed_out && lane == 0) atomicOr(a.err, QF_ERR_COPY_TIMEOUT);
     tc_fence_before();
     __syncthreads();
@@ -378,6 +395,7 @@ static bool wide_plan(int epilogue, const SkinnyArgs& a, int sms, WideGeometry& 
         if (geo.stages >= 2 || (geo.stages == 1 && wanted == 1)) break;
     }
     if (geo.group < 1 || geo.stages < 1) return false;
+    geo.stamps = nullptr;
     smem = (size_t)geo.stages * geo.stage_bytes + extra + 1024;
     return smem <= 224 * 1024;
 }
@@ -413,6 +431,22 @@ QF_EXPORT int qf_wide_gemm(int epilogue, const SkinnyArgs* args, cudaStream_t st
     WideGeometry geo;
     size_t smem = 0;
     if (!wide_plan(epilogue, *args, qf_sm_count(), geo, smem)) return (int)cudaErrorInvalidValue;
+    switch (epilogue) {
+        case EPI_PLAIN: return wide_launch<EPI_PLAIN>(*args, geo, smem, stream);
+        case EPI_RESIDUAL: return wide_launch<EPI_RESIDUAL>(*args, geo, smem, stream);
+        case EPI_SWIGLU: return wide_launch<EPI_SWIGLU>(*args, geo, smem, stream);
+        case EPI_QKV: return wide_launch<EPI_QKV>(*args, geo, smem, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+// A measuring aid: the same launch, with every block writing eight nanosecond time stamps (entry, set-up done, the
+// kernel before done, first stage arrived, products done, sums sent, sums arrived, epilogue done) to stamps[block][8].
+QF_EXPORT int qf_wide_gemm_stamped(int epilogue, const SkinnyArgs* args, unsigned long long* stamps, cudaStream_t stream) {
+    WideGeometry geo;
+    size_t smem = 0;
+    if (!wide_plan(epilogue, *args, qf_sm_count(), geo, smem)) return (int)cudaErrorInvalidValue;
+    geo.stamps = stamps;
     switch (epilogue) {
         case EPI_PLAIN: return wide_launch<EPI_PLAIN>(*args, geo, smem, stream);
         case EPI_RESIDUAL: return wide_launch<EPI_RESIDUAL>(*args, geo, smem, stream);
