@@ -2,9 +2,12 @@
 // unequal lengths, and continuations whose earlier keys already lie in the cache. The span's own keys were
 // written to the cache before this kernel runs, so all keys come from one place.
 //
-// A block (4 warps) serves 64 consecutive query tokens of one (sequence, query head); each warp owns 16 rows.
-// Key/value pages (64 positions) of the head's kv head stream through shared memory with double-buffered
-// cp.async, from the first page that any row's window reaches to the page of the last row's own position.
+// A block serves 64 consecutive query tokens of one (sequence, query head) with G groups of 4 warps; in a group each
+// warp owns 16 rows. Key/value pages (64 positions) of the head's kv head stream through shared memory with
+// double-buffered cp.async, G pages per turn, from the first page that any row's window reaches to the page of the
+// last row's own position; group g takes every G-th page, so a tile's chain of pages is 1 / G as long (a single
+// prompt's last tile walks all of its pages while the SMs have room for more warps). At the end the groups' running
+// maxima, sums and outputs of the same rows are merged through shared memory, lane by lane.
 // S = Q K^T and O += P V run on the tensor cores (m16n8k16, bf16 in, float32 accumulate); the online softmax
 // is float32 with base-2 exponentials (the scale folded in). A query at position p sees keys j with
 // max(0, p - window + 1) <= j <= p.
@@ -14,8 +17,8 @@
 #define PF_THREADS (PF_WARPS * 32)
 #define PF_BM 64
 
-template <int D>
-__global__ void __launch_bounds__(PF_THREADS, D <= 64 ? 4 : 2)
+template <int D, int G>
+__global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                      float scale_log2, int window, int* err) {
@@ -23,8 +26,8 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     constexpr int KS = D / 16;
     constexpr int NT = D / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][64][LD]
-    bf16* v_s = k_s + 2 * QF_PAGE * LD;             // [2][64][LD]
+    bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][G][64][LD]
+    bf16* v_s = k_s + 2 * G * QF_PAGE * LD;         // [2][G][64][LD]
 
     const int seq = blockIdx.z, head = blockIdx.y;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
@@ -33,12 +36,12 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     if (row0 >= q_len) return;
     const int n_rows = min(PF_BM, q_len - row0);
     const int slot = slots[seq];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) % PF_WARPS, group = (threadIdx.x >> 5) / PF_WARPS;
     const int q_width = n_heads * D;
     const int kvh = head / (n_heads / site.kv_heads);
 
     if (slot < 0) {
-        for (int i = threadIdx.x; i < n_rows * D; i += PF_THREADS)
+        for (int i = threadIdx.x; i < n_rows * D; i += PF_THREADS * G)
             out[(size_t)(q_begin + row0 + i / D) * q_width + (size_t)head * D + i % D] = __float2bfloat16_rn(0.f);
         return;
     }
@@ -76,32 +79,37 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     float m_run[2] = {QF_NEG_BIG, QF_NEG_BIG}, l_run[2] = {0.f, 0.f};
 
     const int* table_row = site.table + (long long)slot * site.table_stride;
-    auto load_page = [&](int page_index, int buf) {
-        const int page = table_row[page_index];
-        const bool held = page >= 0;
-        if (!held && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
-        const bf16* kp = site.base + (long long)(held ? page : 0) * site.page_elems + (long long)kvh * QF_PAGE * D;
-        const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
-        constexpr int CH = D / 8;
-        for (int i = threadIdx.x; i < QF_PAGE * CH; i += PF_THREADS) {
-            const int rr = i / CH, c = (i % CH) * 8;
-            cp_async_16(k_s + ((size_t)buf * QF_PAGE + rr) * LD + c, kp + rr * D + c, held);
-            cp_async_16(v_s + ((size_t)buf * QF_PAGE + rr) * LD + c, vp + rr * D + c, held);
+    // the pages of one turn: page first + g goes to group g's buffer; every thread helps to fetch all of them
+    auto load_pages = [&](int first, int buf) {
+        for (int gi = 0; gi < G; ++gi) {
+            if (first + gi >= p_end) break;
+            const int page = table_row[first + gi];
+            const bool held = page >= 0;
+            if (!held && threadIdx.x == 0) atomicOr(err, QF_ERR_NO_PAGE);
+            const bf16* kp = site.base + (long long)(held ? page : 0) * site.page_elems + (long long)kvh * QF_PAGE * D;
+            const bf16* vp = kp + (long long)site.kv_heads * QF_PAGE * D;
+            constexpr int CH = D / 8;
+            for (int i = threadIdx.x; i < QF_PAGE * CH; i += PF_THREADS * G) {
+                const int rr = i / CH, c = (i % CH) * 8;
+                cp_async_16(k_s + (((size_t)buf * G + gi) * QF_PAGE + rr) * LD + c, kp + rr * D + c, held);
+                cp_async_16(v_s + (((size_t)buf * G + gi) * QF_PAGE + rr) * LD + c, vp + rr * D + c, held);
+            }
         }
     };
 
-    load_page(p_begin, 0);
+    load_pages(p_begin, 0);
     cp_async_commit();
-    for (int p = p_begin; p < p_end; ++p) {
-        const int buf = (p - p_begin) & 1;
-        if (p + 1 < p_end) load_page(p + 1, buf ^ 1);
+    for (int first = p_begin, turn = 0; first < p_end; first += G, ++turn) {
+        const int buf = turn & 1;
+        if (first + G < p_end) load_pages(first + G, buf ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const bf16* kb = k_s + (size_t)buf * QF_PAGE * LD;
-        const bf16* vb = v_s + (size_t)buf * QF_PAGE * LD;
+        const int p = first + group;
+        const bf16* kb = k_s + ((size_t)buf * G + group) * QF_PAGE * LD;
+        const bf16* vb = v_s + ((size_t)buf * G + group) * QF_PAGE * LD;
         const int key0 = p * QF_PAGE;
-        if (warp_active && key0 <= warp_last && key0 + QF_PAGE > warp_lo) {
+        if (p < p_end && warp_active && key0 <= warp_last && key0 + QF_PAGE > warp_lo) {
             float s[8][4];
 #pragma unroll
             for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
@@ -212,6 +220,42 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
         __syncthreads();
     }
     cp_async_wait<0>();
+    if (G > 1) {
+        // ---- merge the groups: a lane of group g > 0 leaves its maxima, sums and outputs where the lane of group 0 with
+        // the same rows finds them (the page buffers are free: the loop ended with a block-wide barrier)
+        constexpr int PER_LANE = NT * 4 + 4;
+        float* merge = reinterpret_cast<float*>(smem_raw);  // [G - 1][PF_WARPS][PER_LANE][32]
+        if (group > 0) {
+            float* mine = merge + ((size_t)(group - 1) * PF_WARPS + warp) * PER_LANE * 32 + lane;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mine[(nt * 4 + e) * 32] = o[nt][e];
+            mine[(NT * 4 + 0) * 32] = m_run[0];
+            mine[(NT * 4 + 1) * 32] = m_run[1];
+            mine[(NT * 4 + 2) * 32] = l_run[0];
+            mine[(NT * 4 + 3) * 32] = l_run[1];
+        }
+        __syncthreads();
+        if (group > 0) return;
+        for (int g = 1; g < G; ++g) {
+            const float* theirs = merge + ((size_t)(g - 1) * PF_WARPS + warp) * PER_LANE * 32 + lane;
+            float f_mine[2], f_theirs[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_other = theirs[(NT * 4 + i) * 32], l_other = theirs[(NT * 4 + 2 + i) * 32];
+                const float m_new = fmaxf(m_run[i], m_other);
+                f_mine[i] = fast_exp2(m_run[i] - m_new);     // both maxima QF_NEG_BIG (nothing seen): 2^0, sums stay 0
+                f_theirs[i] = fast_exp2(m_other - m_new);
+                m_run[i] = m_new;
+                l_run[i] = l_run[i] * f_mine[i] + l_other * f_theirs[i];
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[nt][e] = o[nt][e] * f_mine[e >> 1] + theirs[(nt * 4 + e) * 32] * f_theirs[e >> 1];
+        }
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
@@ -223,32 +267,47 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     }
 }
 
-template <int D>
-static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
-                  const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
-    const size_t smem = (size_t)4 * QF_PAGE * (D + 8) * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int D, int G>
+static int launch_groups(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, KvSite<bf16> site,
+                         int n_heads, int n_seqs, int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
+    size_t smem = (size_t)4 * G * QF_PAGE * (D + 8) * sizeof(bf16);
+    const size_t merge = (size_t)(G - 1) * PF_WARPS * (D / 8 * 4 + 4) * 32 * sizeof(float);
+    if (smem < merge) smem = merge;
+    cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     dim3 grid((max_q_len + PF_BM - 1) / PF_BM, n_heads, n_seqs);
-    prefill_flash_kernel<D><<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site,
-                                                                n_heads, scale * 1.4426950408889634f, window, err);
+    prefill_flash_kernel<D, G><<<grid, PF_THREADS * G, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site, n_heads,
+                                                                         scale * 1.4426950408889634f, window, err);
     return (int)cudaGetLastError();
 }
 
-// Same arguments as the generic attention kernel, bf16 only. cudaErrorInvalidValue for a head size without an
+template <int D>
+static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
+                  const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
+                  int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
+    KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
+    // Two groups of warps per tile when tiles walk many pages and there are too few tiles to fill the SMs with
+    // warps otherwise: a tile's chain of pages is then half as long.
+    const long long tiles = (long long)((max_q_len + PF_BM - 1) / PF_BM) * n_heads * n_seqs;
+    const int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
+    const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * 8;
+    return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
+                 : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
+}
+
+// The arguments of the generic attention kernel and `max_kv_len`, an upper bound of any sequence's length after this
+// step (it only steers how a tile's pages are shared among warps); bf16 only. cudaErrorInvalidValue for a head size without an
 // instantiation (the caller then uses the generic kernel).
 QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
                                    void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                   int head_dim, int n_heads, int n_seqs, int max_q_len, float scale, int window,
-                                   int* err, cudaStream_t stream) {
+                                   int head_dim, int n_heads, int n_seqs, int max_q_len, int max_kv_len, float scale,
+                                   int window, int* err, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                 \
     case DIM:                                                                                                        \
         return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
-                           n_seqs, max_q_len, scale, window, err, stream);
+                           n_seqs, max_q_len, max_kv_len, scale, window, err, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)

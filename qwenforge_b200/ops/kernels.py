@@ -231,8 +231,10 @@ FAST_ATTENTION_HEAD_DIMS = (32, 64, 96, 128)
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
-                      window: int, err: torch.Tensor) -> None:
-    """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128."""
+                      window: int, err: torch.Tensor, max_kv_len: Optional[int] = None) -> None:
+    """Tensor-core flash attention of spans of new tokens over the cache: bfloat16, head sizes 32/64/96/128.
+    `max_kv_len`: an upper bound of any sequence's length after the step (None: unknown, taken as long); it only
+    steers whether a tile of rows shares its pages among two groups of warps."""
     _dev("q", q, torch.bfloat16)
     _dev("out", out, torch.bfloat16)
     _dev("cache", site.storage, torch.bfloat16)
@@ -245,7 +247,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
     _check(library("attention_prefill").qf_attention_prefill(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(max_q_len),
-        _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill")
+        _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)

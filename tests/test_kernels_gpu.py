@@ -167,7 +167,7 @@ def test_rope_cache_write(ops, dtype, nh, kvh, d, rot):
     assert torch.equal(before, site_a.storage)
 
 
-def run_attention(ops, fn_name, dtype, nh, kvh, d, q_lens, starts, window, slots=None, seed=6):
+def run_attention(ops, fn_name, dtype, nh, kvh, d, q_lens, starts, window, slots=None, seed=6, **more):
     n_seqs = len(q_lens)
     slots = slots if slots is not None else list(range(n_seqs))[::-1]
     max_len = max(s + q for s, q in zip(starts, q_lens))
@@ -186,7 +186,7 @@ def run_attention(ops, fn_name, dtype, nh, kvh, d, q_lens, starts, window, slots
     e = err_word()
     args = ops.KvSiteArgs(site.storage, site.table, kvh, d)
     scale = d ** -0.5
-    getattr(ops, fn_name)(q, out, cu, tok_pos, slots_t, args, nh, n_seqs, max(q_lens), scale, window, e)
+    getattr(ops, fn_name)(q, out, cu, tok_pos, slots_t, args, nh, n_seqs, max(q_lens), scale, window, e, **more)
     ref.attention_generic(q, want, cu, tok_pos, slots_t, site, nh, n_seqs, max(q_lens), scale, window, None)
     assert int(e) == 0
     return out, want
@@ -297,9 +297,19 @@ FAST_PREFILL_SHAPES = [
 ]
 
 
+FAST_PREFILL_SHAPES += [
+    (2, 1, 64, [1100], [0], 0),                        # 18 pages for the last tile: shared between the groups unevenly
+    (2, 2, 128, [64, 700], [900, 0], 0),               # a short continuation over a long cache beside a long prompt
+    (3, 1, 64, [600], [0], 200),                       # a window of a few pages
+]
+
+
+@pytest.mark.parametrize("max_kv_len", [64, None], ids=["one_group", "two_groups"])
 @pytest.mark.parametrize("nh,kvh,d,q_lens,starts,window", FAST_PREFILL_SHAPES)
-def test_attention_prefill(ops, nh, kvh, d, q_lens, starts, window):
-    out, want = run_attention(ops, "attention_prefill", torch.bfloat16, nh, kvh, d, q_lens, starts, window)
+def test_attention_prefill(ops, nh, kvh, d, q_lens, starts, window, max_kv_len):
+    """`max_kv_len` steers only how a tile's pages are shared among warps: a bound of one page keeps one group of warps
+    per tile, no bound lets two groups take alternate pages and merge."""
+    out, want = run_attention(ops, "attention_prefill", torch.bfloat16, nh, kvh, d, q_lens, starts, window, max_kv_len=max_kv_len)
     assert max_err(out, want) <= 3e-2
 
 
