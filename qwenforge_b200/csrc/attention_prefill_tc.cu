@@ -22,14 +22,20 @@
 // share an SM; one's exponentials overlap another's products. Every wait on a barrier is bounded: a wait that runs
 // out sets QF_ERR_COPY_TIMEOUT and ends the thread's loop, and the block still frees its tensor memory and returns.
 // No copy uses cluster multicast.
+// One prompt of a few thousand tokens gives too few blocks to fill the SMs, and its last tiles walk dozens of pages one
+// after the other. With SPLIT two blocks (a cluster) share a tile: each takes every second page, and at the end the
+// second block passes its rows' reference maxima, sums and outputs to the first through distributed shared memory,
+// which merges them with its own and writes the result.
+#include <cooperative_groups.h>
+
 #include "tcgen05.cuh"
 
 #define TA_BM 128
 #define TA_ROW_THREADS 128
 #define TA_THREADS 160  // four warps of row threads and the issuing warp
 
-template <int D>
-__global__ void __launch_bounds__(TA_THREADS, 3)
+template <int D, bool SPLIT>
+__global__ void __launch_bounds__(TA_THREADS, SPLIT ? 2 : 3)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   bf16* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                   const int* __restrict__ slots, KvSite<bf16> site, int n_heads, float scale_log2, int window, int* err) {
@@ -45,12 +51,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     unsigned char* k_s = q_s + CB * Q_BLOCK;            // [2][CB][64][64]
     unsigned char* v_s = k_s + 2 * KV_BYTES;            // [2][CB][64][64]
     unsigned char* p_s = v_s + 2 * KV_BYTES;            // [128][64]
+    float* merge_s = reinterpret_cast<float*>(p_s + TA_BM * 128);  // SPLIT: [128][D + 2] of the cluster's second block
+    constexpr int STRIDE = SPLIT ? 2 : 1;               // this block takes every STRIDE-th page of the tile
+    const int rank = SPLIT ? (int)(blockIdx.x & 1) : 0;
     __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_sfree, bar_pv, bar_p;
     __shared__ uint32_t tmem_base_s;
 
     const int seq = blockIdx.z, head = blockIdx.y;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-    const int tile = gridDim.x - 1 - blockIdx.x;  // long rows first
+    const int tile = SPLIT ? (int)(gridDim.x / 2) - 1 - (int)(blockIdx.x / 2) : (int)gridDim.x - 1 - (int)blockIdx.x;  // long rows first
     const int row0 = tile * TA_BM;
     if (row0 >= q_len) return;
     const int n_rows = min(TA_BM, q_len - row0);
@@ -66,8 +75,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
     const int pos0 = tok_pos[q_begin + row0];  // position of the tile's first row; row t is at pos0 + t
     const int last_pos = pos0 + n_rows - 1;
-    const int p_begin = (window > 0 ? max(0, pos0 - window + 1) : 0) / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
-    const int n_tiles = p_end - p_begin;
+    const int p_first = (window > 0 ? max(0, pos0 - window + 1) : 0) / QF_PAGE, p_end = last_pos / QF_PAGE + 1;
+    const int p_begin = p_first + rank;  // this block's pages: p_begin, p_begin + STRIDE, ...
+    const int n_tiles = p_end > p_begin ? (p_end - p_begin + STRIDE - 1) / STRIDE : 0;
 
     if (t == 0) {
         mbar_init(&bar_q, 1);
@@ -87,6 +97,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
     bool timed_out = false;
+    float m_ref = QF_NEG_BIG, l_run = 0.f;  // row threads: the reference maximum of the exponentials, and their sum
     // A warp waits as one: the loads and stores of tensor memory and the choice of the issuing lane are collective, so
     // the lanes of a warp must leave their loop together if a wait runs out.
     auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0; };
@@ -98,7 +109,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const int* table_row = site.table + (long long)slot * site.table_stride;
             auto fetch_page = [&](int j) {  // keys and values of the j-th page of the run into stage j & 1
                 const int stage = j & 1;
-                int page = table_row[p_begin + j];
+                int page = table_row[p_begin + j * STRIDE];
                 if (page < 0) {  // a page the sequence does not hold: reported; some held memory is read instead
                     if (leader) atomicOr(err, QF_ERR_NO_PAGE);
                     page = 0;
@@ -134,15 +145,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 __syncwarp();
                 return true;
             };
-            if (leader) {
+            if (leader && n_tiles > 0) {
                 mbar_expect_tx(&bar_q, CB * Q_BLOCK);
 #pragma unroll
                 for (int cb = 0; cb < CB; ++cb) tma_load_2d(q_s + cb * Q_BLOCK, &q_map, head * D + cb * 64, q_begin + row0, &bar_q);
             }
             __syncwarp();
-            fetch_page(0);
+            if (n_tiles > 0) fetch_page(0);
             if (n_tiles > 1) fetch_page(1);
-            timed_out = !wait_all(&bar_q, 0) || !issue_s(0);
+            if (n_tiles > 0) timed_out = !wait_all(&bar_q, 0) || !issue_s(0);
             for (int j = 0; j < n_tiles && !timed_out; ++j) {
                 // as soon as every row holds its S in registers, S of the next page is multiplied under their softmax
                 if (!wait_all(&bar_sfree, j & 1)) {
@@ -181,7 +192,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         // ---- the row threads
         const int row_pos = pos0 + t, row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        float m_ref = QF_NEG_BIG, l_run = 0.f;  // the reference maximum of the exponentials, and their sum
         for (int j = 0; j < n_tiles; ++j) {
             if (!wait_all(&bar_s, j & 1)) {
                 timed_out = true;
@@ -200,7 +210,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             }
             tc_fence_before();
             mbar_arrive(&bar_sfree);  // S is in this thread's registers
-            const int key0 = (p_begin + j) * QF_PAGE;
+            const int key0 = (p_begin + j * STRIDE) * QF_PAGE;
             // a page that every row of the block sees whole needs no mask
             const bool full = key0 + QF_PAGE - 1 <= pos0 && key0 >= (window > 0 ? max(0, pos0 + TA_BM - 1 - window + 1) : 0);
             float mx[4];  // four chains instead of one: the comparisons do not wait for each other
@@ -275,9 +285,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             tc_fence_before();
             mbar_arrive(&bar_p);
         }
-        if (!timed_out && !wait_all(&bar_pv, (n_tiles - 1) & 1)) timed_out = true;
+        if (!timed_out && n_tiles > 0 && !wait_all(&bar_pv, (n_tiles - 1) & 1)) timed_out = true;
         tc_fence_after();
-        if (!timed_out) {  // the loads are collective: every lane of the warp takes part, rows beyond the span store nothing
+        if (SPLIT && rank == 1) {
+            // this block's part of every row goes to the first block: output sums, reference maximum, sum of weights
+            float* theirs = cooperative_groups::this_cluster().map_shared_rank(merge_s, 0) + (size_t)t * (D + 2);
+            const bool have = n_tiles > 0 && !timed_out;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t raw[32];
+                if (have) tmem_load_32(lane_base + PV_COL + c0, raw);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) theirs[c0 + i] = have ? __uint_as_float(raw[i]) : 0.f;
+            }
+            theirs[D] = have ? m_ref : QF_NEG_BIG;
+            theirs[D + 1] = have ? l_run : 0.f;
+        }
+        if (!SPLIT && !timed_out) {  // the loads are collective: every lane of the warp takes part, rows beyond the span store nothing
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -296,6 +320,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             }
         }
     }
+    if (SPLIT) {
+        cooperative_groups::this_cluster().sync();  // every thread of both blocks: the second block's parts have arrived
+        if (rank == 0 && warp < 4) {
+            // merge: both parts carry a reference maximum of their own; the common one is the larger
+            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+            const float* theirs = merge_s + (size_t)t * (D + 2);
+            const float m_other = theirs[D], l_other = theirs[D + 1];
+            const float m_all = fmaxf(m_ref, m_other);
+            const float f_mine = fast_exp2(m_ref - m_all), f_theirs = fast_exp2(m_other - m_all);
+            const float l_all = l_run * f_mine + l_other * f_theirs;
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+            const bool have = n_tiles > 0 && !timed_out;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t raw[32];
+                if (have) tmem_load_32(lane_base + PV_COL + c0, raw);
+                if (t < n_rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            v[i] = ((have ? __uint_as_float(raw[c + i]) * f_mine : 0.f) + theirs[c0 + c + i] * f_theirs) * inv;
+                        *reinterpret_cast<uint4*>(out_row + c0 + c) =
+                            make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+                    }
+                }
+            }
+        }
+    }
     if (timed_out) atomicOr(err, QF_ERR_COPY_TIMEOUT);
     tc_fence_before();
     __syncthreads();
@@ -303,15 +357,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
 }
 
+template <int D, bool SPLIT>
+static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, void* out, const int* cu_q, const int* tok_pos,
+                          const int* slots, KvSite<bf16> site, int n_heads, int n_seqs, int max_q_len, float scale, int window,
+                          int* err, cudaStream_t stream) {
+    size_t smem = (size_t)(D / 64) * TA_BM * 128 + 4 * (size_t)(D / 64) * QF_PAGE * 128 + TA_BM * 128 + 1024;
+    if (SPLIT) smem += (size_t)TA_BM * (D + 2) * sizeof(float);
+    auto kernel = prefill_tc_kernel<D, SPLIT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int row_tiles = (max_q_len + TA_BM - 1) / TA_BM;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(row_tiles * (SPLIT ? 2 : 1), n_heads, n_seqs);
+    config.blockDim = dim3(TA_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = SPLIT ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&config, kernel, q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads,
+                                   scale * 1.4426950408889634f, window, err);
+}
+
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  int n_tokens, int max_q_len, float scale, int window, int* err, cudaStream_t stream) {
+                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
     // the cache pages must be what the map takes them for: [2][kv_heads][64][D] without gaps
     if (page_elems != 2ll * kv_heads * QF_PAGE * D) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)(D / 64) * TA_BM * 128 + 4 * (size_t)(D / 64) * QF_PAGE * 128 + TA_BM * 128 + 1024;
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
     CUtensorMap q_map = {}, kv_map = {};
     const long long q_width = (long long)n_heads * D;
@@ -319,25 +396,28 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     // The cache of this entry as one matrix of rows of D elements. The map is given more rows than any cache has
     // (its extent only bounds what a copy may address; copies address rows of held pages only).
     if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE)) return (int)cudaErrorNotSupported;
-    dim3 grid((max_q_len + TA_BM - 1) / TA_BM, n_heads, n_seqs);
-    prefill_tc_kernel<D><<<grid, TA_THREADS, smem, stream>>>(q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads,
-                                                             scale * 1.4426950408889634f, window, err);
-    return (int)cudaGetLastError();
+    // two blocks per tile while there are no more tiles than two per SM, and tiles walk eight pages or more
+    const long long blocks = (long long)((max_q_len + TA_BM - 1) / TA_BM) * n_heads * n_seqs;
+    const int span = window > 0 && window + TA_BM < max_kv_len ? window + TA_BM : max_kv_len;
+    const bool split = span >= 8 * QF_PAGE && blocks <= (long long)qf_sm_count() * 2;
+    return split ? launch_variant<D, true>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
+                 : launch_variant<D, false>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
 }
 
-// The arguments of qf_attention_prefill and the number of rows of q (n_tokens). cudaErrorInvalidValue for a head
+// The arguments of qf_attention_prefill (with `max_kv_len`, the bound that steers the sharing of a tile) and the number
+// of rows of q (n_tokens). cudaErrorInvalidValue for a head
 // size other than 64 or 128, or for cache pages with gaps (the caller then uses another kernel).
 QF_EXPORT int qf_attention_prefill_tc(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
                                       void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, float scale,
-                                      int window, int* err, cudaStream_t stream) {
+                                      int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                      float scale, int window, int* err, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0 || n_tokens <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
     if (head_dim == 64)
         return launch<64>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads, n_seqs,
-                          n_tokens, max_q_len, scale, window, err, stream);
+                          n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
     if (head_dim == 128)
         return launch<128>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads, n_seqs,
-                           n_tokens, max_q_len, scale, window, err, stream);
+                           n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
     return (int)cudaErrorInvalidValue;
 }

@@ -255,9 +255,10 @@ TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                          slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
-                         window: int, err: torch.Tensor) -> None:
+                         window: int, err: torch.Tensor, max_kv_len: Optional[int] = None) -> None:
     """The same attention on the fifth-generation tensor cores (tcgen05, accumulators in tensor memory): blocks of
-    128 query rows; bfloat16, head sizes 64 and 128, cache pages without gaps."""
+    128 query rows; bfloat16, head sizes 64 and 128, cache pages without gaps. `max_kv_len` as in `attention_prefill`:
+    with few tiles of many pages, two blocks of a cluster share a tile."""
     _dev("q", q, torch.bfloat16)
     _dev("out", out, torch.bfloat16)
     _dev("cache", site.storage, torch.bfloat16)
@@ -272,7 +273,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
     _check(library("attention_prefill_tc").qf_attention_prefill_tc(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
-        _I(max_q_len), _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill_tc")
+        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()),
+        "attention_prefill_tc")
 
 
 class DecodeScratch:

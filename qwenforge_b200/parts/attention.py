@@ -120,12 +120,8 @@ class GqaAttention(Mixer):
             least = TC_PREFILL_MIN_TOKENS.get(self.head_dim)
             prefill = (ops.attention_prefill_tc if least is not None and n >= least and ctx.max_q_len >= 128
                        else ops.attention_prefill)
-            if prefill is ops.attention_prefill:
-                prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                        ctx.max_q_len, self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len)
-            else:
-                prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                        ctx.max_q_len, self.scale, self.window, ctx.err)
+            prefill(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
+                    ctx.max_q_len, self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len)
         else:
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
                                   ctx.max_q_len, self.scale, self.window, ctx.err)

@@ -325,9 +325,19 @@ TC_PREFILL_SHAPES = [
 ]
 
 
+TC_PREFILL_SHAPES += [
+    (2, 1, 64, [1100], [0], 0),                          # 18 pages for the last tile: an odd share for the second block
+    (2, 2, 128, [64, 700], [900, 0], 0),                 # a short continuation over a long cache beside a long prompt
+    (3, 1, 64, [600, 1], [0, 0], 200),                   # a window of a few pages; a one-token sequence (one page, one block idle)
+]
+
+
+@pytest.mark.parametrize("max_kv_len", [64, None], ids=["one_block", "two_blocks"])
 @pytest.mark.parametrize("nh,kvh,d,q_lens,starts,window", TC_PREFILL_SHAPES)
-def test_attention_prefill_tc(ops, nh, kvh, d, q_lens, starts, window):
-    out, want = run_attention(ops, "attention_prefill_tc", torch.bfloat16, nh, kvh, d, q_lens, starts, window)
+def test_attention_prefill_tc(ops, nh, kvh, d, q_lens, starts, window, max_kv_len):
+    """One block per tile of 128 rows, or (few tiles of many pages: no bound given) two blocks of a cluster that take
+    alternate pages and merge through distributed shared memory."""
+    out, want = run_attention(ops, "attention_prefill_tc", torch.bfloat16, nh, kvh, d, q_lens, starts, window, max_kv_len=max_kv_len)
     assert max_err(out, want) <= 3e-2
 
 
