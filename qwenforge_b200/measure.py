@@ -1,0 +1,276 @@
+"""Kernel-level measurements: how the fused kernels of this library compare with one another and with the unfused
+path (norm kernel + library product + elementwise kernel) on the products of one decoder layer, and how the prefill
+attention kernels compare. Every figure is the mean of CUDA-graph replays timed with CUDA events, the kernels of
+`repeat` layers (each with weights of its own, so nothing is served from L2 twice) back to back in one graph.
+
+    python -m qwenforge_b200.measure products --preset qwen2.5-0.5b --rows 1,8,16,64
+    python -m qwenforge_b200.measure chain    --preset qwen2.5-0.5b --rows 8
+    python -m qwenforge_b200.measure phases   --preset qwen2.5-0.5b --rows 1,64
+    python -m qwenforge_b200.measure attention --tokens 1024,2048,4096 --heads 14 --kv-heads 2 --head-dim 64
+
+products   per product of a layer (output projection, gate/up, down, query/key/value): the weight-streaming kernel of
+           skinny_gemm.cu (rows <= 16), the tcgen05 kernel of wide_gemm.cu (rows <= 64), and the unfused kernels
+chain      the four products after attention as separate kernels, as ONE persistent kernel per layer
+           (skinny_chain.cu), and all layers' products inside one launch (the persistent kernel's steady state)
+phases     wide_gemm.cu's own time stamps: when a block's copies, products, exchange and epilogue end
+attention  the mma.sync and the tcgen05 prefill attention on one prompt, with a tile's pages shared or not
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import sys
+
+import torch
+
+from . import ops
+from .cache import PAGE_TOKENS
+from .config import preset_config
+
+NAMES = ("output projection (residual)", "gate/up (norm, SwiGLU)", "down (residual)", "query/key/value (norm, rotation, cache)")
+
+
+class Pages:
+    """A paged key/value store of `n_slots` sequences of up to `max_len` positions, pages in scrambled order."""
+
+    def __init__(self, n_slots: int, max_len: int, kv_heads: int, head_dim: int, device, seed: int = 0):
+        per_seq = (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS
+        g = torch.Generator().manual_seed(seed)
+        self.storage = torch.zeros(n_slots * per_seq + 3, 2, kv_heads, PAGE_TOKENS, head_dim, dtype=torch.bfloat16, device=device)
+        self.table = torch.randperm(n_slots * per_seq + 3, generator=g)[:n_slots * per_seq].to(torch.int32).view(n_slots, per_seq).to(device)
+        self.kv_heads, self.head_dim = kv_heads, head_dim
+
+    def args(self) -> ops.KvSiteArgs:
+        return ops.KvSiteArgs(self.storage, self.table, self.kv_heads, self.head_dim)
+
+
+def layer_products(rows: int, hidden: int, inter: int, heads: int, kv_heads: int, head_dim: int, seed: int = 0, device="cuda"):
+    """The four products that follow a decode step's attention, as `ops.FusedProduct`s over random tensors: output
+    projection into the stream, norm + gate/up + SwiGLU, down into the stream, norm + the next layer's QKV with
+    rotation and cache write. Returns (products, state), state holding every tensor that a run changes."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *shape, scale=1.0: (torch.randn(*shape, generator=g) * scale)
+    stream = rnd(rows, hidden).to(device)
+    attended = rnd(rows, heads * head_dim).to(torch.bfloat16).to(device)
+    o_w = rnd(hidden, heads * head_dim, scale=0.05).to(torch.bfloat16).to(device)
+    gu_w = rnd(2 * inter, hidden, scale=0.05).to(torch.bfloat16).to(device)
+    down_w = rnd(hidden, inter, scale=0.05).to(torch.bfloat16).to(device)
+    qkv_w = rnd((heads + 2 * kv_heads) * head_dim, hidden, scale=0.05).to(torch.bfloat16).to(device)
+    qkv_b = rnd((heads + 2 * kv_heads) * head_dim).to(torch.bfloat16).to(device)
+    n1 = (1 + 0.1 * rnd(hidden)).to(torch.bfloat16).to(device)
+    n2 = (1 + 0.1 * rnd(hidden)).to(torch.bfloat16).to(device)
+    pages = Pages(rows, 400, kv_heads, head_dim, device)
+    act = torch.zeros(rows, inter, dtype=torch.bfloat16, device=device)
+    q_out = torch.zeros(rows, heads * head_dim, dtype=torch.bfloat16, device=device)
+    tok_seq = torch.arange(rows, dtype=torch.int32, device=device)
+    tok_pos = torch.tensor([(37 * i + 63) % 390 for i in range(rows)], dtype=torch.int32, device=device)
+    slots = torch.tensor([(rows - 1 - i) if i != 1 else -1 for i in range(rows)], dtype=torch.int32, device=device)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).to(device)
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    products = [
+        ops.FusedProduct(ops.EPI_RESIDUAL, o_w, x=attended, residual=stream),
+        ops.FusedProduct(ops.EPI_SWIGLU, gu_w, hidden=stream, norm_weight=n1, eps=1e-6, out=act),
+        ops.FusedProduct(ops.EPI_RESIDUAL, down_w, x=act, residual=stream),
+        ops.FusedProduct(ops.EPI_QKV, qkv_w, hidden=stream, norm_weight=n2, eps=1e-6, bias=qkv_b,
+                         qkv=dict(n_heads=heads, site=pages.args(), inv_freq=inv_freq, rot_dim=head_dim, tok_pos=tok_pos,
+                                  tok_seq=tok_seq, slots=slots, q_out=q_out, write_cache=True, err=err)),
+    ]
+    return products, dict(stream=stream, act=act, q_out=q_out, cache=pages.storage, err=err)
+
+
+def graph_time_us(fn, per: int, replays: int = 30) -> float:
+    """Microseconds per unit of work: `fn` captured into a CUDA graph once, replayed `replays` times between events."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        fn()
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        fn()
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / replays / per * 1e3
+
+
+def unfused(product: ops.FusedProduct, err: torch.Tensor) -> None:
+    """The same product by the unfused kernels: norm kernel, library product, elementwise kernel."""
+    t = product.tensors
+    if "hidden" in t:
+        x = torch.empty(t["hidden"].shape, dtype=torch.bfloat16, device=t["hidden"].device)
+        ops.add_rms_norm(t["hidden"], None, t["norm_weight"], t["eps"], x)
+    else:
+        x = t["x"]
+    y = ops.linear(x, product.weight)
+    if product.epilogue == ops.EPI_SWIGLU:
+        ops.swiglu(y, t["out"])
+    elif product.epilogue == ops.EPI_QKV:
+        q = t["qkv"]
+        ops.rope_cache_write(y, q["tok_seq"], q["tok_pos"], q["slots"], q["inv_freq"], q["rot_dim"], q["n_heads"], q["q_out"],
+                             q["site"], True, err, bias=t["bias"])
+    else:
+        ops.residual_add(t["residual"], y)
+
+
+def wide_tensors(product: ops.FusedProduct, x: torch.Tensor) -> dict:
+    """`product`'s keywords for wide_gemm, which wants its rows already normalised: `x` stands for them."""
+    t = dict(product.tensors)
+    if "hidden" in t:
+        for key in ("hidden", "norm_weight", "eps"):
+            t.pop(key)
+        t["x"] = x
+    return t
+
+
+def sizes_of(preset: str):
+    c = preset_config(preset)
+    return c.hidden_size, c.intermediate_size, c.num_attention_heads, c.num_key_value_heads, c.head_dim
+
+
+def measure_products(args) -> None:
+    hidden, inter, heads, kv_heads, head_dim = sizes_of(args.preset)
+    repeat = args.repeat
+    for rows in args.rows:
+        layers = [layer_products(rows, hidden, inter, heads, kv_heads, head_dim, seed=100 + i) for i in range(repeat)]
+        err = layers[0][1]["err"]
+        xs = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(repeat)]
+        for i, name in enumerate(NAMES):
+            line = f"{args.preset} rows {rows:3d} {name:42s}"
+            if rows <= ops.SKINNY_MAX_ROWS:
+                line += f" skinny {graph_time_us(lambda: [layers[l][0][i].run() for l in range(repeat)], repeat):7.2f} us"
+            p0 = layers[0][0][i]
+            if rows <= ops.WIDE_MAX_ROWS and ops.wide_gemm_takes(p0.epilogue, p0.weight, **wide_tensors(p0, xs[0])):
+                line += f"  wide {graph_time_us(lambda: [ops.wide_gemm(layers[l][0][i].epilogue, layers[l][0][i].weight, **wide_tensors(layers[l][0][i], xs[l])) for l in range(repeat)], repeat):7.2f} us"
+            line += f"  unfused {graph_time_us(lambda: [unfused(layers[l][0][i], err) for l in range(repeat)], repeat):7.2f} us"
+            print(line, flush=True)
+        if int(err):
+            raise RuntimeError(f"a kernel reported error word {int(err)}")
+
+
+def measure_chain(args) -> None:
+    hidden, inter, heads, kv_heads, head_dim = sizes_of(args.preset)
+    repeat = args.repeat
+    for rows in args.rows:
+        layers = [layer_products(rows, hidden, inter, heads, kv_heads, head_dim, seed=100 + i) for i in range(repeat)]
+        err = layers[0][1]["err"]
+        sync = torch.zeros(2, dtype=torch.int32, device="cuda")
+        if not ops.skinny_chain_takes(layers[0][0]):
+            print(f"{args.preset} rows {rows}: the chain kernel does not take these products")
+            continue
+        for n in (1, 2, 3, 4):
+            separate = graph_time_us(lambda: [p.run() for l in range(repeat) for p in layers[l][0][:n]], repeat)
+            chained = graph_time_us(lambda: [ops.skinny_chain(layers[l][0][:n], sync, err) for l in range(repeat)], repeat)
+            print(f"{args.preset} rows {rows}: first {n} products of a layer: separate kernels {separate:6.2f} us, one persistent kernel "
+                  f"{chained:6.2f} us", flush=True)
+        # the steady state: every layer's products inside ONE launch (stacked weights)
+        products, _ = layer_products(rows, hidden, inter, heads, kv_heads, head_dim, seed=7)
+        keep = []
+        for p in products:
+            stacked = p.weight.unsqueeze(0).repeat(repeat, 1, 1).contiguous()
+            keep.append(stacked)
+            p.weight = stacked[0]
+            for key in ("bias", "norm_weight"):
+                if key in p.tensors:
+                    more = p.tensors[key].unsqueeze(0).repeat(repeat, 1).contiguous()
+                    keep.append(more)
+                    p.tensors[key] = more[0]
+        for first, count in ((0, 4), (0, 1), (1, 1), (2, 1), (3, 1)):
+            chosen = products[first:first + count]
+            steps = [[p.weight.numel() for p in chosen], [p.tensors["bias"].numel() if "bias" in p.tensors else 0 for p in chosen],
+                     [p.tensors["norm_weight"].numel() if "norm_weight" in p.tensors else 0 for p in chosen]]
+            us = graph_time_us(lambda: ops.skinny_chain_repeated(chosen, repeat, steps, sync, err), repeat)
+            what = "all four products" if count == 4 else NAMES[first]
+            print(f"{args.preset} rows {rows}: {repeat} layers inside one launch, {what}: {us:6.2f} us per layer", flush=True)
+        if int(err):
+            raise RuntimeError(f"a kernel reported error word {int(err)}")
+
+
+def measure_phases(args) -> None:
+    from .csrc import library
+    from .ops import kernels
+    hidden, inter, heads, kv_heads, head_dim = sizes_of(args.preset)
+    print("mean microseconds since the first block's entry: set-up done, the kernel before done, first stage arrived, "
+          "products done, sums sent, sums arrived, epilogue done (and the last block's end)")
+    for rows in args.rows:
+        products, state = layer_products(rows, hidden, inter, heads, kv_heads, head_dim)
+        x = torch.randn(rows, hidden, device="cuda").bfloat16()
+        for i, name in enumerate(NAMES):
+            p = products[i]
+            a, _ = kernels._skinny_args(p.epilogue, p.weight, **wide_tensors(p, x))
+            stamps = torch.zeros(1024, 8, dtype=torch.int64, device="cuda")
+            for _ in range(3):
+                stamps.zero_()
+                torch.cuda.synchronize()
+                code = library("wide_gemm").qf_wide_gemm_stamped(ctypes.c_int(p.epilogue), ctypes.byref(a),
+                                                                 ctypes.c_void_p(stamps.data_ptr()), kernels._stream())
+                torch.cuda.synchronize()
+            if code:
+                print(f"{args.preset} rows {rows} {name}: not taken (code {code})")
+                continue
+            st = stamps.cpu()
+            st = st[st[:, 0] > 0]
+            rel = (st - int(st[:, 0].min())).double() / 1e3
+            print(f"{args.preset} rows {rows:3d} {name:42s} blocks {st.shape[0]:3d}: "
+                  + " ".join(f"{float(rel[:, k].mean()):6.2f}" for k in range(1, 8)) + f"  ({float(rel[:, 7].max()):6.2f})", flush=True)
+
+
+def measure_attention(args) -> None:
+    heads, kv_heads, d = args.heads, args.kv_heads, args.head_dim
+    for n in args.tokens:
+        pages = Pages(1, n, kv_heads, d, "cuda", 1)
+        pages.storage.copy_(torch.randn(pages.storage.shape, device="cuda").to(torch.bfloat16))
+        q = torch.randn(n, heads * d, device="cuda").bfloat16()
+        out = torch.empty_like(q)
+        cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+        pos = torch.arange(n, dtype=torch.int32, device="cuda")
+        slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        flops = 4 * heads * d * n * (n + 1) / 2
+        variants = [("mma.sync, a tile's pages by one group of warps", ops.attention_prefill, 64),
+                    ("mma.sync, as the model runs it", ops.attention_prefill, n)]
+        if d in ops.TC_ATTENTION_HEAD_DIMS:
+            variants += [("tcgen05, one block per tile", ops.attention_prefill_tc, 64),
+                         ("tcgen05, as the model runs it", ops.attention_prefill_tc, n)]
+        for name, fn, bound in variants:
+            run = lambda: fn(q, out, cu, pos, slots, pages.args(), heads, 1, n, d ** -0.5, 0, err, max_kv_len=bound)
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(20):
+                run()
+            end.record()
+            torch.cuda.synchronize()
+            us = start.elapsed_time(end) / 20 * 1e3
+            print(f"one prompt of {n} tokens, {heads}/{kv_heads} heads of {d}: {name:46s} {us:7.1f} us  {flops / us / 1e6:5.0f} TFLOP/s", flush=True)
+        if int(err):
+            raise RuntimeError(f"a kernel reported error word {int(err)}")
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="qwenforge_b200.measure", description=__doc__.split("\n\n")[0])
+    p.add_argument("what", choices=["products", "chain", "phases", "attention"])
+    p.add_argument("--preset", default="qwen2.5-0.5b")
+    p.add_argument("--rows", default="8", type=lambda text: [int(v) for v in text.split(",")])
+    p.add_argument("--repeat", type=int, default=12, help="layers, each with weights of its own, captured into one graph")
+    p.add_argument("--tokens", default="2048", type=lambda text: [int(v) for v in text.split(",")])
+    p.add_argument("--heads", type=int, default=14)
+    p.add_argument("--kv-heads", type=int, default=2)
+    p.add_argument("--head-dim", type=int, default=64)
+    args = p.parse_args(argv)
+    ops.require_cuda("cuda", "the measurement")
+    with torch.inference_mode():
+        {"products": measure_products, "chain": measure_chain, "phases": measure_phases, "attention": measure_attention}[args.what](args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -455,6 +455,17 @@ def skinny_gemm_takes(m: int, weight: torch.Tensor, epilogue: int = EPI_PLAIN, n
     return answer
 
 
+def skinny_gemm_pays(m: int, weight: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel is the faster way to run `m` token rows against `weight`, by measurement on
+    a B200 (`python -m qwenforge_b200.measure products`): for weights of 100 MB and more it loses to the norm kernel,
+    the library product and the elementwise kernel together (Qwen2.5-7B's feed-forward, 272 and 136 MB: 57 and 41
+    microseconds against 52 and 30 at 8 rows, 62 and 51 against 52 and 31 at 16), and from 9 rows on already for
+    weights above 64 MB (Qwen2.5-3B's gate/up, 90 MB: 24.4 against 22.3). Everything smaller it wins, the smaller the
+    clearer (0.5B at 8 rows: 2.9 / 5.9 / 4.8 / 4.4 microseconds against 5.1 / 8.6 / 11.0 / 8.3)."""
+    size = weight.numel() * weight.element_size()
+    return size < 100e6 and (m <= 8 or size < 64e6)
+
+
 def _skinny_args(epilogue: int, weight: torch.Tensor, *, x: Optional[torch.Tensor] = None,
                  hidden: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,

@@ -45,16 +45,34 @@ class SwiGlu(FeedForward):
         ops.swiglu(gate_up, act)
         return ops.linear(act, self.down_weight)
 
-    # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another
+    # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another.
+    # Each of the two products takes the weight-streaming kernel where that kernel takes the shape and is the faster
+    # way by measurement (`ops.skinny_gemm_pays`), else the unfused kernels; the results land in the same places.
+    def _fuse(self, ctx):
+        rows = ctx.n_tokens
+        gate_up = (ops.skinny_gemm_takes(rows, self.gate_up_weight, ops.EPI_SWIGLU, True)
+                   and ops.skinny_gemm_pays(rows, self.gate_up_weight))
+        down = (ops.skinny_gemm_takes(rows, self.down_weight, ops.EPI_RESIDUAL, False)
+                and ops.skinny_gemm_pays(rows, self.down_weight))
+        return gate_up, down
+
     def fused_takes(self, ctx) -> bool:
         return (ctx.dtype == torch.bfloat16 and ctx.attention == "auto" and self.inter % 8 == 0
-                and ops.skinny_gemm_takes(ctx.n_tokens, self.gate_up_weight, ops.EPI_SWIGLU, True)
-                and ops.skinny_gemm_takes(ctx.n_tokens, self.down_weight, ops.EPI_RESIDUAL, False))
+                and ctx.n_tokens <= ops.SKINNY_MAX_ROWS and any(self._fuse(ctx)))
 
     def fused_forward(self, hidden, rms, ctx):
+        fuse_gate_up, fuse_down = self._fuse(ctx)
         act = torch.empty((hidden.shape[0], self.inter), dtype=torch.bfloat16, device=hidden.device)
-        ops.skinny_gemm(ops.EPI_SWIGLU, self.gate_up_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1], out=act)
-        ops.skinny_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden)
+        if fuse_gate_up:
+            ops.skinny_gemm(ops.EPI_SWIGLU, self.gate_up_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1], out=act)
+        else:
+            x = torch.empty(hidden.shape, dtype=torch.bfloat16, device=hidden.device)
+            ops.add_rms_norm(hidden, None, rms[0], rms[1], x)
+            ops.swiglu(ops.linear(x, self.gate_up_weight), act)
+        if fuse_down:
+            ops.skinny_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden)
+        else:
+            ops.residual_add(hidden, ops.linear(act, self.down_weight))
 
 
 register_part("feed_forward", "swiglu", SwiGlu)

@@ -19,6 +19,8 @@ WIDE = {
     "w8192": dict(hidden_size=8192, intermediate_size=29568, num_attention_heads=64, num_key_value_heads=8, head_dim=128),
     "w4096": dict(hidden_size=4096, intermediate_size=11008, num_attention_heads=32, num_key_value_heads=32, head_dim=128),
     "w1000": dict(hidden_size=1000, intermediate_size=8000, num_attention_heads=10, num_key_value_heads=2, head_dim=64),
+    # at 9 rows and more this one's gate/up product (90 MB) runs on the unfused kernels while its down product stays fused
+    "w2048": dict(hidden_size=2048, intermediate_size=11008, num_attention_heads=16, num_key_value_heads=2, head_dim=128),
 }
 CHECKED = (0, 7, 8, 15)   # the sequences whose logits are compared (row 0 is in every step, row 15 only in the widest)
 ROW_COUNTS = (16, 9, 8, 1)
