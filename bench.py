@@ -190,9 +190,16 @@ def check_decode_logits(model, cache, folder, batch, context, vocab, torch, rows
             raise AssertionError(f"decode graph logits of row {row} differ from float32 by {err:.3e} (limit {limit:.3e})")
         worst, bound = max(worst, err), max(bound, limit)
     exact.raise_on_kernel_error()
+    del exact_cache
+    # the true 32-bit path's own speed, at a shorter context (its prompt step is slow): the same batch, graph replays
+    short = min(context, 1024)
+    exact_cache = exact.new_cache(batch * (short + 64), batch)
+    fp32_ms, _ = timed_decode(exact, exact_cache, batch, short, 16, 3, vocab, torch)
     del exact, exact_cache
     torch.cuda.empty_cache()
-    return {"max_abs_diff_vs_fp32": round(worst, 5), "limit": round(bound, 5), "rows": rows_checked, "steps_replayed": CHUNK_STEPS}
+    return {"max_abs_diff_vs_fp32": round(worst, 5), "limit": round(bound, 5), "rows": rows_checked, "steps_replayed": CHUNK_STEPS,
+            "fp32_decode_tokens_per_s": round(batch * 1e3 / fp32_ms, 1), "fp32_decode_ms_per_step": round(fp32_ms, 3),
+            "fp32_decode_context": short}
 
 
 # The two larger workloads: 16 prompts of unequal lengths in ONE prompt step, then 256 decode steps, at Qwen2.5-3B layer
