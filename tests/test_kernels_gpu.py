@@ -78,7 +78,7 @@ def test_add_rms_norm(ops, dtype, rows, width, eps):
         assert max_err(out, want) <= tol(dtype) * float(want.float().abs().max())
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (7, 200, 120), (70, 65, 33), (33, 1152, 896), (130, 50, 4864)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (7, 200, 120), (70, 65, 33), (33, 1152, 896), (130, 50, 4864), (16, 301, 1000), (17, 301, 1000)])
 def test_gemm_f32(ops, m, n, k):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(m, k, generator=g).to(DEV)
