@@ -14,6 +14,8 @@ stay in the launch as padding entries (slot -1), which touch no cache and change
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from typing import Optional, Sequence
 
 import torch
@@ -24,6 +26,23 @@ from .step import StepContext
 
 MAX_STOP_IDS = 8
 CHUNK_STEPS = 32
+
+
+@contextlib.contextmanager
+def capturing(graph: torch.cuda.CUDAGraph, stream: torch.cuda.Stream, pool=None):
+    """`torch.cuda.graph` with Python's cycle collector held off meanwhile. Destroying an older graph is a call that
+    CUDA forbids while any stream captures, and it ends the capture with an error; an older graph that sits in a
+    reference cycle is destroyed whenever the collector happens to run, which may be in the middle of this capture.
+    So what is collectable goes first, and the collector waits until the capture has ended."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, stream=stream, pool=pool):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 def length_bound(n: int) -> int:
@@ -99,7 +118,7 @@ class DecodeGraph:
         torch.cuda.synchronize()
         before = ops.kernels.launches
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        with capturing(graph, stream):
             self._one_step()
         self.kernels_per_step = ops.kernels.launches - before
         self.graph = graph
@@ -205,7 +224,7 @@ class PrefillGraphs:
         torch.cuda.synchronize()
         before = ops.kernels.launches
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream, pool=self.pool):
+        with capturing(graph, stream, self.pool):
             logits = model.forward(ctx, cache)
         if self.pool is None:
             self.pool = graph.pool()

@@ -9,7 +9,8 @@ attention kernels compare. Every figure is the mean of CUDA-graph replays timed 
     python -m qwenforge_b200.measure attention --tokens 1024,2048,4096 --heads 14 --kv-heads 2 --head-dim 64
 
 products   per product of a layer (output projection, gate/up, down, query/key/value): the weight-streaming kernel of
-           skinny_gemm.cu (rows <= 16), the tcgen05 kernel of wide_gemm.cu (rows <= 64), and the unfused kernels
+           skinny_gemm.cu (rows <= 16), the tcgen05 kernel of wide_gemm.cu (rows <= 64; after the norm kernel where the
+           product normalises its rows), and the unfused kernels
 chain      the four products after attention as separate kernels, as ONE persistent kernel per layer
            (skinny_chain.cu), and all layers' products inside one launch (the persistent kernel's steady state)
 phases     wide_gemm.cu's own time stamps: when a block's copies, products, exchange and epilogue end
@@ -26,6 +27,7 @@ import torch
 from . import ops
 from .cache import PAGE_TOKENS
 from .config import preset_config
+from .engine.graphs import capturing
 
 NAMES = ("output projection (residual)", "gate/up (norm, SwiGLU)", "down (residual)", "query/key/value (norm, rotation, cache)")
 
@@ -86,7 +88,7 @@ def graph_time_us(fn, per: int, replays: int = 30) -> float:
         fn()
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
+    with capturing(graph, stream):
         fn()
     for _ in range(5):
         graph.replay()
@@ -120,13 +122,21 @@ def unfused(product: ops.FusedProduct, err: torch.Tensor) -> None:
 
 
 def wide_tensors(product: ops.FusedProduct, x: torch.Tensor) -> dict:
-    """`product`'s keywords for wide_gemm, which wants its rows already normalised: `x` stands for them."""
+    """`product`'s keywords for wide_gemm, which wants its rows already normalised: `x` receives them."""
     t = dict(product.tensors)
     if "hidden" in t:
         for key in ("hidden", "norm_weight", "eps"):
             t.pop(key)
         t["x"] = x
     return t
+
+
+def wide(product: ops.FusedProduct, x: torch.Tensor) -> None:
+    """The product by wide_gemm.cu, after the norm kernel where the product normalises its rows."""
+    t = product.tensors
+    if "hidden" in t:
+        ops.add_rms_norm(t["hidden"], None, t["norm_weight"], t["eps"], x)
+    ops.wide_gemm(product.epilogue, product.weight, **wide_tensors(product, x))
 
 
 def sizes_of(preset: str):
@@ -147,7 +157,7 @@ def measure_products(args) -> None:
                 line += f" skinny {graph_time_us(lambda: [layers[l][0][i].run() for l in range(repeat)], repeat):7.2f} us"
             p0 = layers[0][0][i]
             if rows <= ops.WIDE_MAX_ROWS and ops.wide_gemm_takes(p0.epilogue, p0.weight, **wide_tensors(p0, xs[0])):
-                line += f"  wide {graph_time_us(lambda: [ops.wide_gemm(layers[l][0][i].epilogue, layers[l][0][i].weight, **wide_tensors(layers[l][0][i], xs[l])) for l in range(repeat)], repeat):7.2f} us"
+                line += f"  wide {graph_time_us(lambda: [wide(layers[l][0][i], xs[l]) for l in range(repeat)], repeat):7.2f} us"
             line += f"  unfused {graph_time_us(lambda: [unfused(layers[l][0][i], err) for l in range(repeat)], repeat):7.2f} us"
             print(line, flush=True)
         if int(err):

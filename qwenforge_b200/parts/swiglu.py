@@ -26,7 +26,7 @@ class SwiGlu(FeedForward):
         ]
 
     def kernel_libraries(self, dtype):
-        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm", "tc_gemm"})
+        return {"activation"} | ({"gemm_f32"} if dtype == torch.float32 else {"skinny_gemm", "tc_gemm", "wide_gemm"})
 
     def bind(self, tensors, dtype, device):
         self.gate_up_weight = torch.cat((tensors[self.file_name("gate_weight")], tensors[self.file_name("up_weight")]),
@@ -46,31 +46,39 @@ class SwiGlu(FeedForward):
         return ops.linear(act, self.down_weight)
 
     # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another.
-    # Each of the two products takes the weight-streaming kernel where that kernel takes the shape and is the faster
-    # way by measurement (`ops.skinny_gemm_pays`), else the unfused kernels; the results land in the same places.
-    def _fuse(self, ctx):
+    # Each of the two products goes the way that is fastest by measurement (`python -m qwenforge_b200.measure products`):
+    # the weight-streaming kernel where it takes the shape and pays (`ops.skinny_gemm_pays`); for a down product of
+    # 100 MB and more the tcgen05 kernel of wide_gemm.cu (Qwen2.5-7B sizes: 28 microseconds against 41 to 51 in the
+    # weight-streaming kernel and 31 unfused); else the unfused kernels. The results land in the same places.
+    def _ways(self, ctx):
         rows = ctx.n_tokens
-        gate_up = (ops.skinny_gemm_takes(rows, self.gate_up_weight, ops.EPI_SWIGLU, True)
-                   and ops.skinny_gemm_pays(rows, self.gate_up_weight))
-        down = (ops.skinny_gemm_takes(rows, self.down_weight, ops.EPI_RESIDUAL, False)
-                and ops.skinny_gemm_pays(rows, self.down_weight))
+        gate_up = "unfused"
+        if ops.skinny_gemm_takes(rows, self.gate_up_weight, ops.EPI_SWIGLU, True) and ops.skinny_gemm_pays(rows, self.gate_up_weight):
+            gate_up = "skinny"
+        down = "unfused"
+        if ops.skinny_gemm_takes(rows, self.down_weight, ops.EPI_RESIDUAL, False) and ops.skinny_gemm_pays(rows, self.down_weight):
+            down = "skinny"
+        elif self.down_weight.numel() * 2 >= 100e6 and self.hidden % 8 == 0:
+            down = "wide"
         return gate_up, down
 
     def fused_takes(self, ctx) -> bool:
         return (ctx.dtype == torch.bfloat16 and ctx.attention == "auto" and self.inter % 8 == 0
-                and ctx.n_tokens <= ops.SKINNY_MAX_ROWS and any(self._fuse(ctx)))
+                and ctx.n_tokens <= ops.SKINNY_MAX_ROWS and self._ways(ctx) != ("unfused", "unfused"))
 
     def fused_forward(self, hidden, rms, ctx):
-        fuse_gate_up, fuse_down = self._fuse(ctx)
+        gate_up, down = self._ways(ctx)
         act = torch.empty((hidden.shape[0], self.inter), dtype=torch.bfloat16, device=hidden.device)
-        if fuse_gate_up:
+        if gate_up == "skinny":
             ops.skinny_gemm(ops.EPI_SWIGLU, self.gate_up_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1], out=act)
         else:
             x = torch.empty(hidden.shape, dtype=torch.bfloat16, device=hidden.device)
             ops.add_rms_norm(hidden, None, rms[0], rms[1], x)
             ops.swiglu(ops.linear(x, self.gate_up_weight), act)
-        if fuse_down:
+        if down == "skinny":
             ops.skinny_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden)
+        elif down == "wide" and ops.wide_gemm_takes(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden):
+            ops.wide_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden, err=ctx.err)
         else:
             ops.residual_add(hidden, ops.linear(act, self.down_weight))
 

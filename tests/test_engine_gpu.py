@@ -278,6 +278,53 @@ def test_far_key_through_the_tensor_core_kernels(case, tcgen05, tmp_path, monkey
     assert_logits_close(torch.cat(got), ref, torch.bfloat16, f"{case}: sharp attention over far keys")
 
 
+def test_a_capture_survives_the_cycle_collector(folders):
+    """An older graph that sits in a reference cycle is destroyed when Python's cycle collector runs; CUDA forbids that
+    call while a stream captures and ends the capture with an error. Here such a cycle is made and dropped in the
+    middle of a capture, and enough young objects follow it for the collector to run: the capture must hold it off."""
+    import gc
+
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.engine.graphs import DecodeGraph
+    from qwenforge_b200.sampling import Sampler
+    model = Model.from_dir(folders["tiny_a"][0], torch.bfloat16, "cuda")
+    cache = model.new_cache(512, 2)
+    old = torch.cuda.CUDAGraph()
+    counter = torch.zeros(8, device="cuda")
+    with torch.cuda.graph(old, stream=torch.cuda.Stream()):
+        counter += 1
+    holder = [old]
+    del old
+    graph = DecodeGraph(model, cache, 2, 256, Sampler())
+    calls, young = [], []
+
+    def let_go(index, hidden, delta):
+        calls.append(index)
+        if len(calls) == 2 * (len(model.spec.schedule) + 1) + 1:   # the first call of the third step: the captured one
+            ring = [holder.pop()]
+            ring.append(ring)   # a cycle: only the collector frees it
+            del ring
+        young.extend([] for _ in range(200))
+
+    saved = gc.get_threshold()
+    model.observer = let_go
+    try:
+        gc.set_threshold(50, 1000, 1000)
+        graph.capture()
+    finally:
+        gc.set_threshold(*saved)
+        model.observer = None
+    assert not holder and len(calls) == 3 * (len(model.spec.schedule) + 1)
+    slot = cache.open()
+    cache.reserve([(slot, 8)])
+    model.step(cache, [(slot, [3, 1, 4])])
+    cache.flush()
+    graph.load([slot], [5], [3], [1], [1 << 30], [0], [])
+    graph.run(1)
+    model.raise_on_kernel_error()
+    assert torch.isfinite(graph.last_logits).all()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_greedy_generation_through_entry_point(folders, name, dtype):
@@ -304,6 +351,32 @@ def test_greedy_generation_through_entry_point(folders, name, dtype):
     texts = engine.generate(["hello", "a b c"], max_new_tokens=4, batch_size=2)
     assert isinstance(texts, list) and len(texts) == 2 and all(isinstance(t, str) and t for t in texts)
     assert engine.generate([], 4) == [] and engine.generate(["x"], 0) == [""]
+
+
+@pytest.mark.parametrize("preset,seed,lengths,steps", [("tiny-a", 0, (5, 11, 17), 8), ("tiny-b", 1, (1, 7, 19, 33), 12)])
+def test_the_two_tiny_workloads_as_they_are_written(preset, seed, lengths, steps, tmp_path):
+    """The two tiny configurations exactly as the package's presets hold them (maximum positions 128 and 256), weights
+    from the package's random mode with the workload's seed, the workload's batch of unequal prompts and decode steps,
+    float32: the tokens and the logits of the plain implementation."""
+    from qwenforge_b200.config import preset_config
+    from qwenforge_b200.engine import Model, StudentEngine
+    from qwenforge_b200.weights import SafetensorsFile, write_random_model
+    config = preset_config(preset)
+    write_random_model(config, seed, tmp_path, torch.float32)
+    with SafetensorsFile(tmp_path / "model.safetensors") as f:
+        weights = {name: f.tensor(name) for name in f.names()}
+    data = config.to_dict()
+    prompts = [random_tokens(config.vocab_size, n, 40 + n) for n in lengths]
+    engine = StudentEngine(str(tmp_path), device="cuda", dtype="float32")
+    got = engine.generate_ids(prompts, steps + 1, batch_size=len(prompts), ignore_eos=True)
+    want = [plain.greedy_generate(data, weights, p, steps + 1) for p in prompts]
+    assert got == want
+    model = Model.from_dir(tmp_path, torch.float32, "cuda")
+    cache = model.new_cache(64 * len(prompts), len(prompts))
+    slots = [cache.open() for _ in prompts]
+    logits = model.step(cache, list(zip(slots, prompts)))
+    for row, p in enumerate(prompts):
+        assert_logits_close(logits[row:row + 1], plain.forward_logits(data, weights, p)[-1:], torch.float32, f"{preset} prompt {len(p)}")
 
 
 def test_temperature_sampling_is_independent_of_batching(folders):
