@@ -15,14 +15,16 @@ stay in the launch as padding entries (slot -1), which touch no cache and change
 from __future__ import annotations
 
 import contextlib
+import dataclasses
 import gc
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..sampling import Sampler
-from .step import StepContext
+from .step import StepContext, pack_step
 
 MAX_STOP_IDS = 8
 CHUNK_STEPS = 32
@@ -164,15 +166,19 @@ class PrefillGraphs:
     A step of a few thousand tokens of a small model is bound by the host: two hundred launches take longer to issue
     than to run. What fixes those launches is the step's shape (tokens, entries, longest entry, wanted rows) and
     the cache it works on; everything else (token ids, positions, slots, page tables) is data in device buffers.
-    The second step of a shape is captured, with its integers in a buffer of the graph's own; every later one
-    copies its integers there and replays. Steps of more than `MAX_TOKENS` tokens are bound by the GPU and are
-    left alone, as are single-token steps (the decode graphs' business). The newest `keep` graphs are kept; they
-    share one memory pool, since no two run at the same time.
+    So that prompts of any length meet a shape that came before, a step is first brought to a rounded shape: one
+    padding entry (slot -1: computed, touches no cache, changes no result) fills its token count up to the next
+    multiple of a granule (64 tokens up to 512, then 128, 256 and 512: at most an eighth more work), and the longest
+    entry is rounded up likewise (blocks of rows that no entry has end at once). A step whose token count is a
+    multiple of the granule already gets no padding entry. The second step of a rounded shape is captured, with its
+    integers in a buffer of the graph's own; every later one copies its integers there and replays. Steps of more
+    than `MAX_TOKENS` tokens are bound by the GPU and are left alone, as are single-token steps (the decode graphs'
+    business). The newest `keep` graphs are kept; they share one memory pool, since no two run at the same time.
     """
 
     MAX_TOKENS = 8192
 
-    def __init__(self, model, keep: int = 8):
+    def __init__(self, model, keep: int = 24):
         self.model, self.keep = model, keep
         self.seen: dict = {}     # shape -> how often it came
         self.graphs: dict = {}   # shape -> (graph, integer buffer, logits); newest last
@@ -182,9 +188,27 @@ class PrefillGraphs:
     def takes(self, step) -> bool:
         return 1 < step.max_q_len and step.n_tokens <= self.MAX_TOKENS
 
-    def run(self, cache, step) -> Optional[torch.Tensor]:
-        """The step's logits by replay, or None if this shape has no graph yet (the caller then runs it as usual;
-        the second time a shape comes it is captured here and its logits are returned)."""
+    @staticmethod
+    def granule(n_tokens: int) -> int:
+        return 64 if n_tokens <= 512 else 128 if n_tokens <= 2048 else 256 if n_tokens <= 4096 else 512
+
+    @classmethod
+    def rounded(cls, step, triples, want):
+        """The step brought to its rounded shape (see the class): the same entries and wanted places, then one padding
+        entry if the token count is no multiple of the granule; the bounds on the longest entry rounded up."""
+        g = cls.granule(step.n_tokens)
+        pad = -step.n_tokens % g
+        if pad:
+            triples = list(triples) + [(-1, 0, np.zeros(pad, dtype=np.int32))]
+            want = None if want is None else list(want) + [[]]
+            step = pack_step(triples, want)
+        up = lambda n: -(-n // g) * g
+        return dataclasses.replace(step, max_q_len=up(step.max_q_len), max_kv_len=up(step.max_kv_len))
+
+    def run(self, cache, step, triples, want) -> Optional[torch.Tensor]:
+        """The step's logits by replay, or None if its rounded shape has no graph yet (the caller then runs the step
+        as it is; the second time a rounded shape comes it is captured here and its logits are returned)."""
+        step = self.rounded(step, triples, want)
         key = (cache.serial,) + step.shape_key
         held = self.graphs.pop(key, None)
         if held is None:

@@ -167,7 +167,7 @@ class Model:
         logits, replayed = None, False
         if self.prefill_graphs is not None and not extras and self.prefill_graphs.takes(step):
             before = self.prefill_graphs.replays
-            logits = self.prefill_graphs.run(cache, step)
+            logits = self.prefill_graphs.run(cache, step, triples, want)
             replayed = self.prefill_graphs.replays > before
         if not replayed:
             # from pageable memory the copy is complete when the call returns, so the host array may go

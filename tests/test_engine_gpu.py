@@ -278,6 +278,39 @@ def test_far_key_through_the_tensor_core_kernels(case, tcgen05, tmp_path, monkey
     assert_logits_close(torch.cat(got), ref, torch.bfloat16, f"{case}: sharp attention over far keys")
 
 
+def test_prompts_of_new_lengths_replay_a_rounded_shape(folders):
+    """A prompt whose length never came before replays the graph of its rounded shape (a padding entry fills it up):
+    the logits are the plain implementation's, the padding leaves no trace in the cache, and a continuation over the
+    same slots reads what the replays wrote."""
+    from qwenforge_b200.engine import Model
+    name = "small_64"
+    model = Model.from_dir(folders[name][0], torch.bfloat16, "cuda")
+    model.enable_prefill_graphs()
+    vocab = ALL_CONFIGS[name]["vocab_size"]
+    cache = model.new_cache(4096, 4)
+    held = []
+    for turn, (na, nb) in enumerate([(150, 70), (133, 101), (158, 49), (140, 97)]):   # 220 .. 237 tokens: all 256 rounded
+        a, b = random_tokens(vocab, na, 1200 + turn), random_tokens(vocab, nb, 1210 + turn)
+        sa, sb = cache.open(), cache.open()
+        places = [[0, na // 3, na - 1], [0, nb // 2, nb - 2, nb - 1]]
+        logits = model.step(cache, [(sa, a), (sb, b)], want=places)
+        model.raise_on_kernel_error()
+        assert_logits_close(logits[:3], plain_logits(folders, name, a)[places[0]], torch.bfloat16, f"rounded turn {turn} a")
+        assert_logits_close(logits[3:], plain_logits(folders, name, b)[places[1]], torch.bfloat16, f"rounded turn {turn} b")
+        assert cache.lengths[sa] == na and cache.lengths[sb] == nb
+        if turn < 3:
+            cache.close(sa)
+            cache.close(sb)
+        else:
+            held = [(sa, a), (sb, b)]
+    assert model.prefill_graphs.replays == 3 and len(model.prefill_graphs.graphs) == 1
+    more = [random_tokens(vocab, 5, 1230), random_tokens(vocab, 9, 1231)]
+    logits = model.step(cache, [(held[0][0], more[0]), (held[1][0], more[1])])
+    model.raise_on_kernel_error()
+    for row, ((_, first), rest) in enumerate(zip(held, more)):
+        assert_logits_close(logits[row:row + 1], plain_logits(folders, name, first + rest)[-1:], torch.bfloat16, f"rounded continuation {row}")
+
+
 def test_a_capture_survives_the_cycle_collector(folders):
     """An older graph that sits in a reference cycle is destroyed when Python's cycle collector runs; CUDA forbids that
     call while a stream captures and ends the capture with an error. Here such a cycle is made and dropped in the

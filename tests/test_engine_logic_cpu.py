@@ -172,7 +172,7 @@ def test_prompt_graphs_decisions_without_a_gpu():
     captured = []
 
     def fake_capture(self, cache, step):
-        if step.n_tokens == 13:
+        if step.host_q_lens[0] == 13:
             raise RuntimeError("no memory")
         graph = FakeGraph()
         captured.append((cache.serial, step.shape_key, graph))
@@ -181,21 +181,49 @@ def test_prompt_graphs_decisions_without_a_gpu():
     graphs = PrefillGraphs(model=types.SimpleNamespace(), keep=2)
     graphs._capture = types.MethodType(fake_capture, graphs)
     cache_a, cache_b = types.SimpleNamespace(serial=1), types.SimpleNamespace(serial=2)
-    step = lambda lens, slot0=0: pack_step([(slot0 + i, 0, list(range(n))) for i, n in enumerate(lens)], None)
+    triples = lambda lens, slot0=0: [(slot0 + i, 0, list(range(n))) for i, n in enumerate(lens)]
+    step = lambda lens, slot0=0: pack_step(triples(lens, slot0), None)
+    run = lambda cache, lens, slot0=0: graphs.run(cache, step(lens, slot0), triples(lens, slot0), None)
 
     assert not graphs.takes(step([1, 1])) and graphs.takes(step([2, 1])) and not graphs.takes(step([9000]))
-    assert graphs.run(cache_a, step([5, 3])) is None and not captured           # first of its shape: launch by launch
-    out = graphs.run(cache_a, step([5, 3], slot0=4))                             # second: captured and replayed
+    assert run(cache_a, [50, 30]) is None and not captured                       # first of its shape: launch by launch
+    out = run(cache_a, [45, 33], slot0=4)                                        # second (other lengths, same rounded shape): captured and replayed
     assert out is not None and out.shape == (2, 4) and len(captured) == 1 and captured[0][2].replayed == 1
-    held_integers = graphs.graphs[(1, 8, 2, 5, 2)][1]
-    assert held_integers.tolist() == step([5, 3], slot0=4).packed.tolist()      # the replay's own integers went in
-    graphs.run(cache_a, step([5, 3]))
+    assert captured[0][1] == (128, 3, 64, 2)
+    held_integers = graphs.graphs[(1, 128, 3, 64, 2)][1]
+    padded = pack_step(triples([45, 33], 4) + [(-1, 0, [0] * 50)], None)
+    assert held_integers.tolist() == padded.packed.tolist()                      # the replay's own integers went in, padding entry last
+    run(cache_a, [64, 1])
     assert captured[0][2].replayed == 2 and graphs.replays == 2 and len(captured) == 1
-    assert graphs.run(cache_b, step([5, 3])) is None                             # another cache: its own count
-    assert graphs.run(cache_a, step([4, 4])) is None                             # same tokens, another longest entry
-    for lens in ([6, 1], [7, 1]):
-        graphs.run(cache_a, step(lens))
-        graphs.run(cache_a, step(lens))
-    assert len(graphs.graphs) == 2 and (1, 8, 2, 5, 2) not in graphs.graphs      # the oldest graph was dropped
-    assert graphs.run(cache_a, step([13])) is None and graphs.run(cache_a, step([13])) is None
-    assert graphs.run(cache_a, step([13])) is None and len(captured) == 3       # the failed capture is not tried again
+    assert run(cache_b, [50, 30]) is None                                        # another cache: its own count
+    assert run(cache_a, [70, 10]) is None                                        # same tokens, a longer longest entry
+    assert run(cache_a, [64, 64]) is None                                        # a full granule: no padding entry, a shape of its own
+    for lens in ([130, 1], [200, 1]):
+        run(cache_a, lens)
+        run(cache_a, lens)
+    assert len(graphs.graphs) == 2 and (1, 128, 3, 64, 2) not in graphs.graphs   # the oldest graph was dropped
+    assert run(cache_a, [13]) is None and run(cache_a, [13]) is None
+    assert run(cache_a, [13]) is None and len(captured) == 3                     # the failed capture is not tried again
+
+
+def test_prompt_steps_are_rounded_to_shapes_that_come_back():
+    """Prompt steps replay a graph when their rounded shape came before: token counts go up to the next multiple of
+    the granule through ONE padding entry, the bound on the longest entry likewise, and nothing else changes."""
+    from qwenforge_b200.engine.graphs import PrefillGraphs
+    from qwenforge_b200.engine.step import pack_step
+    assert [PrefillGraphs.granule(n) for n in (2, 512, 513, 2048, 2049, 4096, 4097, 8192)] == [64, 64, 128, 128, 256, 256, 512, 512]
+    triples = [(3, 0, list(range(100))), (1, 7, list(range(30)))]
+    want = [[0, 99], [29]]
+    step = pack_step(triples, want)
+    rounded = PrefillGraphs.rounded(step, triples, want)
+    assert rounded.shape_key == (192, 3, 128, 3)
+    assert rounded.host_slots == [3, 1, -1] and rounded.host_q_lens == [100, 30, 62] and rounded.max_kv_len == 128
+    n = step.n_tokens
+    assert list(rounded.packed[:n]) == list(step.packed[:n]) and not rounded.packed[n:192].any()      # ids, then zeros
+    assert list(rounded.packed[-3:]) == list(step.packed[-3:])                                          # the wanted rows
+    assert step.max_q_len == 100                                                                        # the step itself is left alone
+    other = [(0, 0, list(range(90))), (2, 0, list(range(41)))]
+    assert PrefillGraphs.rounded(pack_step(other, None), other, None).shape_key == (192, 3, 128, 2)
+    exact = [(0, 0, list(range(128)))]
+    same = PrefillGraphs.rounded(pack_step(exact, None), exact, None)
+    assert same.shape_key == (128, 1, 128, 1) and same.host_slots == [0]
