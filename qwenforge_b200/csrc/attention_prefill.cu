@@ -21,7 +21,7 @@ template <int D, int G>
 __global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
-                     float scale_log2, int window, int* err) {
+                     int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err) {
     constexpr int LD = D + 8;
     constexpr int KS = D / 16;
     constexpr int NT = D / 8;
@@ -29,9 +29,17 @@ prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const i
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][G][64][LD]
     bf16* v_s = k_s + 2 * G * QF_PAGE * LD;         // [2][G][64][LD]
 
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // Which (tile, head, sequence) this block serves. Tiles further down a prompt walk more pages, and the SMs hold
+    // several blocks each, so what counts is that the blocks that share an SM have about the same work together:
+    // blocks are taken in waves of `wave` (one block per SM), the first wave gets the longest tiles in falling order,
+    // the second the next longest in rising order, and so on, so that the block that follows a long tile onto the same
+    // SM is a short one.
+    const int total = (int)gridDim.x, w = blockIdx.x / wave, j = blockIdx.x % wave;
+    const int in_wave = min(wave, total - w * wave);
+    const int item = w * wave + ((w & 1) ? in_wave - 1 - j : j);
+    const int per_tile = n_heads * n_seqs;
+    const int tile = n_tiles - 1 - item / per_tile, head = (item % per_tile) % n_heads, seq = (item % per_tile) / n_heads;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-    const int tile = gridDim.x - 1 - blockIdx.x;    // long rows first
     const int row0 = tile * PF_BM;
     if (row0 >= q_len) return;
     const int n_rows = min(PF_BM, q_len - row0);
@@ -275,41 +283,47 @@ static int launch_groups(const void* q, void* out, const int* cu_q, const int* t
     if (smem < merge) smem = merge;
     cudaError_t e = cudaFuncSetAttribute(prefill_flash_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((max_q_len + PF_BM - 1) / PF_BM, n_heads, n_seqs);
-    prefill_flash_kernel<D, G><<<grid, PF_THREADS * G, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site, n_heads,
-                                                                         scale * 1.4426950408889634f, window, err);
+    const int n_tiles = (max_q_len + PF_BM - 1) / PF_BM;
+    const long long blocks = (long long)n_tiles * n_heads * n_seqs;
+    if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    prefill_flash_kernel<D, G><<<(unsigned)blocks, PF_THREADS * G, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site,
+                                                                                     n_heads, n_seqs, n_tiles, qf_sm_count(),
+                                                                                     scale * 1.4426950408889634f, window, err);
     return (int)cudaGetLastError();
 }
 
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
                   const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
+                  int n_tokens, int max_q_len, int max_kv_len, float scale, int window, int* err, cudaStream_t stream) {
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
-    // Two groups of warps per tile when tiles walk many pages and there are too few tiles to give every SM two blocks
-    // (a short continuation over a long cache, one short prompt): a tile's chain of pages is then half as long.
-    // With more tiles the SMs are busy anyway; measured on a 2,048-token prompt of 14 heads (448 tiles), two groups
-    // were no faster than one (3.63 against 3.53 ms for the whole prompt step).
-    const long long tiles = (long long)((max_q_len + PF_BM - 1) / PF_BM) * n_heads * n_seqs;
+    // Two groups of warps per tile when tiles walk many pages and all tiles find room on the SMs at once (a short
+    // continuation over a long cache, one prompt of a few thousand tokens): what bounds the kernel then is the longest
+    // tile's chain of pages, which two groups halve. With more tiles than room, the SMs are busy anyway and one group
+    // per tile wastes nothing. Measured on one prompt of 2,048 tokens, 14 heads of 64 (448 tiles, room for 592): 55.5
+    // microseconds with one group, 41.6 with two; 16 heads of 128 (512 tiles, room for 296): 73 against 94.
+    // (tiles that hold rows: the grid also has blocks for the rows that shorter sequences lack, which end at once)
+    const long long tiles = (long long)min((max_q_len + PF_BM - 1) / PF_BM * n_seqs, n_tokens / PF_BM + n_seqs) * n_heads;
     const int span = window > 0 && window + PF_BM < max_kv_len ? window + PF_BM : max_kv_len;
-    const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * 2;
+    const bool split = span >= 8 * QF_PAGE && tiles < (long long)qf_sm_count() * (D <= 64 ? 4 : 2);
     return split ? launch_groups<D, 2>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
                  : launch_groups<D, 1>(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
 }
 
-// The arguments of the generic attention kernel and `max_kv_len`, an upper bound of any sequence's length after this
-// step (it only steers how a tile's pages are shared among warps); bf16 only. cudaErrorInvalidValue for a head size without an
+// The arguments of the generic attention kernel, `n_tokens` (the rows of q: all sequences' new tokens) and `max_kv_len`,
+// an upper bound of any sequence's length after this step (both only steer how a tile's pages are shared among warps);
+// bf16 only. cudaErrorInvalidValue for a head size without an
 // instantiation (the caller then uses the generic kernel).
 QF_EXPORT int qf_attention_prefill(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
                                    void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                   int head_dim, int n_heads, int n_seqs, int max_q_len, int max_kv_len, float scale,
-                                   int window, int* err, cudaStream_t stream) {
+                                   int head_dim, int n_heads, int n_seqs, int n_tokens, int max_q_len, int max_kv_len,
+                                   float scale, int window, int* err, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                 \
     case DIM:                                                                                                        \
         return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads,  \
-                           n_seqs, max_q_len, max_kv_len, scale, window, err, stream);
+                           n_seqs, n_tokens, max_q_len, max_kv_len, scale, window, err, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)

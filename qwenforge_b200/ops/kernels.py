@@ -246,8 +246,9 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         raise KernelError("attention_prefill: q/out widths do not match the head count")
     _check(library("attention_prefill").qf_attention_prefill(
         _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
-        _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(max_q_len),
-        _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()), "attention_prefill")
+        _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _I(q.shape[0]),
+        _I(max_q_len), _I(1 << 30 if max_kv_len is None else int(max_kv_len)), _F(scale), _I(window), _ptr(err), _stream()),
+        "attention_prefill")
 
 
 TC_ATTENTION_HEAD_DIMS = (64, 128)
