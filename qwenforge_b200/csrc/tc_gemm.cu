@@ -160,6 +160,195 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem_acc), "r"(BN));
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// The persistent form, for products of many tiles: one block per SM walks tiles of 128 x 256 (tile index = block,
+// block + blocks, ...; neighbouring blocks work on the same 256 weight rows, which the L2 then serves). The ring of
+// stages runs on across tiles, and the accumulator is double: while the tensor cores fill one half of tensor memory
+// (256 columns) with a tile's sums, eight epilogue warps read the other half, so a tile's epilogue and the start of
+// the next tile's copies hide under products. Warp 0 issues copies, warp 1 products, warps 2 to 9 own the epilogue:
+// warp w reads accumulator lanes 32 (w % 4) .. + 31 (the lanes a warp may read are fixed by its number) and one half
+// of the tile's columns.
+#define TP_THREADS 320
+#define TP_EPI_WARPS 8
+#define TP_BN 256
+#define TP_STAGES 4
+#define TP_STAGE_BYTES ((TC_BM + TP_BN) * TC_BK * 2)
+
+__device__ __forceinline__ float fast_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <int EPI>
+__global__ void __launch_bounds__(TP_THREADS, 1)
+tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          bf16* __restrict__ out, int M, int n_out, int K, int inter, int ldo, int m_tiles, int n_tiles, int* err) {
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+    constexpr int HALF = TP_BN / 2;  // TC_SWIGLU: gate columns [0, HALF), up columns [HALF, BN)
+    __shared__ __align__(8) uint64_t full_bar[TP_STAGES], empty_bar[TP_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_k = (K + TC_BK - 1) / TC_BK, total = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TP_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], TP_EPI_WARPS);
+        }
+    }
+    if (warp == 0) {  // both accumulators: all 512 columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_s)), "r"(2 * TP_BN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // ---- copies: all lanes run the loops, one issues
+        const bool leader = elect_one();
+        int it = 0;
+        for (int t = blockIdx.x; t < total && !timed_out; t += gridDim.x) {
+            const int tile_m = t % m_tiles, tile_n = t / m_tiles;
+            for (int kb = 0; kb < n_k; ++kb, ++it) {
+                const int s = it % TP_STAGES;
+                if (it >= TP_STAGES && !__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((it / TP_STAGES) - 1) & 1))) {
+                    timed_out = true;
+                    break;
+                }
+                if (leader) {
+                    unsigned char* a_s = smem + (size_t)s * TP_STAGE_BYTES;
+                    unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
+                    mbar_expect_tx(&full_bar[s], TP_STAGE_BYTES);
+                    tma_load_2d(a_s, &map_a, kb * TC_BK, tile_m * TC_BM, &full_bar[s]);
+#pragma unroll
+                    for (int box = 0; box < TP_BN / 64; ++box) {  // boxes of 64 weight rows
+                        int w_row = tile_n * TP_BN + 64 * box;
+                        if (EPI == TC_SWIGLU)  // HALF gate rows, then the HALF matching up rows
+                            w_row = 64 * box < HALF ? tile_n * HALF + 64 * box : inter + tile_n * HALF + (64 * box - HALF);
+                        tma_load_2d(b_s + (size_t)box * 64 * TC_BK * 2, &map_b, kb * TC_BK, w_row, &full_bar[s]);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ---- products
+        const bool leader = elect_one();
+        int it = 0, i = 0;
+        for (int t = blockIdx.x; t < total && !timed_out; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            if (i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((i >> 1) - 1) & 1))) {  // the epilogue has read this half
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t acc = tmem + (uint32_t)(buf * TP_BN);
+            for (int kb = 0; kb < n_k; ++kb, ++it) {
+                const int s = it % TP_STAGES;
+                if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], (it / TP_STAGES) & 1))) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                if (leader) {
+                    const unsigned char* a_s = smem + (size_t)s * TP_STAGE_BYTES;
+                    const uint64_t da = smem_desc_sw128(a_s), db = smem_desc_sw128(a_s + TC_BM * TC_BK * 2);
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                        umma_bf16(acc, da + 2 * k4, db + 2 * k4, tc_idesc<TP_BN>(), (kb > 0 || k4 > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                __syncwarp();
+            }
+            if (timed_out) break;
+            if (leader) umma_commit(&acc_full[buf]);  // arrives when the tile's products have finished
+            __syncwarp();
+        }
+    } else {
+        // ---- epilogue
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        int i = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++i) {
+            const int tile_m = t % m_tiles, tile_n = t / m_tiles, buf = i & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (i >> 1) & 1))) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const int row = tile_m * TC_BM + quad * 32 + lane;
+            const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * TP_BN);
+            if (EPI == TC_SWIGLU) {
+#pragma unroll
+                for (int c0 = half * (HALF / 2); c0 < (half + 1) * (HALF / 2); c0 += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_load_32(lane_base + c0, g);
+                    tmem_load_32(lane_base + HALF + c0, u);
+                    const int col = tile_n * HALF + c0;
+                    if (row < M && col < n_out) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            packed[j] = pack_bf16(fast_silu(__uint_as_float(g[2 * j])) * __uint_as_float(u[2 * j]),
+                                                  fast_silu(__uint_as_float(g[2 * j + 1])) * __uint_as_float(u[2 * j + 1]));
+                        bf16* dst = out + (size_t)row * ldo + col;
+                        if (col + 32 <= n_out) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < n_out - col; ++j) dst[j] = reinterpret_cast<const bf16*>(packed)[j];
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int c0 = half * HALF; c0 < (half + 1) * HALF; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_load_32(lane_base + c0, v);
+                    const int col = tile_n * TP_BN + c0;
+                    if (row < M && col < n_out) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) packed[j] = pack_bf16(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                        bf16* dst = out + (size_t)row * ldo + col;
+                        if (col + 32 <= n_out) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < n_out - col; ++j) dst[j] = reinterpret_cast<const bf16*>(packed)[j];
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);  // this warp has read its part of the half
+        }
+    }
+    if (timed_out && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32  %0, %1;" ::"r"(tmem), "r"(2 * TP_BN));
+}
+
+template <int EPI>
+static int launch_persistent(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n_out, int k, int inter,
+                             int ldo, int m_tiles, int n_tiles, int* err, cudaStream_t stream) {
+    const size_t smem = (size_t)TP_STAGES * TP_STAGE_BYTES + 1024;
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int total = m_tiles * n_tiles, sms = qf_sm_count();
+    tc_gemm_persistent_kernel<EPI><<<total < sms ? total : sms, TP_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter,
+                                                                                          ldo, m_tiles, n_tiles, err);
+    return (int)cudaGetLastError();
+}
+
 template <int EPI, int BN>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n_out, int k, int inter, int ldo,
                      int* err, dim3 grid, cudaStream_t stream) {
@@ -168,6 +357,18 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* o
     if (e != cudaSuccess) return (int)e;
     tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, err);
     return (int)cudaGetLastError();
+}
+
+static int g_persistent = 1;
+// A measuring aid: 0 sends every product to the one-tile-per-block kernel.
+QF_EXPORT void qf_tc_gemm_set_persistent(int on) { g_persistent = on; }
+
+// Whether a product of these sizes has tiles for every SM and so runs in the persistent kernel (n as in qf_tc_gemm).
+QF_EXPORT int qf_tc_gemm_is_persistent(int epilogue, int m, int n) {
+    if (!g_persistent || m <= 0 || n <= 0) return 0;
+    const long long m_tiles = (m + TC_BM - 1) / TC_BM;
+    const long long n_tiles = epilogue == TC_SWIGLU ? (n / 2 + 127) / 128 : (n + 255) / 256;
+    return m_tiles * n_tiles >= qf_sm_count();
 }
 
 // a [m][lda], w [n][ldw] (for TC_SWIGLU: n = 2 * inter, gate rows then up rows), out [m][ldo] with n columns
@@ -188,11 +389,13 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
         if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
         const int inter = n / 2;
         const bool wide = (long long)m_tiles * ((inter + 127) / 128) >= qf_sm_count();
+        if (wide && g_persistent) return launch_persistent<TC_SWIGLU>(map_a, map_b, out, m, inter, k, inter, ldo, m_tiles, (inter + 127) / 128, err, stream);
         return wide ? launch_tc<TC_SWIGLU, 256>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 127) / 128, m_tiles), stream)
                     : launch_tc<TC_SWIGLU, 128>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 63) / 64, m_tiles), stream);
     }
     if (epilogue != TC_PLAIN) return (int)cudaErrorInvalidValue;
     const bool wide = (long long)m_tiles * ((out_cols + 255) / 256) >= qf_sm_count();
+    if (wide && g_persistent) return launch_persistent<TC_PLAIN>(map_a, map_b, out, m, n, k, 0, ldo, m_tiles, (n + 255) / 256, err, stream);
     return wide ? launch_tc<TC_PLAIN, 256>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 255) / 256, m_tiles), stream)
                 : launch_tc<TC_PLAIN, 128>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, m_tiles), stream);
 }

@@ -673,6 +673,11 @@ def tc_gemm_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def tc_gemm_is_persistent(epilogue: int, m: int, n: int) -> bool:
+    """Whether `tc_gemm` runs x [m, K] against weight [n, K] in its persistent kernel (tiles for every SM)."""
+    return library("tc_gemm").qf_tc_gemm_is_persistent(_I(epilogue), _I(m), _I(n)) != 0
+
+
 def tc_gemm(epilogue: int, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
     """out = x @ weight.T on the tcgen05 tensor cores (bf16 in, float32 accumulate in tensor memory, bf16 out).
     TC_SWIGLU: weight = [gate rows | up rows], out [M, N / 2] = silu(x gate^T) * (x up^T)."""

@@ -13,9 +13,10 @@ import torch
 
 from . import kernels
 
-# Products of 128 or more token rows can run on this library's own tcgen05 kernel (`csrc/tc_gemm.cu`) instead of the
-# cuBLAS call. Off by default: measured on a B200 at 2048 x 9728 x 896 it reaches 665 TFLOP/s where cuBLAS reaches
-# 1,150, and fused with the SwiGLU gate 60 microseconds where cuBLAS plus the gate kernel need 46.
+# Plain products of 128 or more token rows can run on this library's own tcgen05 kernel (`csrc/tc_gemm.cu`) instead of
+# the cuBLAS call. Off by default: measured on a B200 at 2048 x 9728 x 896 its persistent form reaches 800 TFLOP/s where
+# cuBLAS reaches 1,140 (at 2048 x 37888 x 3584: 1,215 against 1,620). The gate/up product with the gate in its epilogue
+# does not wait for this switch: it is the faster way wherever the persistent kernel runs (`parts/swiglu.py`).
 _own_tensor_core_products = False
 OWN_PRODUCT_MIN_ROWS = 128
 

@@ -797,7 +797,9 @@ def test_linear_bf16_matches_a_plain_product(ops):
 
 # ------------------------------------------------------------------------------------------------ tcgen05 products
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 1152, 896), (2048, 896, 4864), (130, 136, 72), (1, 8, 8)])
+# the last three have tiles for every SM and more: the persistent kernel, with ragged last tiles in every direction
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 1152, 896), (2048, 896, 4864), (130, 136, 72), (1, 8, 8),
+                                   (2048, 9728, 896), (1999, 5000, 264), (4100, 2568, 72)])
 def test_tc_gemm_plain(ops, m, n, k):
     g = torch.Generator().manual_seed(40)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
@@ -807,9 +809,13 @@ def test_tc_gemm_plain(ops, m, n, k):
     ops.tc_gemm(ops.TC_PLAIN, x, w, out, e)
     want = x.double() @ w.double().T
     assert int(e) == 0 and max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+    assert ops.tc_gemm_is_persistent(ops.TC_PLAIN, m, n) == (-(-m // 128) * -(-n // 256) >= ops.sm_count(DEV))
+    assert ops.tc_gemm_is_persistent(ops.TC_PLAIN, m, n) == (m >= 1999 and n > 1000)   # the cases meant for it reach it
 
 
-@pytest.mark.parametrize("m,inter,k", [(128, 64, 64), (300, 200, 896), (2048, 4864, 896), (70, 72, 120)])
+# the last three run in the persistent kernel (ragged last tiles of rows and of features, a K that is no multiple of 64)
+@pytest.mark.parametrize("m,inter,k", [(128, 64, 64), (300, 200, 896), (70, 72, 120), (2048, 4864, 896), (1999, 2504, 264),
+                                       (700, 3400, 1000)])
 def test_tc_gemm_swiglu(ops, m, inter, k):
     g = torch.Generator().manual_seed(41)
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
@@ -820,6 +826,8 @@ def test_tc_gemm_swiglu(ops, m, inter, k):
     gu = x.double() @ w.double().T
     want = gu[:, :inter] * torch.sigmoid(gu[:, :inter]) * gu[:, inter:]
     assert int(e) == 0 and max_err(out, want) <= 2e-2 * max(1.0, float(want.abs().max()))
+    assert ops.tc_gemm_is_persistent(ops.TC_SWIGLU, m, 2 * inter) == (-(-m // 128) * -(-inter // 128) >= ops.sm_count(DEV))
+    assert ops.tc_gemm_is_persistent(ops.TC_SWIGLU, m, 2 * inter) == (m >= 700)   # the cases meant for it reach it
 
 
 def test_tc_gemm_refuses_misaligned_shapes(ops):
