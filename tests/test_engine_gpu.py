@@ -516,6 +516,38 @@ def test_real_layer_sizes(preset, layers, tmp_path):
         torch.cuda.empty_cache()
 
 
+def test_long_prompt_through_the_persistent_gate_product(tmp_path):
+    """A prompt long enough that the gate/up product has tiles for every SM runs it on the persistent tcgen05 kernel
+    with the gate in its epilogue (Qwen2.5-0.5B layer sizes, one layer): launch by launch, then replayed from a graph
+    of its rounded shape with other tokens, against the plain implementation."""
+    import json
+
+    from qwenforge_b200 import ops
+    from qwenforge_b200.config import preset_dict
+    from qwenforge_b200.engine import Model
+    from qwenforge_b200.weights import save_safetensors
+    config = dict(preset_dict("qwen2.5-0.5b"), num_hidden_layers=1, vocab_size=1000, max_position_embeddings=1024)
+    weights = plain.random_weights(config, 11)
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    save_safetensors(tmp_path / "model.safetensors", weights)
+    model = Model.from_dir(tmp_path, torch.bfloat16, "cuda")
+    model.enable_prefill_graphs()
+    cache = model.new_cache(2048, 2)
+    places = [0, 1, 63, 64, 127, 128, 300, 511, 512, 640]
+    for turn, n in enumerate((700, 690, 650)):
+        assert ops.tc_gemm_is_persistent(ops.TC_SWIGLU, n, 2 * config["intermediate_size"])
+        tokens = random_tokens(1000, n, 800 + turn)
+        slot = cache.open()
+        logits = model.step(cache, [(slot, tokens)], want=[places + [n - 1]])
+        model.raise_on_kernel_error()
+        ref = plain.forward_logits(config, weights, tokens, dtype=torch.float32)[places + [n - 1]]
+        bound = 2e-2 + 4e-2 * float(ref.abs().max())
+        err = float((logits.double().cpu() - ref.double()).abs().max())
+        assert err <= bound, f"turn {turn}: {err:.3e} > {bound:.3e}"
+        cache.close(slot)
+    assert model.prefill_graphs.replays == 2
+
+
 def test_own_tensor_core_products_in_the_model(folders):
     """With the library's own tcgen05 products switched on, a 200-token prompt gives the plain implementation's logits."""
     from qwenforge_b200 import ops
