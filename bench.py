@@ -232,17 +232,25 @@ def run_workload(name, pk, torch, layers=None, timed_last=256):
     cache = model.new_cache(sum(-(-(n + steps) // 64) * 64 for n in lengths), batch, max(lengths) + steps)
     sampler = Sampler(SamplingParams(w["temperature"], w["seed"]))
     prompts = [torch.randint(0, config.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    slots = [cache.open() for _ in range(batch)]
-    cache.reserve([(s, n + steps) for s, n in zip(slots, lengths)])
     ev = lambda: torch.cuda.Event(enable_timing=True)
     model.step(cache, [(-1, [1, 2, 3])], want=[[]])   # an untimed padding step: loads what a first step loads
-    torch.cuda.synchronize()
-    a, b = ev(), ev()
-    a.record()
-    logits = model.step(cache, list(zip(slots, prompts)))
-    b.record()
-    torch.cuda.synchronize()
-    prefill_ms = a.elapsed_time(b)
+    # The prompt step twice, launch by launch both times (no prompt graphs here): the process's first run of these
+    # kernels at these sizes also loads them and lets the library choose its products; the second is what a step costs.
+    prefill_runs = []
+    for run in range(2):
+        slots = [cache.open() for _ in range(batch)]
+        cache.reserve([(s, n + steps) for s, n in zip(slots, lengths)])
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        logits = model.step(cache, list(zip(slots, prompts)))
+        b.record()
+        torch.cuda.synchronize()
+        prefill_runs.append(a.elapsed_time(b))
+        if run == 0:
+            for s in slots:
+                cache.close(s)
+    prefill_ms = prefill_runs[1]
     seq_ids = torch.arange(batch, dtype=torch.int64, device="cuda:0")
     first = sampler(logits, seq_ids, torch.zeros(batch, dtype=torch.int32, device="cuda:0")).tolist()
     cache.flush()
@@ -281,7 +289,8 @@ def run_workload(name, pk, torch, layers=None, timed_last=256):
         "last_roofline_frac": round(gbs_last / pk["hbm_gbs"], 4),
         "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(total_tokens / prefill_ms * 1e3, 1),
         "prefill_frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-        "prefill_how": "ONE step of all prompts, seen for the first time (launch by launch)",
+        "prefill_how": "ONE step of all prompts, launch by launch (its second run; the process's first run is prefill_first_ms)",
+        "prefill_first_ms": round(prefill_runs[0], 3),
         "kernels_per_step": graph.kernels_per_step, "clocks": clocks.summary(),
     }
     for s in slots:
@@ -428,7 +437,7 @@ def main():
                 "roofline": {"bound": "hbm", "achieved": out["gbs"], "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": out["roofline_frac"], "peaks": pk["source"]},
                 "prefill": {"value": out["prefill_tokens_per_s"], "tokens": out["prompt_tokens"], "ms": out["prefill_ms"],
-                            "frac": out["prefill_frac"], "how": out["prefill_how"]},
+                            "frac": out["prefill_frac"], "first_ms": out["prefill_first_ms"], "how": out["prefill_how"]},
                 "workload": out}
         print(json.dumps(line))
         return 0
