@@ -240,13 +240,11 @@ tc_gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     unsigned char* b_s = a_s + TC_BM * TC_BK * 2;
                     mbar_expect_tx(&full_bar[s], TP_STAGE_BYTES);
                     tma_load_2d(a_s, &map_a, kb * TC_BK, tile_m * TC_BM, &full_bar[s]);
-#pragma unroll
-                    for (int box = 0; box < TP_BN / 64; ++box) {  // boxes of 64 weight rows
-                        int w_row = tile_n * TP_BN + 64 * box;
-                        if (EPI == TC_SWIGLU)  // HALF gate rows, then the HALF matching up rows
-                            w_row = 64 * box < HALF ? tile_n * HALF + 64 * box : inter + tile_n * HALF + (64 * box - HALF);
-                        tma_load_2d(b_s + (size_t)box * 64 * TC_BK * 2, &map_b, kb * TC_BK, w_row, &full_bar[s]);
-                    }
+                    // two boxes of 128 weight rows: the tile's halves, or HALF gate rows and the HALF matching up rows
+                    const int w_row0 = EPI == TC_SWIGLU ? tile_n * HALF : tile_n * TP_BN;
+                    const int w_row1 = EPI == TC_SWIGLU ? inter + tile_n * HALF : tile_n * TP_BN + HALF;
+                    tma_load_2d(b_s, &map_b, kb * TC_BK, w_row0, &full_bar[s]);
+                    tma_load_2d(b_s + (size_t)HALF * TC_BK * 2, &map_b, kb * TC_BK, w_row1, &full_bar[s]);
                 }
                 __syncwarp();
             }
@@ -409,13 +407,19 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
         if (n % 2 || (n / 2) % 8) return (int)cudaErrorInvalidValue;
         const int inter = n / 2;
         const bool wide = (long long)m_tiles * ((inter + 127) / 128) >= qf_sm_count();
-        if (wide && g_persistent) return launch_persistent<TC_SWIGLU>(map_a, map_b, out, m, inter, k, inter, ldo, m_tiles, (inter + 127) / 128, err, stream);
+        if (wide && g_persistent) {
+            if (!qf_make_map_bf16(&map_b, w, n, k, ldw, 128)) return (int)cudaErrorNotSupported;  // boxes of 128 weight rows
+            return launch_persistent<TC_SWIGLU>(map_a, map_b, out, m, inter, k, inter, ldo, m_tiles, (inter + 127) / 128, err, stream);
+        }
         return wide ? launch_tc<TC_SWIGLU, 256>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 127) / 128, m_tiles), stream)
                     : launch_tc<TC_SWIGLU, 128>(map_a, map_b, out, m, inter, k, inter, ldo, err, dim3((inter + 63) / 64, m_tiles), stream);
     }
     if (epilogue != TC_PLAIN) return (int)cudaErrorInvalidValue;
     const bool wide = (long long)m_tiles * ((out_cols + 255) / 256) >= qf_sm_count();
-    if (wide && g_persistent) return launch_persistent<TC_PLAIN>(map_a, map_b, out, m, n, k, 0, ldo, m_tiles, (n + 255) / 256, err, stream);
+    if (wide && g_persistent) {
+        if (!qf_make_map_bf16(&map_b, w, n, k, ldw, 128)) return (int)cudaErrorNotSupported;
+        return launch_persistent<TC_PLAIN>(map_a, map_b, out, m, n, k, 0, ldo, m_tiles, (n + 255) / 256, err, stream);
+    }
     return wide ? launch_tc<TC_PLAIN, 256>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 255) / 256, m_tiles), stream)
                 : launch_tc<TC_PLAIN, 128>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, m_tiles), stream);
 }

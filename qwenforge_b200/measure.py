@@ -7,6 +7,7 @@ attention kernels compare. Every figure is the mean of CUDA-graph replays timed 
     python -m qwenforge_b200.measure chain    --preset qwen2.5-0.5b --rows 8
     python -m qwenforge_b200.measure phases   --preset qwen2.5-0.5b --rows 1,64
     python -m qwenforge_b200.measure attention --tokens 1024,2048,4096 --heads 14 --kv-heads 2 --head-dim 64
+    python -m qwenforge_b200.measure gemm --preset qwen2.5-0.5b --rows 2048,16384
 
 products   per product of a layer (output projection, gate/up, down, query/key/value): the weight-streaming kernel of
            skinny_gemm.cu (rows <= 16), the tcgen05 kernel of wide_gemm.cu (rows <= 64; after the norm kernel where the
@@ -15,6 +16,8 @@ chain      the four products after attention as separate kernels, as ONE persist
            (skinny_chain.cu), and all layers' products inside one launch (the persistent kernel's steady state)
 phases     wide_gemm.cu's own time stamps: when a block's copies, products, exchange and epilogue end
 attention  the mma.sync and the tcgen05 prefill attention on one prompt, with a tile's pages shared or not
+gemm       a feed-forward's gate/up product on many rows: the library product, the library product and the gate kernel,
+           this library's tcgen05 product (one tile per block, and persistent) plain and with the gate in its epilogue
 """
 from __future__ import annotations
 
@@ -265,9 +268,46 @@ def measure_attention(args) -> None:
             raise RuntimeError(f"a kernel reported error word {int(err)}")
 
 
+def measure_gemm(args) -> None:
+    from .csrc import library
+    hidden, inter, _, _, _ = sizes_of(args.preset)
+    switch = library("tc_gemm").qf_tc_gemm_set_persistent
+
+    def timed(fn, n=30):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n * 1e3
+
+    for rows in args.rows:
+        x = (torch.randn(rows, hidden, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(2 * inter, hidden, device="cuda") * 0.05).bfloat16()
+        full = torch.empty(rows, 2 * inter, dtype=torch.bfloat16, device="cuda")
+        act = torch.empty(rows, inter, dtype=torch.bfloat16, device="cuda")
+        flops = 2 * rows * 2 * inter * hidden
+        print(f"{args.preset} gate/up product, {rows} x {2 * inter} x {hidden}:")
+        rate = lambda us: f"{us:8.1f} us {flops / us / 1e6:6.0f} TFLOP/s"
+        print("  library product                                   " + rate(timed(lambda: torch.mm(x, w.t(), out=full))))
+        print("  library product, then the gate kernel             " + rate(timed(lambda: (torch.mm(x, w.t(), out=full), ops.swiglu(full, act)))))
+        try:
+            for mode, name in ((0, "one tile per block"), (1, "persistent")):
+                switch(ctypes.c_int(mode))
+                print(f"  tcgen05 product, {name:19s}              " + rate(timed(lambda: ops.tc_gemm(ops.TC_PLAIN, x, w, full))))
+                print(f"  tcgen05 product with the gate, {name:19s}" + rate(timed(lambda: ops.tc_gemm(ops.TC_SWIGLU, x, w, act))), flush=True)
+        finally:
+            switch(ctypes.c_int(1))
+        print(f"  (the persistent kernel {'runs' if ops.tc_gemm_is_persistent(ops.TC_SWIGLU, rows, 2 * inter) else 'does not run: too few tiles'} at this size)")
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="qwenforge_b200.measure", description=__doc__.split("\n\n")[0])
-    p.add_argument("what", choices=["products", "chain", "phases", "attention"])
+    p.add_argument("what", choices=["products", "chain", "phases", "attention", "gemm"])
     p.add_argument("--preset", default="qwen2.5-0.5b")
     p.add_argument("--rows", default="8", type=lambda text: [int(v) for v in text.split(",")])
     p.add_argument("--repeat", type=int, default=12, help="layers, each with weights of its own, captured into one graph")
@@ -278,7 +318,8 @@ def main(argv=None) -> int:
     args = p.parse_args(argv)
     ops.require_cuda("cuda", "the measurement")
     with torch.inference_mode():
-        {"products": measure_products, "chain": measure_chain, "phases": measure_phases, "attention": measure_attention}[args.what](args)
+        {"products": measure_products, "chain": measure_chain, "phases": measure_phases, "attention": measure_attention,
+         "gemm": measure_gemm}[args.what](args)
     return 0
 
 
