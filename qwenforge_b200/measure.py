@@ -162,6 +162,13 @@ def measure_products(args) -> None:
             if rows <= ops.WIDE_MAX_ROWS and ops.wide_gemm_takes(p0.epilogue, p0.weight, **wide_tensors(p0, xs[0])):
                 line += f"  wide {graph_time_us(lambda: [wide(layers[l][0][i], xs[l]) for l in range(repeat)], repeat):7.2f} us"
             line += f"  unfused {graph_time_us(lambda: [unfused(layers[l][0][i], err) for l in range(repeat)], repeat):7.2f} us"
+            if p0.epilogue == ops.EPI_SWIGLU and rows > ops.SKINNY_MAX_ROWS:
+                # the norm kernel, then the many-row tcgen05 product with the gate in its epilogue (one tile per block here)
+                def own(l):
+                    t = layers[l][0][i].tensors
+                    ops.add_rms_norm(t["hidden"], None, t["norm_weight"], t["eps"], xs[l])
+                    ops.tc_gemm(ops.TC_SWIGLU, xs[l], layers[l][0][i].weight, t["out"], err)
+                line += f"  tc_gemm {graph_time_us(lambda: [own(l) for l in range(repeat)], repeat):7.2f} us"
             print(line, flush=True)
         if int(err):
             raise RuntimeError(f"a kernel reported error word {int(err)}")

@@ -565,6 +565,45 @@ def wide_gemm_takes(epilogue: int, weight: torch.Tensor, **tensors) -> bool:
     return answer
 
 
+def wide_gemm_takes_rows(epilogue: int, m: int, weight: torch.Tensor) -> bool:
+    """`wide_gemm_takes` for planning, before the step's tensors exist: `m` contiguous, aligned token rows against
+    `weight`, for the epilogues without further arguments (EPI_RESIDUAL, EPI_SWIGLU, EPI_PLAIN)."""
+    if not (weight.is_cuda and weight.dtype == torch.bfloat16) or epilogue == EPI_QKV:
+        return False
+    key = (weight.device.index, epilogue, tuple(weight.shape), weight.stride(0), m, weight.data_ptr() % 16)
+    answer = _wide_answers.get(key)
+    if answer is None:
+        a = _SkinnyArgs()
+        a.w, a.n, a.k, a.ldw = weight.data_ptr(), weight.shape[0], weight.shape[1], weight.stride(0)
+        a.x, a.ldx, a.m = 256, weight.shape[1], m          # only the alignment of the rows is looked at
+        a.inter = a.n // 2 if epilogue == EPI_SWIGLU else 0
+        with torch.cuda.device(weight.device):
+            answer = library("wide_gemm").qf_wide_gemm_takes(_I(epilogue), ctypes.byref(a)) != 0
+        _wide_answers[key] = answer
+    return answer
+
+
+def residual_product_way(m: int, weight: torch.Tensor) -> str:
+    """How `m` token rows (64 at most) are multiplied by `weight` [N, K] and added into the residual stream fastest, by
+    measurement on a B200 (`python -m qwenforge_b200.measure products`, Qwen2.5 0.5B / 3B / 7B sizes).
+    Up to 16 rows the choice is between the two kernels that add in place: "skinny" (the mma.sync streamer) up to 8 rows
+    while the weight is under 20 MB (0.5B: 3.0 and 4.8 microseconds against 3.4 and 5.5 on the tcgen05 streamer; 7B's
+    26 MB output projection: 9.0 against 8.0), "wide" (the tcgen05 streamer) beyond (16 rows: 3.4 / 5.5 against 4.1 /
+    6.6 at 0.5B, 14.9 against 16.2 at 3B's down product, 25.8 against 50 at 7B's).
+    From 17 rows on the other way is the library product, whose result the next norm kernel adds at no cost: "wide" is
+    the faster one only for products with a long K (a feed-forward's down product: 7.2 against 9 microseconds at 0.5B
+    with 64 rows, 29.5 against 31.6 at 7B; an output projection: 4.6 against 3.1), so it needs K >= 2 N there.
+    "unfused" (library product, addition by the next norm) is what remains."""
+    size = weight.numel() * weight.element_size()
+    skinny = m <= SKINNY_MAX_ROWS and skinny_gemm_takes(m, weight, EPI_RESIDUAL, False)
+    wide = m <= WIDE_MAX_ROWS and wide_gemm_takes_rows(EPI_RESIDUAL, m, weight)
+    if m > SKINNY_MAX_ROWS:
+        return "wide" if wide and weight.shape[1] >= 2 * weight.shape[0] else "unfused"
+    if skinny and (not wide or (m <= 8 and size < 20e6)):
+        return "skinny"
+    return "wide" if wide else "unfused"
+
+
 def wide_gemm(epilogue: int, weight: torch.Tensor, **tensors) -> None:
     """One fused product for up to 64 token rows on the tcgen05 tensor cores (csrc/wide_gemm.cu): the keywords of
     `skinny_gemm`, with the input rows always given as `x` [m, K] bf16 (already normalised)."""

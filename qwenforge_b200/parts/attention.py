@@ -78,7 +78,7 @@ class GqaAttention(Mixer):
         if dtype == torch.float32:
             libs.add("gemm_f32")
         elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
-            libs |= {"attention_decode", "attention_prefill", "skinny_gemm"}
+            libs |= {"attention_decode", "attention_prefill", "skinny_gemm", "wide_gemm"}
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 libs.add("attention_prefill_tc")
         return libs
@@ -131,31 +131,55 @@ class GqaAttention(Mixer):
                                   ctx.max_q_len, self.scale, self.window, ctx.err)
         return ops.linear(attended, self.o_weight, self.o_bias_t)
 
-    # ---- the fused form for decode steps of a few sequences: three kernels per layer instead of seven
+    # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,
+    # rotation and cache write ride on the QKV product and the addition on the output projection wherever a kernel of
+    # this library takes the sizes and is the faster way by measurement; each product chooses for itself.
+    def _ways(self, ctx):
+        rows = ctx.n_tokens
+        rotary = self.position.fused_rotary() if self.position is not None else None
+        qkv = "unfused"
+        if rows <= ops.SKINNY_MAX_ROWS and ops.skinny_gemm_takes(rows, self.qkv_weight, ops.EPI_QKV, True, n_heads=self.n_heads,
+                                                                 kv_heads=self.n_kv, head_dim=self.head_dim,
+                                                                 rot_dim=rotary[1] if rotary else 0):
+            qkv = "skinny"
+        return qkv, ops.residual_product_way(rows, self.o_weight)
+
     def fused_takes(self, ctx) -> bool:
-        if not (ctx.attention == "auto" and ctx.is_decode and ctx.dtype == torch.bfloat16
+        if not (ctx.attention == "auto" and ctx.is_decode and ctx.dtype == torch.bfloat16 and ctx.n_tokens <= ops.WIDE_MAX_ROWS
                 and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.out_bias):
             return False
         rotary = self.position.fused_rotary() if self.position is not None else None
         if self.position is not None and (rotary is None or rotary[1] != self.head_dim):
             return False
-        return (ops.skinny_gemm_takes(ctx.n_tokens, self.qkv_weight, ops.EPI_QKV, True, n_heads=self.n_heads,
-                                      kv_heads=self.n_kv, head_dim=self.head_dim, rot_dim=rotary[1] if rotary else 0)
-                and ops.skinny_gemm_takes(ctx.n_tokens, self.o_weight, ops.EPI_RESIDUAL, False))
+        return self._ways(ctx) != ("unfused", "unfused")
 
-    def fused_forward(self, hidden, rms, ctx, site, writes_cache):
+    def fused_forward(self, hidden, rms, ctx, site, writes_cache, delta=None):
         n = hidden.shape[0]
+        qkv_way, o_way = self._ways(ctx)
         inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
         args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
         q = torch.empty((n, self.q_width), dtype=torch.bfloat16, device=hidden.device)
-        ops.skinny_gemm(ops.EPI_QKV, self.qkv_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1],
-                        bias=self.qkv_bias_t,
-                        qkv=dict(n_heads=self.n_heads, site=args, inv_freq=inv_freq, rot_dim=rot_dim, tok_pos=ctx.tok_pos,
-                                 tok_seq=ctx.tok_seq, slots=ctx.slots, q_out=q, write_cache=writes_cache, err=ctx.err))
+        if qkv_way == "skinny":
+            if delta is not None:
+                ops.residual_add(hidden, delta)
+            ops.skinny_gemm(ops.EPI_QKV, self.qkv_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1],
+                            bias=self.qkv_bias_t,
+                            qkv=dict(n_heads=self.n_heads, site=args, inv_freq=inv_freq, rot_dim=rot_dim, tok_pos=ctx.tok_pos,
+                                     tok_seq=ctx.tok_seq, slots=ctx.slots, q_out=q, write_cache=writes_cache, err=ctx.err))
+        else:
+            x = torch.empty(hidden.shape, dtype=torch.bfloat16, device=hidden.device)
+            ops.add_rms_norm(hidden, delta, rms[0], rms[1], x)   # the norm kernel adds the pending delta on its way
+            ops.rope_cache_write(ops.linear(x, self.qkv_weight), ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim,
+                                 self.n_heads, q, args, writes_cache, ctx.err, bias=self.qkv_bias_t)
         attended = torch.empty_like(q)
         ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
                              self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
-        ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
+        if o_way == "skinny":
+            ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
+        elif o_way == "wide":
+            ops.wide_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden, err=ctx.err)
+        else:
+            ops.residual_add(hidden, ops.linear(attended, self.o_weight))
 
     def decode_splits(self, ctx) -> int:
         """How many blocks share one (sequence, kv head): a block's warps take one page each (8 warps up to head size

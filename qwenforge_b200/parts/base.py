@@ -25,8 +25,9 @@ Interfaces by role (T = tokens of the step, W = model width):
                  apply(q [T, NH, D], k [T, KVH, D], ctx) -> None    in place, when there is no fused form
   Block          forward(hidden, delta, ctx, site, writes_cache) -> delta
                  arranges norms, mixer and feed-forward around the residual stream `hidden`.
-Mixers and feed-forwards may also offer a fused form for steps of a few tokens (`fused_takes`, `fused_forward`):
-it applies the preceding RMSNorm in its own first kernel and adds its result to `hidden` in place.
+Mixers and feed-forwards may also offer a form for steps of a few tokens that works on the stream in place
+(`fused_takes`, `fused_forward`): it adds the pending delta of the part before, applies the preceding RMSNorm in its own
+first kernel and adds its result to `hidden`.
 """
 from __future__ import annotations
 
@@ -106,13 +107,14 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, site, writes_cache: bool) -> torch.Tensor:
         raise NotImplementedError
 
-    # Optional fast form for steps of a few tokens: the part applies the preceding RMSNorm itself and adds its
-    # output to the residual stream in place (hidden += mixer(rmsnorm(hidden))). A block uses it when
-    # `fused_takes(ctx)` is true and its norm has a `fused_rms()` form.
+    # Optional fast form for steps of a few tokens: the part adds the pending `delta` (if any) to the residual stream,
+    # applies the preceding RMSNorm itself and adds its output to the stream in place
+    # (hidden += delta; hidden += mixer(rmsnorm(hidden))). A block uses it when `fused_takes(ctx)` is true and its norm
+    # has a `fused_rms()` form.
     def fused_takes(self, ctx) -> bool:
         return False
 
-    def fused_forward(self, hidden: torch.Tensor, rms, ctx, site, writes_cache: bool) -> None:
+    def fused_forward(self, hidden: torch.Tensor, rms, ctx, site, writes_cache: bool, delta=None) -> None:
         raise NotImplementedError
 
 
@@ -123,7 +125,7 @@ class FeedForward(Part):
     def fused_takes(self, ctx) -> bool:
         return False
 
-    def fused_forward(self, hidden: torch.Tensor, rms, ctx) -> None:
+    def fused_forward(self, hidden: torch.Tensor, rms, ctx, delta=None) -> None:
         raise NotImplementedError
 
 

@@ -29,18 +29,14 @@ class PreNormBlock(Part):
     def forward(self, hidden, delta, ctx, site, writes_cache):
         rms = self.mixer_norm.fused_rms()
         if rms is not None and self.mixer.fused_takes(ctx):
-            if delta is not None:
-                ops.residual_add(hidden, delta)
-            self.mixer.fused_forward(hidden, rms, ctx, site, writes_cache)
+            self.mixer.fused_forward(hidden, rms, ctx, site, writes_cache, delta)
             delta = None
         else:
             x = self.mixer_norm.forward(hidden, delta)
             delta = self.mixer.forward(x, ctx, site, writes_cache)
         rms = self.feed_forward_norm.fused_rms()
         if rms is not None and self.feed_forward.fused_takes(ctx):
-            if delta is not None:
-                ops.residual_add(hidden, delta)
-            self.feed_forward.fused_forward(hidden, rms, ctx)
+            self.feed_forward.fused_forward(hidden, rms, ctx, delta)
             return None
         x = self.feed_forward_norm.forward(hidden, delta)
         return self.feed_forward.forward(x, ctx)

@@ -51,39 +51,43 @@ class SwiGlu(FeedForward):
         ops.swiglu(gate_up, act)
         return ops.linear(act, self.down_weight)
 
-    # ---- the fused form for steps of a few tokens: norm + gate/up + SwiGLU in one kernel, down + residual in another.
-    # Each of the two products goes the way that is fastest by measurement (`python -m qwenforge_b200.measure products`):
-    # the weight-streaming kernel where it takes the shape and pays (`ops.skinny_gemm_pays`); for a down product of
-    # 100 MB and more the tcgen05 kernel of wide_gemm.cu (Qwen2.5-7B sizes: 28 microseconds against 41 to 51 in the
-    # weight-streaming kernel and 31 unfused); else the unfused kernels. The results land in the same places.
+    # ---- the form for steps of up to 64 tokens that works on the residual stream in place: norm + gate/up + SwiGLU in
+    # one kernel, down + residual in another. Each of the two products goes the way that is fastest by measurement
+    # (`python -m qwenforge_b200.measure products`). Gate/up: the mma.sync streamer where it takes the shape and pays
+    # (`ops.skinny_gemm_pays`); the tcgen05 streamer after the norm kernel for weights of 100 MB and more (Qwen2.5-7B:
+    # 50 microseconds against 52 unfused and 56 to 62 in the mma.sync streamer); else norm kernel, library product and
+    # gate kernel. Down: `ops.residual_product_way`.
     def _ways(self, ctx):
         rows = ctx.n_tokens
         gate_up = "unfused"
-        if ops.skinny_gemm_takes(rows, self.gate_up_weight, ops.EPI_SWIGLU, True) and ops.skinny_gemm_pays(rows, self.gate_up_weight):
+        if (rows <= ops.SKINNY_MAX_ROWS and ops.skinny_gemm_takes(rows, self.gate_up_weight, ops.EPI_SWIGLU, True)
+                and ops.skinny_gemm_pays(rows, self.gate_up_weight)):
             gate_up = "skinny"
-        down = "unfused"
-        if ops.skinny_gemm_takes(rows, self.down_weight, ops.EPI_RESIDUAL, False) and ops.skinny_gemm_pays(rows, self.down_weight):
-            down = "skinny"
-        elif self.down_weight.numel() * 2 >= 100e6 and self.hidden % 8 == 0:
-            down = "wide"
-        return gate_up, down
+        elif self.gate_up_weight.numel() * 2 >= 100e6 and ops.wide_gemm_takes_rows(ops.EPI_SWIGLU, rows, self.gate_up_weight):
+            gate_up = "wide"
+        return gate_up, ops.residual_product_way(rows, self.down_weight)
 
     def fused_takes(self, ctx) -> bool:
         return (ctx.dtype == torch.bfloat16 and ctx.attention == "auto" and self.inter % 8 == 0
-                and ctx.n_tokens <= ops.SKINNY_MAX_ROWS and self._ways(ctx) != ("unfused", "unfused"))
+                and ctx.n_tokens <= ops.WIDE_MAX_ROWS and self._ways(ctx) != ("unfused", "unfused"))
 
-    def fused_forward(self, hidden, rms, ctx):
+    def fused_forward(self, hidden, rms, ctx, delta=None):
         gate_up, down = self._ways(ctx)
         act = torch.empty((hidden.shape[0], self.inter), dtype=torch.bfloat16, device=hidden.device)
         if gate_up == "skinny":
+            if delta is not None:
+                ops.residual_add(hidden, delta)
             ops.skinny_gemm(ops.EPI_SWIGLU, self.gate_up_weight, hidden=hidden, norm_weight=rms[0], eps=rms[1], out=act)
         else:
             x = torch.empty(hidden.shape, dtype=torch.bfloat16, device=hidden.device)
-            ops.add_rms_norm(hidden, None, rms[0], rms[1], x)
-            ops.swiglu(ops.linear(x, self.gate_up_weight), act)
+            ops.add_rms_norm(hidden, delta, rms[0], rms[1], x)   # the norm kernel adds the pending delta on its way
+            if gate_up == "wide":
+                ops.wide_gemm(ops.EPI_SWIGLU, self.gate_up_weight, x=x, out=act, err=ctx.err)
+            else:
+                ops.swiglu(ops.linear(x, self.gate_up_weight), act)
         if down == "skinny":
             ops.skinny_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden)
-        elif down == "wide" and ops.wide_gemm_takes(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden):
+        elif down == "wide":
             ops.wide_gemm(ops.EPI_RESIDUAL, self.down_weight, x=act, residual=hidden, err=ctx.err)
         else:
             ops.residual_add(hidden, ops.linear(act, self.down_weight))
