@@ -35,10 +35,11 @@
 #define TA_THREADS 160  // four warps of row threads and the issuing warp
 
 template <int D, bool SPLIT>
-__global__ void __launch_bounds__(TA_THREADS, SPLIT ? 2 : 3)
+__global__ void __launch_bounds__(TA_THREADS, (SPLIT || D > 64) ? 2 : 3)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   bf16* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
-                  const int* __restrict__ slots, KvSite<bf16> site, int n_heads, float scale_log2, int window, int* err) {
+                  const int* __restrict__ slots, KvSite<bf16> site, int n_heads, int n_seqs, int row_tiles, int wave,
+                  float scale_log2, int window, int* err) {
     constexpr int CB = D / 64;                    // blocks of 64 columns in a row of Q, K or V
     constexpr int Q_BLOCK = TA_BM * 128;          // bytes of one [128][64] block of Q
     constexpr int KV_BLOCK = QF_PAGE * 128;       // bytes of one [64][64] block of a page's keys or values
@@ -57,9 +58,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_sfree, bar_pv, bar_p;
     __shared__ uint32_t tmem_base_s;
 
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // Which (tile, head, sequence) this block serves (with SPLIT: this pair of blocks). Tiles further down a prompt walk
+    // more pages and an SM holds two or three blocks, so the blocks are taken in waves of `wave` (one per SM): the first
+    // wave gets the longest tiles in falling order, the second the next longest in rising order, and so on, so that the
+    // blocks that share an SM have about the same work together.
+    const int unit = SPLIT ? (int)(blockIdx.x / 2) : (int)blockIdx.x, units = SPLIT ? (int)(gridDim.x / 2) : (int)gridDim.x;
+    const int w = unit / wave, in_wave = min(wave, units - w * wave), at = unit % wave;
+    const int item = w * wave + ((w & 1) ? in_wave - 1 - at : at);
+    const int per_tile = n_heads * n_seqs;
+    const int tile = row_tiles - 1 - item / per_tile, head = (item % per_tile) % n_heads, seq = (item % per_tile) / n_heads;
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-    const int tile = SPLIT ? (int)(gridDim.x / 2) - 1 - (int)(blockIdx.x / 2) : (int)gridDim.x - 1 - (int)blockIdx.x;  // long rows first
     const int row0 = tile * TA_BM;
     if (row0 >= q_len) return;
     const int n_rows = min(TA_BM, q_len - row0);
@@ -264,13 +272,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             }
             if (__any_sync(0xffffffffu, moved)) {  // the warp's 32 rows of O are loaded and stored together
                 tc_fence_after();
+                // (16 columns at a time: the row of weights is still in this thread's registers)
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 16) {
+                    uint32_t raw[16];
+                    tmem_load_16(lane_base + PV_COL + c0, raw);
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t raw[32];
-                    tmem_load_32(lane_base + PV_COL + c0, raw);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * f_o);
-                    tmem_store_32(lane_base + PV_COL + c0, raw);
+                    for (int i = 0; i < 16; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * f_o);
+                    tmem_store_16(lane_base + PV_COL + c0, raw);
                 }
                 tmem_store_wait();
             }
@@ -367,8 +376,10 @@ static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, v
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int row_tiles = (max_q_len + TA_BM - 1) / TA_BM;
+    const long long blocks = (long long)row_tiles * n_heads * n_seqs * (SPLIT ? 2 : 1);
+    if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(row_tiles * (SPLIT ? 2 : 1), n_heads, n_seqs);
+    config.gridDim = dim3((unsigned)blocks);
     config.blockDim = dim3(TA_THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
@@ -379,8 +390,8 @@ static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, v
     attr[0].val.clusterDim.z = 1;
     config.attrs = attr;
     config.numAttrs = SPLIT ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&config, kernel, q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads,
-                                   scale * 1.4426950408889634f, window, err);
+    return (int)cudaLaunchKernelEx(&config, kernel, q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs,
+                                   row_tiles, SPLIT ? qf_sm_count() / 2 : qf_sm_count(), scale * 1.4426950408889634f, window, err);
 }
 
 template <int D>

@@ -22,11 +22,11 @@ from .registry import build_part, register_part
 
 
 # Fewest new tokens of a step, by head size, from which the tcgen05 prefill attention runs instead of the mma.sync one.
-# Measured on one prompt (`python -m qwenforge_b200.measure attention`): at head size 128 the tcgen05 kernel is the
-# faster one from 2,048 tokens (64 against 71 microseconds with 16 heads; 172 against 245 at 4,096), the slower one
-# below (54 against 36 at 1,024). At head size 64 its softmax, one thread per row, bounds it at 280 TFLOP/s, which the
-# mma.sync kernel reaches as well (290 at 8,192 tokens, 180 against 124 at 2,048): it is never chosen there.
-TC_PREFILL_MIN_TOKENS = {128: 2048}
+# Measured on one prompt (`python -m qwenforge_b200.measure attention`): the tcgen05 kernel is the faster one from about
+# 1,536 tokens at both head sizes (head size 64, 14 heads: 28.6 against 32.0 microseconds there, 37 against 42 at 2,048,
+# 72 against 116 at 4,096, 199 against 415 at 8,192; head size 128, 16 heads: 33 against 52, 52 against 72, 140 against
+# 245) and the slower one below (1,024 tokens: 27 against 21, and 52 against 36): its tiles of 128 rows are too few there.
+TC_PREFILL_MIN_TOKENS = {64: 1536, 128: 1536}
 
 
 class GqaAttention(Mixer):
@@ -120,7 +120,7 @@ class GqaAttention(Mixer):
                                  self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
         elif fast:
             # the tcgen05 kernel works on blocks of 128 query rows, a long chain of pages per block: it pays for steps
-            # with many rows at head size 128
+            # with many rows
             least = TC_PREFILL_MIN_TOKENS.get(self.head_dim)
             prefill = (ops.attention_prefill_tc if least is not None and n >= least and ctx.max_q_len >= 128
                        else ops.attention_prefill)
