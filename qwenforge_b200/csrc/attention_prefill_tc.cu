@@ -407,14 +407,14 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     // The cache of this entry as one matrix of rows of D elements. The map is given more rows than any cache has
     // (its extent only bounds what a copy may address; copies address rows of held pages only).
     if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE)) return (int)cudaErrorNotSupported;
-    // Two blocks per tile while there are no more tiles than SMs, and tiles walk eight pages or more: then a tile's
-    // chain of pages is what takes the time (measured: one 8,192-token prompt of 2 heads 130 -> 79 us, 2,048 tokens
-    // 39 -> 27 us). With more tiles than SMs the blocks that share an SM are the limit and sharing a tile gains nothing
-    // (2,048 tokens of 14 heads: 62 -> 58 us at head size 64, and slower at head size 128, where only one such block
-    // fits an SM).
+    // Two blocks per tile when a tile's chain of pages is what takes the time: chains of 32 pages and more, and room on
+    // the SMs for every pair at once (two such blocks fit an SM at head size 64, one at 128). Measured on one prompt of
+    // 8,192 tokens and 2 heads: 115 -> 77 microseconds; of 2,048 tokens: 34 -> 27. Shorter chains lose more to the
+    // cluster's start and the merge than they gain (1,024 tokens of 14 heads: 21 -> 27), and pairs that do not all
+    // start together run in two rounds (1,024 tokens of 16 heads of 128: 24 -> 52).
     const long long blocks = (long long)((max_q_len + TA_BM - 1) / TA_BM) * n_heads * n_seqs;
     const int span = window > 0 && window + TA_BM < max_kv_len ? window + TA_BM : max_kv_len;
-    const bool split = span >= 8 * QF_PAGE && blocks <= (long long)qf_sm_count();
+    const bool split = span >= 32 * QF_PAGE && blocks * 2 <= (long long)qf_sm_count() * (D <= 64 ? 2 : 1);
     return split ? launch_variant<D, true>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
                  : launch_variant<D, false>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
 }
