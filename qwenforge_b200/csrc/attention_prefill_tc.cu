@@ -24,8 +24,9 @@
 // No copy uses cluster multicast.
 // One prompt of a few thousand tokens gives too few blocks to fill the SMs, and its last tiles walk dozens of pages one
 // after the other. With SPLIT two blocks (a cluster) share a tile: each takes every second page, and at the end the
-// second block passes its rows' reference maxima, sums and outputs to the first through distributed shared memory,
-// which merges them with its own and writes the result.
+// second block passes its rows' reference maxima, sums and outputs to the first through distributed shared memory
+// (column by column, so that a warp's 32 rows make one 128-byte store; row by row the same transfer cost 17
+// microseconds), which merges them with its own and writes the result.
 #include <cooperative_groups.h>
 
 #include "tcgen05.cuh"
@@ -35,7 +36,7 @@
 #define TA_THREADS 160  // four warps of row threads and the issuing warp
 
 template <int D, bool SPLIT>
-__global__ void __launch_bounds__(TA_THREADS, (SPLIT || D > 64) ? 2 : 3)
+__global__ void __launch_bounds__(TA_THREADS, D > 64 ? 2 : 3)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   bf16* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ tok_pos,
                   const int* __restrict__ slots, KvSite<bf16> site, int n_heads, int n_seqs, int row_tiles, int wave,
@@ -52,7 +53,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     unsigned char* k_s = q_s + CB * Q_BLOCK;            // [2][CB][64][64]
     unsigned char* v_s = k_s + 2 * KV_BYTES;            // [2][CB][64][64]
     unsigned char* p_s = v_s + 2 * KV_BYTES;            // [128][64]
-    float* merge_s = reinterpret_cast<float*>(p_s + TA_BM * 128);  // SPLIT: [128][D + 2] of the cluster's second block
+    // SPLIT: [D + 2][128] of the cluster's second block (a warp writes 32 neighbouring rows at once). It lies over Q and the pages' stages, which are free when both
+    // blocks have left their loops (the first barrier of the cluster below).
+    float* merge_s = reinterpret_cast<float*>(smem);
     constexpr int STRIDE = SPLIT ? 2 : 1;               // this block takes every STRIDE-th page of the tile
     const int rank = SPLIT ? (int)(blockIdx.x & 1) : 0;
     __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_sfree, bar_pv, bar_p;
@@ -296,20 +299,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
         if (!timed_out && n_tiles > 0 && !wait_all(&bar_pv, (n_tiles - 1) & 1)) timed_out = true;
         tc_fence_after();
-        if (SPLIT && rank == 1) {
-            // this block's part of every row goes to the first block: output sums, reference maximum, sum of weights
-            float* theirs = cooperative_groups::this_cluster().map_shared_rank(merge_s, 0) + (size_t)t * (D + 2);
-            const bool have = n_tiles > 0 && !timed_out;
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t raw[32];
-                if (have) tmem_load_32(lane_base + PV_COL + c0, raw);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) theirs[c0 + i] = have ? __uint_as_float(raw[i]) : 0.f;
-            }
-            theirs[D] = have ? m_ref : QF_NEG_BIG;
-            theirs[D + 1] = have ? l_run : 0.f;
-        }
         if (!SPLIT && !timed_out) {  // the loads are collective: every lane of the warp takes part, rows beyond the span store nothing
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
@@ -330,12 +319,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
     }
     if (SPLIT) {
-        cooperative_groups::this_cluster().sync();  // every thread of both blocks: the second block's parts have arrived
+        cooperative_groups::this_cluster().sync();  // every thread of both blocks: both have left their loops, their stages are free
+        if (rank == 1 && warp < 4) {
+            // this block's part of every row goes to the first block: output sums, reference maximum, sum of weights
+            const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+            float* theirs = cooperative_groups::this_cluster().map_shared_rank(merge_s, 0) + t;
+            const bool have = n_tiles > 0 && !timed_out;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 16) {
+                uint32_t raw[16];
+                if (have) tmem_load_16(lane_base + PV_COL + c0, raw);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) theirs[(c0 + i) * TA_BM] = have ? __uint_as_float(raw[i]) : 0.f;
+            }
+            theirs[D * TA_BM] = have ? m_ref : QF_NEG_BIG;
+            theirs[(D + 1) * TA_BM] = have ? l_run : 0.f;
+        }
+        cooperative_groups::this_cluster().sync();  // the second block's parts have arrived
         if (rank == 0 && warp < 4) {
             // merge: both parts carry a reference maximum of their own; the common one is the larger
             const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-            const float* theirs = merge_s + (size_t)t * (D + 2);
-            const float m_other = theirs[D], l_other = theirs[D + 1];
+            const float* theirs = merge_s + t;
+            const float m_other = theirs[D * TA_BM], l_other = theirs[(D + 1) * TA_BM];
             const float m_all = fmaxf(m_ref, m_other);
             const float f_mine = fast_exp2(m_ref - m_all), f_theirs = fast_exp2(m_other - m_all);
             const float l_all = l_run * f_mine + l_other * f_theirs;
@@ -351,7 +356,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         float v[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            v[i] = ((have ? __uint_as_float(raw[c + i]) * f_mine : 0.f) + theirs[c0 + c + i] * f_theirs) * inv;
+                            v[i] = ((have ? __uint_as_float(raw[c + i]) * f_mine : 0.f) + theirs[(c0 + c + i) * TA_BM] * f_theirs) * inv;
                         *reinterpret_cast<uint4*>(out_row + c0 + c) =
                             make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
                     }
@@ -371,7 +376,6 @@ static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, v
                           const int* slots, KvSite<bf16> site, int n_heads, int n_seqs, int max_q_len, float scale, int window,
                           int* err, cudaStream_t stream) {
     size_t smem = (size_t)(D / 64) * TA_BM * 128 + 4 * (size_t)(D / 64) * QF_PAGE * 128 + TA_BM * 128 + 1024;
-    if (SPLIT) smem += (size_t)TA_BM * (D + 2) * sizeof(float);
     auto kernel = prefill_tc_kernel<D, SPLIT>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -407,14 +411,16 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
     // The cache of this entry as one matrix of rows of D elements. The map is given more rows than any cache has
     // (its extent only bounds what a copy may address; copies address rows of held pages only).
     if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE)) return (int)cudaErrorNotSupported;
-    // Two blocks per tile when a tile's chain of pages is what takes the time: chains of 32 pages and more, and room on
-    // the SMs for every pair at once (two such blocks fit an SM at head size 64, one at 128). Measured on one prompt of
-    // 8,192 tokens and 2 heads: 115 -> 77 microseconds; of 2,048 tokens: 34 -> 27. Shorter chains lose more to the
-    // cluster's start and the merge than they gain (1,024 tokens of 14 heads: 21 -> 27), and pairs that do not all
-    // start together run in two rounds (1,024 tokens of 16 heads of 128: 24 -> 52).
-    const long long blocks = (long long)((max_q_len + TA_BM - 1) / TA_BM) * n_heads * n_seqs;
+    // Two blocks per tile when a tile's chain of pages is what takes the time. Measured on one prompt, head size 64, 14
+    // heads (three blocks fit an SM): 1,024 tokens 21 -> 17 microseconds, 2,048 tokens 38 -> 27, 3,072 tokens 54 -> 48,
+    // 4,096 tokens no gain; so chains of 16 pages and more, while the pairs need no more than two rounds on the SMs.
+    // Head size 128 (two blocks per SM, a merge twice as large): 8 tiles of 16 pages 24 -> 29 and pairs in two rounds 51 ->
+    // 64, so chains of 32 pages and room for every pair at once.
+    // (tiles that hold rows: the grid also has blocks for the rows that shorter sequences lack, which end at once)
+    const long long blocks = (long long)min((max_q_len + TA_BM - 1) / TA_BM * n_seqs, n_tokens / TA_BM + n_seqs) * n_heads;
     const int span = window > 0 && window + TA_BM < max_kv_len ? window + TA_BM : max_kv_len;
-    const bool split = span >= 32 * QF_PAGE && blocks * 2 <= (long long)qf_sm_count() * (D <= 64 ? 2 : 1);
+    const long long room = (long long)qf_sm_count() * (D <= 64 ? 3 : 2);
+    const bool split = D <= 64 ? span >= 16 * QF_PAGE && blocks <= room : span >= 32 * QF_PAGE && blocks * 2 <= room;
     return split ? launch_variant<D, true>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream)
                  : launch_variant<D, false>(q_map, kv_map, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, stream);
 }

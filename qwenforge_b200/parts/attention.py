@@ -22,10 +22,10 @@ from .registry import build_part, register_part
 
 
 # Fewest new tokens of a step, by head size, from which the tcgen05 prefill attention runs instead of the mma.sync one.
-# Measured on one prompt (`python -m qwenforge_b200.measure attention`): head size 64, 14 heads: equal at 1,024 tokens
-# (21 microseconds), then 29 against 32 at 1,536, 37 against 42 at 2,048, 72 against 116 at 4,096, 199 against 415 at
-# 8,192; head size 128, 16 heads: 16 against 17 at 512 tokens, 24 against 36 at 1,024, 52 against 72 at 2,048, 140
-# against 245 at 4,096. Below, its tiles of 128 rows are too few to fill the SMs.
+# Measured on one prompt (`python -m qwenforge_b200.measure attention`): head size 64, 14 heads: 17 against 21
+# microseconds at 1,024 tokens, 27 against 42 at 2,048, 72 against 116 at 4,096, 199 against 415 at 8,192 (at 512 tokens
+# 15 against 13); head size 128, 16 heads: 16 against 17 at 512 tokens, 24 against 36 at 1,024, 52 against 72 at 2,048,
+# 140 against 245 at 4,096. Below, its tiles of 128 rows are too few to fill the SMs.
 TC_PREFILL_MIN_TOKENS = {64: 1024, 128: 512}
 
 
