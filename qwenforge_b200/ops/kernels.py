@@ -208,10 +208,17 @@ def rope_cache_write(qkv: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Te
         _stream()), "rope_cache_write")
 
 
+GENERIC_DECODE_CHUNK = 256
+
+
 def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                       slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, max_q_len: int, scale: float,
-                      window: int, err: torch.Tensor) -> None:
-    """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math)."""
+                      window: int, err: torch.Tensor, scratch: Optional["DecodeScratch"] = None,
+                      max_kv_len: Optional[int] = None) -> None:
+    """Causal grouped-query attention of the step's queries over each sequence's cache (any sizes, SIMT float32 math).
+    A step of one token per sequence whose longest sequence exceeds one chunk of 256 keys is cut into chunks of keys
+    when `scratch` and `max_kv_len` (a bound on any sequence's length after the step) are given: a block per chunk,
+    then a fold in rising order; which chunks a row has depends on its own position only."""
     _dev("q", q)
     _dev("out", out, q.dtype)
     _dev("cache", site.storage, q.dtype)
@@ -220,6 +227,16 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, to
         raise KernelError(f"attention_generic: head_dim {d} > 256 is not supported")
     if q.shape[1] != n_heads * d or out.shape != q.shape:
         raise KernelError("attention_generic: q/out widths do not match the head count")
+    if (scratch is not None and max_kv_len is not None and max_q_len == 1 and q.shape[0] == n_seqs
+            and max_kv_len > GENERIC_DECODE_CHUNK):
+        n_chunks = -(-int(max_kv_len) // GENERIC_DECODE_CHUNK)
+        scratch.ensure(n_seqs, n_heads, n_chunks, d, 0)
+        _check(library("attention_generic").qf_attention_generic_decode(
+            _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
+            _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
+            _I(n_seqs), _I(int(max_kv_len)), _F(scale), _I(window), _ptr(scratch.part_o), _ptr(scratch.part_ml), _ptr(err),
+            _stream()), "attention_generic")
+        return
     _check(library("attention_generic").qf_attention_generic(
         _I(_is_bf16(q.dtype)), _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage),
         _ptr(site.table), _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads),
@@ -293,7 +310,7 @@ class DecodeScratch:
             self.part_o = torch.empty(rows * head_dim, dtype=torch.float32, device=self.device)
         if self.part_ml is None or self.part_ml.numel() < rows * 2:
             self.part_ml = torch.empty(rows * 2, dtype=torch.float32, device=self.device)
-        if self.counters is None or self.counters.numel() < n_counters:
+        if n_counters and (self.counters is None or self.counters.numel() < n_counters):
             self.counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
 
 

@@ -128,7 +128,8 @@ class GqaAttention(Mixer):
                     ctx.max_q_len, self.scale, self.window, ctx.err, max_kv_len=ctx.max_kv_len)
         else:
             ops.attention_generic(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                                  ctx.max_q_len, self.scale, self.window, ctx.err)
+                                  ctx.max_q_len, self.scale, self.window, ctx.err, scratch=ctx.decode_scratch,
+                                  max_kv_len=ctx.max_kv_len)
         return ops.linear(attended, self.o_weight, self.o_bias_t)
 
     # ---- the form for decode steps of up to 64 sequences that works on the residual stream in place: the norm, bias,

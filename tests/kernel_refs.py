@@ -103,7 +103,7 @@ def gather_kv(site, slot, lo, hi):
     return _f(k).transpose(0, 1), _f(v).transpose(0, 1)
 
 
-def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err):
+def attention_generic(q, out, cu_q, tok_pos, slots, site, n_heads, n_seqs, max_q_len, scale, window, err, scratch=None, max_kv_len=None):
     d, kvh = site.head_dim, site.kv_heads
     groups = n_heads // kvh
     for s in range(n_seqs):

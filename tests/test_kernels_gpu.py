@@ -212,6 +212,52 @@ def test_attention_generic(ops, dtype, nh, kvh, d, q_lens, starts, window):
     assert max_err(out, want) <= tol(dtype) * 3
 
 
+GENERIC_DECODE_SHAPES = [
+    # nh, kvh, d, starts (one token per sequence), window, slots
+    # (the longest sequence first: it is also run alone)
+    (14, 2, 64, [1500, 0, 255, 256, 257, 700], 0, None),
+    (5, 1, 24, [1023, 511, 512, 3], 0, None),
+    (6, 3, 16, [900, 300, 40, 256], 290, None),          # a window that crosses chunks of keys
+    (33, 1, 16, [600, 10], 0, None),                     # a group larger than a block's rows
+    (4, 2, 40, [800, 5, 400], 0, [1, -1, 0]),            # a padding entry in the middle
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,kvh,d,starts,window,slots", GENERIC_DECODE_SHAPES)
+def test_attention_generic_decode_in_chunks_of_keys(ops, dtype, nh, kvh, d, starts, window, slots):
+    """One token per sequence over caches longer than one chunk of keys: a block per chunk and a fold, against the plain
+    reference; and a row's result is bit for bit the same whatever else the batch holds (here: alone, with a far larger
+    bound on the lengths, hence more chunks in the launch)."""
+    n = len(starts)
+    slots = slots if slots is not None else list(range(n))[::-1]
+    site = FakeSite(n, max(starts) + 1, kvh, d, dtype, 6)
+    for slot, s in zip(slots, starts):
+        if slot >= 0:
+            fill_site(site, slot, s + 1, 6 + slot, dtype)
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(n, nh * d, generator=g).to(dtype).to(DEV)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    out = torch.full((n, nh * d), 7.0, dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    e = err_word()
+    args = ops.KvSiteArgs(site.storage, site.table, kvh, d)
+    scratch = ops.DecodeScratch(DEV)
+    bound = max(starts) + 1
+    ops.attention_generic(q, out, cu, tok_pos, slots_t, args, nh, n, 1, d ** -0.5, window, e, scratch=scratch, max_kv_len=bound)
+    ref.attention_generic(q, want, cu, tok_pos, slots_t, site, nh, n, 1, d ** -0.5, window, None)
+    assert int(e) == 0 and bound > ops.GENERIC_DECODE_CHUNK and scratch.part_o is not None     # the split form ran
+    assert max_err(out, want) <= tol(dtype) * 3
+    if -1 in slots:
+        assert float(out[slots.index(-1)].abs().max()) == 0.0
+    alone = torch.full((1, nh * d), 7.0, dtype=dtype, device=DEV)
+    ops.attention_generic(q[:1].contiguous(), alone, cu[:2], tok_pos[:1], slots_t[:1], args, nh, 1, 1, d ** -0.5, window, e,
+                          scratch=ops.DecodeScratch(DEV), max_kv_len=4 * bound)
+    assert int(e) == 0 and torch.equal(alone[0], out[0])
+
+
 def test_attention_generic_padding_entry(ops):
     out, want = run_attention(ops, "attention_generic", torch.float32, 4, 2, 16, [3, 2, 4], [0, 0, 7], 0, slots=[1, -1, 0])
     assert max_err(out, want) <= 1e-5
