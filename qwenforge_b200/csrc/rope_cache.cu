@@ -221,3 +221,21 @@ QF_EXPORT int qf_rope_cache_write(int is_bf16, const void* qkv, const void* bias
                                    table, page_elems, table_stride, kv_heads, head_dim, write_cache, n_tokens, err,
                                    stream);
 }
+
+// The rotation angles of a step, once for all its layers: table[t][j] = (cos, sin) of tok_pos[t] * inv_freq[j], float32,
+// the same expression as in the kernels above.
+__global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int n_tokens, int half,
+                                  float2* __restrict__ table) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * half) return;
+    float sn, c;
+    sincosf((float)tok_pos[i / half] * inv_freq[i % half], &sn, &c);
+    table[i] = make_float2(c, sn);
+}
+
+QF_EXPORT int qf_rope_table(const int* tok_pos, const float* inv_freq, int n_tokens, int half, void* table, cudaStream_t stream) {
+    if (n_tokens <= 0 || half <= 0) return 0;
+    const long long total = (long long)n_tokens * half;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(tok_pos, inv_freq, n_tokens, half, (float2*)table);
+    return (int)cudaGetLastError();
+}

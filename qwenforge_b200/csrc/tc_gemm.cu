@@ -13,7 +13,63 @@
 // Copies use no cluster multicast; every block loads its own tiles.
 #include "tcgen05.cuh"
 
-enum { TC_PLAIN = 0, TC_SWIGLU = 1 };
+enum { TC_PLAIN = 0, TC_SWIGLU = 1, TC_QKV = 2 };
+
+// What the TC_QKV epilogue needs beside the product: W = [q heads | k heads | v heads] of head_dim rows each; the sums get
+// the bias, q and k heads are rotated by the token's angles (a table [tokens][head_dim / 2] of (cos, sin) made once per
+// step), q goes to q_out [tokens][n_heads * head_dim], k and v to the token's place in its sequence's cache page.
+struct TcQkvArgs {
+    const bf16* bias;        // [(n_heads + 2 kv_heads) * head_dim] or null
+    const float2* angles;    // [tokens][head_dim / 2] (cos, sin), or null: no rotation
+    const int* tok_pos;
+    const int* tok_seq;
+    const int* slots;
+    bf16* q_out;
+    bf16* kv_base;
+    const int* table;
+    long long page_elems;
+    int table_stride, n_heads, kv_heads, head_dim, write_cache;
+};
+
+// One head (or half of one) of the TC_QKV epilogue for this thread's token row: P = D / 2 rotation pairs, W of them per
+// turn from tensor memory columns `col` (first halves) and `col + P` (second halves).
+template <int W>
+__device__ __forceinline__ void qkv_head_turn(uint32_t lane_addr, int col, int P, const float* bias_s, const float2* angle_row,
+                                              int first_pair, bool rotate, bf16* dst, bool store) {
+    uint32_t lo[W], hi[W];
+    if constexpr (W == 32) {
+        tmem_load_32(lane_addr + col, lo);
+        tmem_load_32(lane_addr + col + P, hi);
+    } else {
+        tmem_load_16(lane_addr + col, lo);
+        tmem_load_16(lane_addr + col + P, hi);
+    }
+    if (!store) return;
+    uint32_t o1[W / 2], o2[W / 2];
+#pragma unroll
+    for (int j = 0; j < W; j += 2) {
+        float y1[2], y2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const float x1 = __uint_as_float(lo[j + e]) + bias_s[col + j + e], x2 = __uint_as_float(hi[j + e]) + bias_s[col + P + j + e];
+            if (rotate) {
+                const float2 a = angle_row[first_pair + j + e];  // (cos, sin)
+                y1[e] = x1 * a.x - x2 * a.y;
+                y2[e] = x2 * a.x + x1 * a.y;
+            } else {
+                y1[e] = x1;
+                y2[e] = x2;
+            }
+        }
+        o1[j / 2] = pack_bf16(y1[0], y1[1]);
+        o2[j / 2] = pack_bf16(y2[0], y2[1]);
+    }
+#pragma unroll
+    for (int j = 0; j < W / 2; j += 4) {
+        *reinterpret_cast<uint4*>(dst + first_pair + 2 * j) = make_uint4(o1[j], o1[j + 1], o1[j + 2], o1[j + 3]);
+        *reinterpret_cast<uint4*>(dst + P + first_pair + 2 * j) = make_uint4(o2[j], o2[j + 1], o2[j + 2], o2[j + 3]);
+    }
+}
 
 #define TC_BM 128
 #define TC_BK 64
@@ -33,16 +89,30 @@ template <int BN> __device__ __forceinline__ constexpr uint32_t tc_idesc() {
 template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, bf16* __restrict__ out,
-               int M, int n_out, int K, int inter, int ldo, int* err) {
+               int M, int n_out, int K, int inter, int ldo, const TcQkvArgs qa, int* err) {
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
     constexpr int TC_STAGES = TcGeometry<BN>::stages, TC_STAGE_BYTES = TcGeometry<BN>::stage_bytes;
     constexpr int HALF = BN / 2;  // TC_SWIGLU: gate columns [0, HALF), up columns [HALF, BN)
     __shared__ __align__(8) uint64_t full_bar[TC_STAGES], empty_bar[TC_STAGES], acc_bar;
     __shared__ uint32_t tmem_base_s;
+    __shared__ float bias_s[EPI == TC_QKV ? BN : 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_n = blockIdx.x, tile_m = blockIdx.y;
     const int n_k = (K + TC_BK - 1) / TC_BK;
+    // TC_QKV: where this thread's token row stands and where its key and value go (element offset in the cache, -1: nowhere)
+    long long kv_at = -1;
+    auto find_row = [&]() {
+        const int row = tile_m * TC_BM + warp * 32 + lane;
+        if (row < M && qa.write_cache) {
+            const int slot = qa.slots[qa.tok_seq[row]], pos = qa.tok_pos[row];
+            if (slot >= 0) {
+                const int page = qa.table[(long long)slot * qa.table_stride + pos / QF_PAGE];
+                if (page < 0) atomicOr(err, QF_ERR_NO_PAGE);
+                else kv_at = (long long)page * qa.page_elems + (long long)(pos % QF_PAGE) * qa.head_dim;
+            }
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -99,7 +169,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             umma_commit(&empty_bar[s]);  // arrives when these products have finished reading the stage
         }
         umma_commit(&acc_bar);           // arrives when every product has finished
+    } else if (EPI == TC_QKV) {
+        // the other threads use the time of the products: the tile's bias values and their rows' places in the cache
+        for (int i = threadIdx.x - (threadIdx.x > 32 ? 2 : 1); i < BN; i += TC_THREADS - 2) {
+            const int col = tile_n * BN + i;
+            bias_s[i] = (qa.bias && col < n_out) ? __bfloat162float(qa.bias[col]) : 0.f;
+        }
+        find_row();
     }
+    if (EPI == TC_QKV && lane == 0 && warp < 2) find_row();  // the two issuing threads' own rows
     if (timed_out) atomicOr(err, QF_ERR_COPY_TIMEOUT);
     __syncwarp();
 
@@ -108,7 +186,28 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const int row = tile_m * TC_BM + warp * 32 + lane;
     const uint32_t lane_base = tmem_acc + ((uint32_t)(warp * 32) << 16);
-    if (EPI == TC_SWIGLU) {
+    if (EPI == TC_QKV) {
+        __syncthreads();  // the tile's bias values are in shared memory
+        const int D = qa.head_dim, P = D / 2, total_heads = qa.n_heads + 2 * qa.kv_heads;
+        const float2* angle_row = qa.angles ? qa.angles + (size_t)row * P : nullptr;
+        for (int h = 0; h < BN / D; ++h) {   // the heads of this tile (the launch made sure that heads do not straddle tiles)
+            const int head = tile_n * (BN / D) + h;
+            if (head >= total_heads) break;
+            const bool is_q = head < qa.n_heads, rotate = angle_row != nullptr && head < qa.n_heads + qa.kv_heads;
+            bf16* dst = nullptr;
+            if (row < M) {
+                if (is_q) dst = qa.q_out + ((size_t)row * qa.n_heads + head) * D;
+                else if (kv_at >= 0) dst = qa.kv_base + kv_at + (long long)(head - qa.n_heads) * QF_PAGE * D;  // keys, then values
+            }
+            // the loads from tensor memory are the whole warp's: every lane walks the turns, rows without a place store nothing
+            if (P >= 32) {
+                for (int first = 0; first < P; first += 32)
+                    qkv_head_turn<32>(lane_base, h * D + first, P, bias_s, angle_row, first, rotate, dst, dst != nullptr);
+            } else {
+                qkv_head_turn<16>(lane_base, h * D, P, bias_s, angle_row, 0, rotate, dst, dst != nullptr);
+            }
+        }
+    } else if (EPI == TC_SWIGLU) {
 #pragma unroll
         for (int c0 = 0; c0 < HALF; c0 += 32) {
             uint32_t g[32], u[32];
@@ -373,7 +472,7 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* o
     const size_t smem = TcGeometry<BN>::smem;
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, err);
+    tc_gemm_kernel<EPI, BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, (bf16*)out, m, n_out, k, inter, ldo, TcQkvArgs{}, err);
     return (int)cudaGetLastError();
 }
 
@@ -424,3 +523,25 @@ QF_EXPORT int qf_tc_gemm(int epilogue, const void* a, int lda, const void* w, in
                 : launch_tc<TC_PLAIN, 128>(map_a, map_b, out, m, n, k, 0, ldo, err, dim3((n + 127) / 128, m_tiles), stream);
 }
 
+
+// The QKV product with bias, rotation and cache write in its epilogue (see TcQkvArgs): a [m][lda] against
+// w [(n_heads + 2 kv_heads) * head_dim][ldw]. Head sizes 32, 64 and 128 (whole heads per tile of 128 columns); k, lda, ldw
+// multiples of 8, 16-byte aligned bases, and rows of q_out and cache pages that keep 16-byte alignment. Returns
+// cudaErrorInvalidValue for what it does not take, cudaErrorNotSupported when the driver has no tensor-map encoder.
+QF_EXPORT int qf_tc_gemm_qkv(const void* a, int lda, const void* w, int ldw, int m, int k, const TcQkvArgs* args, int* err,
+                             cudaStream_t stream) {
+    const TcQkvArgs& q = *args;
+    const int d = q.head_dim, n = (q.n_heads + 2 * q.kv_heads) * d;
+    if (m <= 0 || n <= 0) return 0;
+    if (d != 32 && d != 64 && d != 128) return (int)cudaErrorInvalidValue;
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8 || q.page_elems % 8) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)q.q_out | (uintptr_t)q.kv_base) % 16) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_a, map_b;
+    if (!qf_make_map_bf16(&map_a, a, m, k, lda, TC_BM) || !qf_make_map_bf16(&map_b, w, n, k, ldw, 64)) return (int)cudaErrorNotSupported;
+    const size_t smem = TcGeometry<128>::smem;
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<TC_QKV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((n + 127) / 128, (m + TC_BM - 1) / TC_BM);
+    tc_gemm_kernel<TC_QKV, 128><<<grid, TC_THREADS, smem, stream>>>(map_a, map_b, nullptr, m, n, k, 0, 0, q, err);
+    return (int)cudaGetLastError();
+}

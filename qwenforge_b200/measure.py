@@ -310,6 +310,33 @@ def measure_gemm(args) -> None:
         finally:
             switch(ctypes.c_int(1))
         print(f"  (the persistent kernel {'runs' if ops.tc_gemm_is_persistent(ops.TC_SWIGLU, rows, 2 * inter) else 'does not run: too few tiles'} at this size)")
+        # the query/key/value product: library product and the rotation / cache-write kernel, against the tcgen05 product
+        # with bias, rotation and cache write in its epilogue
+        _, _, heads, kv_heads, head_dim = sizes_of(args.preset)
+        n_qkv = (heads + 2 * kv_heads) * head_dim
+        wq = (torch.randn(n_qkv, hidden, device="cuda") * 0.05).bfloat16()
+        bq = torch.randn(n_qkv, device="cuda").bfloat16()
+        pages = Pages(1, rows, kv_heads, head_dim, "cuda")
+        tok_seq = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        tok_pos = torch.arange(rows, dtype=torch.int32, device="cuda")
+        slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+        q_out = torch.empty(rows, heads * head_dim, dtype=torch.bfloat16, device="cuda")
+        qkv = torch.empty(rows, n_qkv, dtype=torch.bfloat16, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        flops_q = 2 * rows * n_qkv * hidden
+        rate_q = lambda us: f"{us:8.1f} us {flops_q / us / 1e6:6.0f} TFLOP/s"
+        print(f"{args.preset} query/key/value product, {rows} x {n_qkv} x {hidden}:")
+        print("  library product                                   " + rate_q(timed(lambda: torch.mm(x, wq.t(), out=qkv))))
+        print("  library product, then rotation and cache write    " + rate_q(timed(lambda: (
+            torch.mm(x, wq.t(), out=qkv), ops.rope_cache_write(qkv, tok_seq, tok_pos, slots, inv_freq, head_dim, heads, q_out,
+                                                               pages.args(), True, err, bias=bq)))))
+        if ops.tc_gemm_qkv_takes(x, wq, head_dim):
+            angles = ops.rope_table(tok_pos, inv_freq)
+            print("  tcgen05 product with bias, rotation, cache write  " + rate_q(timed(lambda: ops.tc_gemm_qkv(
+                x, wq, bq, angles, tok_seq, tok_pos, slots, heads, q_out, pages.args(), True, err))), flush=True)
+        if int(err):
+            raise RuntimeError(f"a kernel reported error word {int(err)}")
 
 
 def main(argv=None) -> int:

@@ -729,6 +729,63 @@ def tc_gemm_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+class _TcQkvArgs(ctypes.Structure):
+    _fields_ = [("bias", ctypes.c_void_p), ("angles", ctypes.c_void_p), ("tok_pos", ctypes.c_void_p), ("tok_seq", ctypes.c_void_p),
+                ("slots", ctypes.c_void_p), ("q_out", ctypes.c_void_p), ("kv_base", ctypes.c_void_p), ("table", ctypes.c_void_p),
+                ("page_elems", ctypes.c_longlong), ("table_stride", _I), ("n_heads", _I), ("kv_heads", _I), ("head_dim", _I),
+                ("write_cache", _I)]
+
+
+def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """The rotation angles of a step's tokens, [tokens, rot_dim / 2, 2] float32 (cos, sin): made once, read by every layer."""
+    _dev("tok_pos", tok_pos, torch.int32)
+    _dev("inv_freq", inv_freq, torch.float32)
+    table = torch.empty((tok_pos.numel(), inv_freq.numel(), 2), dtype=torch.float32, device=tok_pos.device)
+    _check(library("rope_cache").qf_rope_table(_ptr(tok_pos), _ptr(inv_freq), _I(tok_pos.numel()), _I(inv_freq.numel()), _ptr(table),
+                                               _stream()), "rope_table")
+    return table
+
+
+TC_QKV_HEAD_DIMS = (32, 64, 128)
+
+
+def tc_gemm_qkv_takes(x: torch.Tensor, weight: torch.Tensor, head_dim: int) -> bool:
+    """Whether `tc_gemm_qkv` takes these operands: what `tc_gemm_takes` asks, and whole heads per tile of 128 columns."""
+    return head_dim in TC_QKV_HEAD_DIMS and tc_gemm_takes(x, weight)
+
+
+def tc_gemm_qkv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], angles: Optional[torch.Tensor],
+                tok_seq: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, n_heads: int, q_out: torch.Tensor,
+                site: KvSiteArgs, write_cache: bool, err: torch.Tensor) -> None:
+    """The query/key/value product of many token rows on the tcgen05 tensor cores with its bias, the rotation of q and k
+    heads by the tokens' angles (`rope_table`; None: no rotation) and the writes in its epilogue: q to `q_out`
+    [tokens, n_heads * head_dim], k and v to each token's place in its sequence's cache page."""
+    _dev("x", x, torch.bfloat16, contiguous=False)
+    _dev("weight", weight, torch.bfloat16, contiguous=False)
+    _dev("q_out", q_out, torch.bfloat16)
+    _dev("cache", site.storage, torch.bfloat16)
+    d = site.head_dim
+    m, k = x.shape
+    if weight.shape != ((n_heads + 2 * site.kv_heads) * d, k) or q_out.shape != (m, n_heads * d):
+        raise KernelError("tc_gemm_qkv: weight must be [(n_heads + 2 kv_heads) * head_dim, K] and q_out [tokens, n_heads * head_dim]")
+    if not tc_gemm_qkv_takes(x, weight, d):
+        raise KernelError(f"tc_gemm_qkv: head_dim {d} or the operands' alignment is not taken (head sizes {TC_QKV_HEAD_DIMS})")
+    if angles is not None and (angles.dtype != torch.float32 or angles.shape != (m, d // 2, 2) or not angles.is_contiguous()):
+        raise KernelError("tc_gemm_qkv: angles must be float32 [tokens, head_dim / 2, 2] (the whole head is rotated)")
+    a = _TcQkvArgs()
+    a.bias = None if bias is None else bias.data_ptr()
+    a.angles = None if angles is None else angles.data_ptr()
+    a.tok_pos, a.tok_seq, a.slots = tok_pos.data_ptr(), tok_seq.data_ptr(), slots.data_ptr()
+    a.q_out, a.kv_base, a.table = q_out.data_ptr(), site.storage.data_ptr(), site.table.data_ptr()
+    a.page_elems, a.table_stride = site.page_elems, site.table_stride
+    a.n_heads, a.kv_heads, a.head_dim, a.write_cache = n_heads, site.kv_heads, d, int(bool(write_cache))
+    code = library("tc_gemm").qf_tc_gemm_qkv(_ptr(x), _I(x.stride(0)), _ptr(weight), _I(weight.stride(0)), _I(m), _I(k),
+                                             ctypes.byref(a), _ptr(err), _stream())
+    if code == 801:
+        raise KernelError("tc_gemm_qkv: the driver offers no tensor-map encoder (cuTensorMapEncodeTiled)")
+    _check(code, "tc_gemm_qkv")
+
+
 def tc_gemm_is_persistent(epilogue: int, m: int, n: int) -> bool:
     """Whether `tc_gemm` runs x [m, K] against weight [n, K] in its persistent kernel (tiles for every SM)."""
     return library("tc_gemm").qf_tc_gemm_is_persistent(_I(epilogue), _I(m), _I(n)) != 0

@@ -101,6 +101,9 @@ class GqaAttention(Mixer):
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
         rotary = self.position.fused_rotary() if self.position is not None else None
+        # (The product with bias, rotation and cache write in its epilogue, `ops.tc_gemm_qkv`, was measured inside the
+        # prompt graph of 2,048 tokens at Qwen2.5-0.5B sizes: 2.88 ms for the step against 2.76 with the library product
+        # and the rotation kernel; it is not used here.)
         late_bias = self.position is None or rotary is not None  # the kernel that rotates and stores adds the bias
         qkv = ops.linear(x, self.qkv_weight, None if late_bias else self.qkv_bias_t)
         if self.position is not None and rotary is None:

@@ -876,6 +876,51 @@ def test_tc_gemm_swiglu(ops, m, inter, k):
     assert ops.tc_gemm_is_persistent(ops.TC_SWIGLU, m, 2 * inter) == (m >= 700)   # the cases meant for it reach it
 
 
+@pytest.mark.parametrize("q_lens,nh,kvh,d,k,rotary,with_bias", [
+    ([300, 1, 70], 7, 1, 64, 448, True, True),        # three sequences, a padding entry, ragged last tiles of rows and of heads
+    ([640], 14, 2, 64, 896, True, True),              # Qwen2.5-0.5B's heads
+    ([130, 64], 4, 2, 128, 264, True, False),         # one head per tile, K no multiple of 64
+    ([200], 3, 3, 32, 120, True, True),               # four heads per tile
+    ([150], 5, 1, 64, 72, False, True),               # no rotation
+])
+def test_tc_gemm_qkv(ops, q_lens, nh, kvh, d, k, rotary, with_bias):
+    """The query/key/value product with bias, rotation and cache write in its epilogue, against the float64 product put
+    through the plain rotation and cache write; the cache untouched where nothing is to be written."""
+    g = torch.Generator().manual_seed(44)
+    n, n_seqs = sum(q_lens), len(q_lens)
+    starts = [0, 63, 60][:n_seqs]
+    slots = [2, -1, 0][:n_seqs] if n_seqs == 3 else list(range(n_seqs))[::-1]
+    site_a = FakeSite(3, 1024, kvh, d, torch.bfloat16)
+    site_b = FakeSite(3, 1024, kvh, d, torch.bfloat16)
+    site_b.table = site_a.table
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((nh + 2 * kvh) * d, k, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    bias = torch.randn((nh + 2 * kvh) * d, generator=g).to(torch.bfloat16).to(DEV) if with_bias else None
+    tok_seq = torch.tensor(sum(([i] * q for i, q in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(sum((list(range(s, s + q)) for s, q in zip(starts, q_lens)), []), dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV) if rotary else None
+    angles = ops.rope_table(tok_pos, inv_freq) if rotary else None
+    if rotary:
+        want_angle = tok_pos.float().unsqueeze(-1) * inv_freq
+        assert max_err(angles[..., 0], want_angle.double().cos()) < 1e-6 and max_err(angles[..., 1], want_angle.double().sin()) < 1e-6
+    q1 = torch.full((n, nh * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    q2 = torch.empty_like(q1)
+    e = err_word()
+    args = ops.KvSiteArgs(site_a.storage, site_a.table, kvh, d)
+    assert ops.tc_gemm_qkv_takes(x, w, d)
+    ops.tc_gemm_qkv(x, w, bias, angles, tok_seq, tok_pos, slots_t, nh, q1, args, True, e)
+    product = x.double() @ w.double().T
+    ref.rope_cache_write(product, tok_seq, tok_pos, slots_t, inv_freq, d if rotary else 0, nh, q2, site_b, True, None, bias=bias)
+    scale = max(1.0, float(product.abs().max()))
+    assert int(e) == 0
+    assert max_err(q1, q2) <= 2e-2 * scale
+    assert max_err(site_a.storage, site_b.storage) <= 2e-2 * scale and float(site_a.storage.float().abs().sum()) > 0
+    before = site_a.storage.clone()
+    ops.tc_gemm_qkv(x, w, bias, angles, tok_seq, tok_pos, slots_t, nh, q1, args, False, e)   # without the write flag
+    assert int(e) == 0 and torch.equal(before, site_a.storage) and max_err(q1, q2) <= 2e-2 * scale
+
+
 def test_tc_gemm_refuses_misaligned_shapes(ops):
     x = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
