@@ -86,11 +86,63 @@ add_rms_norm_vec_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
     }
 }
 
+// Narrow rows (width <= 1024, a multiple of 4): a warp per row, eight rows per block. The row stays in the lanes'
+// registers, the sum of squares needs shuffles only, and a lane has up to eight independent 16-byte loads in flight, where
+// a block per row had one load per thread and two block-wide barriers. Which kernel runs depends on the width alone, so a
+// row's result does not depend on how many rows the step has.
+#define NW_ROWS 8
+#define NW_MAX 8   // 16-byte groups per lane
+template <typename T>
+__global__ void __launch_bounds__(NW_ROWS * 32)
+add_rms_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const T* __restrict__ weight,
+                         T* __restrict__ out, int rows, int width, float eps) {
+    const int row = blockIdx.x * NW_ROWS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float* h = hidden + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    T* o = out + (size_t)row * width;
+    const int n4 = width / 4;
+    float4 v[NW_MAX], dv[NW_MAX];
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        v[u] = c < n4 ? Vec4<float>::load(h + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        dv[u] = (d && c < n4) ? Vec4<T>::load(d + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        if (d && c < n4) {
+            v[u].x += dv[u].x;
+            v[u].y += dv[u].y;
+            v[u].z += dv[u].z;
+            v[u].w += dv[u].w;
+            Vec4<float>::store(h + 4 * c, v[u]);
+        }
+        ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
+#pragma unroll
+    for (int u = 0; u < NW_MAX; ++u) {
+        const int c = lane + 32 * u;
+        if (c < n4) {
+            const float4 w = Vec4<T>::load(weight + 4 * c);
+            Vec4<T>::store(o + 4 * c, make_float4(v[u].x * inv * w.x, v[u].y * inv * w.y, v[u].z * inv * w.z, v[u].w * inv * w.w));
+        }
+    }
+}
+
 template <typename T>
 static int launch(float* hidden, const void* delta, const void* weight, void* out, int rows, int width, float eps,
                   cudaStream_t stream) {
     if (rows <= 0) return 0;
     const uintptr_t align = (uintptr_t)hidden | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out;
+    if (width % 4 == 0 && width <= 4 * 32 * NW_MAX && align % 16 == 0) {
+        add_rms_norm_warp_kernel<T><<<(rows + NW_ROWS - 1) / NW_ROWS, NW_ROWS * 32, 0, stream>>>(hidden, (const T*)delta, (const T*)weight,
+                                                                                              (T*)out, rows, width, eps);
+        return (int)cudaGetLastError();
+    }
     if (width % 4 == 0 && width <= 4096 && align % 16 == 0) {
         add_rms_norm_vec_kernel<T><<<rows, 256, 0, stream>>>(hidden, (const T*)delta, (const T*)weight, (T*)out, width, eps);
         return (int)cudaGetLastError();
