@@ -419,7 +419,7 @@ def main():
 
     import torch
 
-    from qwenforge_b200.config import preset_config, preset_dict
+    from qwenforge_b200.config import preset_config
     from qwenforge_b200.engine import Model, StudentEngine
     from qwenforge_b200.weights import write_random_model
 

@@ -17,7 +17,7 @@ from __future__ import annotations
 import contextlib
 import dataclasses
 import gc
-from typing import Optional, Sequence
+from typing import Optional
 
 import numpy as np
 import torch

@@ -18,7 +18,7 @@ from ..config import ModelConfig, ModelSpec, load_config, resolve_dtype
 from ..csrc import prepare
 from ..parts import build_block, build_part
 from ..weights import load_weights, random_state_on_device
-from .step import StepContext, build_context, context_of, pack_step
+from .step import StepContext, context_of, pack_step
 
 
 def _walk(part):

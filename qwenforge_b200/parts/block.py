@@ -5,7 +5,6 @@ The stream `hidden` is float32 and is updated in place; a part's output (`delta`
 the *next* norm's kernel, so a block takes the pending delta of the layer before it and returns its own."""
 from __future__ import annotations
 
-from .. import ops
 from .base import Part
 from .registry import build_part, register_part
 
