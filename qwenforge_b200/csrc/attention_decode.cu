@@ -1,6 +1,8 @@
 // Split-K flash decoding over the paged cache (bf16): one new token per sequence attends to its own
-// cache; the key range of every (sequence, kv head) is cut into `n_splits` runs of whole pages that
-// separate blocks reduce at once, so that a batch of a few sequences still fills the GPU.
+// cache; the key range of every (sequence, kv head) is cut into up to `n_splits` runs of whole pages that
+// separate blocks reduce at once, so that a batch of a few sequences still fills the GPU. How many runs a sequence
+// gets is decided on the device from the lengths of the batch (see the kernel's first lines): a long sequence among
+// short ones gets more blocks, not longer ones.
 //
 // A block serves one (sequence, kv head, chunk of up to 16 query heads of the group, split). The query heads of
 // the group are the 16 rows of an m16n8k16 tensor-core tile, so keys and values are read once for the whole
@@ -16,17 +18,86 @@
 // No block waits for another. (Merging the splits of a thread-block cluster through distributed shared memory
 // instead was measured slower, and so was a variant of sixteen warps with half a page each.)
 // The kernel is launched as a programmatic dependent of the kernel before it.
+#include <algorithm>
+
 #include "tma.cuh"
 
 // TMA: head sizes whose rows are a multiple of 128 bytes (64, 128) take the half pages by tiled copies of the tensor
 // memory accelerator (128-byte swizzle; one copy per 64 columns for the keys and as many for the values, completing
 // on the warp's own barrier with a bounded wait); other head sizes use 16-byte asynchronous copies into padded rows.
+// ---- The plan of a step: which block takes which run of which sequence. The lengths live on the device (a captured
+// graph replays these launches with other lengths every step), so one warp works the plan out once per step, for every
+// layer whose attention has the same shape. A sequence of P pages is cut into ceil(P / target) runs of equal size,
+// target being the pages per block at which the batch's pages fill the SMs once (and at least one page per warp of a
+// block); where the rounding up gives more blocks than SMs, target grows until they fit, so that no block waits for
+// a free SM while others are done. Sequences of unequal lengths thus get blocks of about
+// equal work, and a batch that fills the SMs unsplit stays unsplit.
+// plan[j] for j < n_pairs: x = sequence (batch entry; -1: no such block), y = run | runs << 16, z = the sequence's
+// length with the new token, w = its cache slot (-1: a padding entry, whose one block writes zeros).
+// The kernel does not let its dependents start early: whatever runs later in the stream may read the plan without
+// waiting for anything but its own predecessor.
+__global__ void __launch_bounds__(32)
+decode_plan_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots, int n_seqs,
+                   int kvc, int sms, int warps, int window, int max_splits, int4* __restrict__ plan, int n_pairs) {
+    const int lane = threadIdx.x;
+    auto length_of = [&](int s) -> int { return s < n_seqs && slots[s] >= 0 ? tok_pos[cu_q[s]] + 1 : 0; };
+    auto pages_of = [&](int len) -> int {
+        if (len <= 0) return 0;
+        const int from = window > 0 ? max(0, len - window) : 0;
+        return (len - 1) / QF_PAGE - from / QF_PAGE + 1;
+    };
+    auto runs_of = [&](int pages, float target) -> int {
+        if (pages <= 0) return 1;
+        int n = min(max((int)ceilf((float)pages / target), 1), max_splits);
+        const int each = (pages + n - 1) / n;
+        return (pages + each - 1) / each;  // no run without a page
+    };
+    auto warp_sum = [](int v) -> int {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    };
+    int total = 0;
+    for (int s0 = 0; s0 < n_seqs; s0 += 32) total += pages_of(length_of(s0 + lane));
+    total = warp_sum(total);
+    float target = fmaxf((float)warps, (float)total * (float)kvc / (float)sms);
+    for (int round = 0; round < 16; ++round) {
+        int pairs = 0;
+        for (int s0 = 0; s0 < n_seqs; s0 += 32) pairs += s0 + lane < n_seqs ? runs_of(pages_of(length_of(s0 + lane)), target) : 0;
+        pairs = warp_sum(pairs);
+        if (pairs <= n_seqs || (long long)pairs * kvc <= sms) break;
+        if (round == 15) {
+            target = 3.0e38f;  // one run each: always within the grid
+            break;
+        }
+        target *= fmaxf(1.05f, (float)pairs * (float)kvc / (float)sms);
+    }
+    grid_dependency_wait();  // nothing is written before this; and when this kernel is done, so is everything before it
+    int before = 0;
+    for (int s0 = 0; s0 < n_seqs; s0 += 32) {
+        const int s = s0 + lane;
+        const int len = length_of(s);
+        const int n = s < n_seqs ? runs_of(pages_of(len), target) : 0;
+        int upto = n;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, upto, o);
+            if (lane >= o) upto += t;
+        }
+        const int first = before + upto - n;
+        for (int k = 0; k < n; ++k)
+            if (first + k < n_pairs) plan[first + k] = make_int4(s, k | (n << 16), len, len > 0 ? slots[s] : -1);
+        before += __shfl_sync(0xffffffffu, upto, 31);
+    }
+    for (int j = before + lane; j < n_pairs; j += 32) plan[j] = make_int4(-1, 0, 0, -1);
+}
+
 template <int D, int WARPS, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
-                    const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots,
-                    KvSite<bf16> site, int n_heads, int chunks, float scale_log2, int window, int n_splits,
-                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
+                    const int* __restrict__ cu_q, const int4* __restrict__ plan, KvSite<bf16> site, int n_heads, int chunks, float scale_log2,
+                    int window, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                    int* __restrict__ counters, int* err) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
     constexpr int LD = TMA ? D : D + 8;  // shared-memory row (bf16 elements): padded, or swizzled blocks of 64 columns
     constexpr int KS = D / 16;          // k-steps of Q K^T
@@ -40,14 +111,22 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     __shared__ __align__(8) uint64_t bars[DEC_WARPS][2];
 
     grid_launch_dependents();
-    const int split = blockIdx.x, seq = blockIdx.z;
-    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    // ---- which (sequence, split) this block is: a record of the plan that decode_plan_kernel made from the lengths of
+    // this step's batch (see there). The grid holds as many blocks as any batch of this shape can need; those beyond
+    // the plan end here.
+    const int kvc = site.kv_heads * chunks;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int4 record = __ldg(plan + blockIdx.x / kvc);
+    const int seq = record.x;
+    if (seq < 0) return;
+    const int split = record.y & 0xffff, n_splits = record.y >> 16;
+    const int y = blockIdx.x % kvc;
+    const int kvh = y / chunks, chunk = y % chunks;
     const int G = n_heads / site.kv_heads;
     const int g0 = chunk * 16, n_g = min(16, G - g0);
     const int head0 = kvh * G + g0;
     const int tok = cu_q[seq];
-    const int slot = slots[seq];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slot = record.w;
     const int q_width = n_heads * D;
     bf16* out_row = out + (size_t)tok * q_width + (size_t)head0 * D;
 
@@ -57,7 +136,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) out_row[i] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int L = tok_pos[tok] + 1;
+    const int L = record.z;
     const int lo = window > 0 ? max(0, L - window) : 0;
     const int first_page = lo / QF_PAGE, last_page = (L - 1) / QF_PAGE;
     const int pps = (last_page - first_page + n_splits) / n_splits;  // ceil(pages / splits)
@@ -292,7 +371,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     }
     __syncthreads();
     // block result: row r: maximum max_w m_s[w][r], sum sum_w l_s[w][r], numerator sum_w (warp w's buffer)[r][:]
-    const size_t part_row0 = ((size_t)seq * n_heads + head0) * n_splits;  // partial index of (row 0, split 0)
+    const size_t part_row0 = ((size_t)seq * n_heads + head0) * max_splits;  // partial index of (row 0, split 0)
     for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
         const int r = i / D, d = i % D;
         float num = 0.f;
@@ -304,7 +383,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
             out_row[i] = __float2bfloat16_rn(l > 0.f ? num / l : 0.f);
         } else {
-            part_o[(part_row0 + (size_t)r * n_splits + split) * D + d] = num;
+            part_o[(part_row0 + (size_t)r * max_splits + split) * D + d] = num;
         }
     }
     if (n_splits == 1) return;
@@ -315,13 +394,13 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         for (int w = 1; w < DEC_WARPS; ++w) m = fmaxf(m, m_s[w][r]);
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
-        part_ml[(part_row0 + (size_t)r * n_splits + split) * 2] = m;
-        part_ml[(part_row0 + (size_t)r * n_splits + split) * 2 + 1] = l;
+        part_ml[(part_row0 + (size_t)r * max_splits + split) * 2] = m;
+        part_ml[(part_row0 + (size_t)r * max_splits + split) * 2 + 1] = l;
     }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        int* counter = counters + (size_t)seq * gridDim.y + blockIdx.y;
+        int* counter = counters + (size_t)seq * kvc + y;
         const int ticket = atomicAdd(counter, 1);
         if (ticket == n_splits - 1) {
             // the last block of this (sequence, kv head, chunk): every partial is visible after this fence; the
@@ -333,33 +412,35 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     }
     __syncthreads();
     if (ticket_s != n_splits - 1) return;
-    // Every output element folds its row's partials in split order, eight at a time, keeping a running maximum:
-    // out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s. A thread takes two elements at once, so that the loads
-    // of both are in flight together.
-    const int n_out = n_g * D;
-    for (int i0 = threadIdx.x; i0 < n_out; i0 += 2 * DEC_THREADS) {
+    // Every group of four output elements folds its row's partials in split order, eight at a time, keeping a running
+    // maximum: out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s. A thread takes two groups at once, which covers
+    // a block's whole output in one round at every head size, so that all of the fold's loads are in flight together.
+    constexpr int D4 = D / 4;
+    const int n_items = n_g * D4;
+    for (int i0 = threadIdx.x; i0 < n_items; i0 += 2 * DEC_THREADS) {
         const float2* ml[2];
-        const float* po[2];
+        const float4* po[2];
         bool live[2];
-        float big[2] = {QF_NEG_BIG, QF_NEG_BIG}, den[2] = {0.f, 0.f}, num[2] = {0.f, 0.f};
+        float big[2] = {QF_NEG_BIG, QF_NEG_BIG}, den[2] = {0.f, 0.f};
+        float4 num[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
             const int i = i0 + x * DEC_THREADS;
-            live[x] = i < n_out;
-            const int r = live[x] ? i / D : 0, d = live[x] ? i % D : 0;
-            ml[x] = reinterpret_cast<const float2*>(part_ml) + part_row0 + (size_t)r * n_splits;
-            po[x] = part_o + (part_row0 + (size_t)r * n_splits) * D + d;
+            live[x] = i < n_items;
+            const int r = live[x] ? i / D4 : 0, d4 = live[x] ? i % D4 : 0;
+            ml[x] = reinterpret_cast<const float2*>(part_ml) + part_row0 + (size_t)r * max_splits;
+            po[x] = reinterpret_cast<const float4*>(part_o + (part_row0 + (size_t)r * max_splits) * D) + d4;
         }
         for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
             float2 a[2][8];
-            float v[2][8];
+            float4 v[2][8];
 #pragma unroll
             for (int x = 0; x < 2; ++x)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const bool in = live[x] && sp0 + j < n_splits;
                     a[x][j] = in ? __ldcg(ml[x] + sp0 + j) : make_float2(QF_NEG_BIG, 0.f);
-                    v[x][j] = in ? __ldcg(po[x] + (size_t)(sp0 + j) * D) : 0.f;
+                    v[x][j] = in ? __ldcg(po[x] + (size_t)(sp0 + j) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
@@ -368,27 +449,45 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                 for (int j = 0; j < 8; ++j) top = fmaxf(top, a[x][j].x);
                 const float keep = exp2f(big[x] - top);
                 den[x] *= keep;
-                num[x] *= keep;
+                num[x].x *= keep;
+                num[x].y *= keep;
+                num[x].z *= keep;
+                num[x].w *= keep;
                 big[x] = top;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float w = exp2f(a[x][j].x - top);
                     den[x] += w * a[x][j].y;
-                    num[x] += w * v[x][j];
+                    num[x].x += w * v[x][j].x;
+                    num[x].y += w * v[x][j].y;
+                    num[x].z += w * v[x][j].z;
+                    num[x].w += w * v[x][j].w;
                 }
             }
         }
 #pragma unroll
         for (int x = 0; x < 2; ++x)
-            if (live[x]) out_row[i0 + x * DEC_THREADS] = __float2bfloat16_rn(den[x] > 0.f ? num[x] / den[x] : 0.f);
+            if (live[x]) {
+                const float inv = den[x] > 0.f ? 1.f / den[x] : 0.f;
+                uint2 packed;
+                packed.x = pack_bf16(num[x].x * inv, num[x].y * inv);
+                packed.y = pack_bf16(num[x].z * inv, num[x].w * inv);
+                *reinterpret_cast<uint2*>(out_row + (size_t)(i0 + x * DEC_THREADS) * 4) = packed;
+            }
     }
 }
 
+// (sequence, run) pairs of any plan: every sequence has one, and the runs beyond that fill the SMs at most once
+static long long plan_pairs(int n_seqs, int kv_heads, int n_heads, int n_splits) {
+    const int sms = qf_sm_count() > 0 ? qf_sm_count() : 1;
+    const long long kvc = (long long)kv_heads * ((n_heads / kv_heads + 15) / 16);
+    return std::min((long long)n_seqs * n_splits, (long long)n_seqs + sms / kvc);
+}
+
 template <int D>
-static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots, void* base,
-                  const int* table, long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs,
-                  float scale, int window, int n_splits, float* part_o, float* part_ml, int* counters, int* err,
-                  cudaStream_t stream) {
+static int launch(const void* q, void* out, const int* cu_q, const int4* plan, void* base, const int* table,
+                  long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
+                  int n_splits, float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
     constexpr int WARPS = D <= 64 ? 8 : 4;  // two half-page buffers per warp: 16 to 18 KB at D = 64, 33 to 35 KB at D = 128
     constexpr bool TMA = D % 64 == 0;
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
@@ -402,24 +501,43 @@ static int launch(const void* q, void* out, const int* cu_q, const int* tok_pos,
         // (its extent only bounds what a copy may address; copies address rows of held pages only).
         if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE / 2)) return (int)cudaErrorNotSupported;
     }
-    dim3 grid(n_splits, kv_heads * chunks, n_seqs);
+    dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
-                           (bf16*)out, cu_q, tok_pos, slots, site, n_heads, chunks, scale * 1.4426950408889634f, window,
-                           n_splits, part_o, part_ml, counters, err);
+                           (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
+                           part_o, part_ml, counters, err);
+}
+
+// How many int4 records a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode reads).
+QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int n_heads, int n_splits) {
+    if (n_seqs <= 0 || kv_heads <= 0 || n_heads % kv_heads || n_splits < 1) return 0;
+    return plan_pairs(n_seqs, kv_heads, n_heads, n_splits);
+}
+
+// The plan of one step for attention of this shape (see decode_plan_kernel); the same plan serves every layer of the
+// step that has this shape. `n_splits` is the most runs that one sequence may get.
+QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, int kv_heads,
+                                       int head_dim, int n_heads, int window, int n_splits, void* plan, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || n_splits > 0x7fff) return (int)cudaErrorInvalidValue;
+    const int sms = qf_sm_count() > 0 ? qf_sm_count() : 1;
+    const int kvc = kv_heads * ((n_heads / kv_heads + 15) / 16);
+    return (int)launch_pdl(decode_plan_kernel, dim3(1), dim3(32), 0, stream, cu_q, tok_pos, slots, n_seqs, kvc, sms,
+                           head_dim <= 64 ? 8 : 4, window, n_splits, (int4*)plan,
+                           (int)plan_pairs(n_seqs, kv_heads, n_heads, n_splits));
 }
 
 // Scratch (used when n_splits > 1): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml float32
 // [n_seqs * n_heads * n_splits * 2], counters int32 [n_seqs * kv_heads * ceil(group / 16)], zero before the first
 // call (the kernel leaves them zero). Returns cudaErrorInvalidValue for a head size without an instantiation.
-QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, const int* tok_pos, const int* slots,
-                                  void* base, const int* table, long long page_elems, int table_stride, int kv_heads,
-                                  int head_dim, int n_heads, int n_seqs, float scale, int window, int n_splits,
-                                  float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
+QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, const void* plan, void* base,
+                                  const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
+                                  int n_heads, int n_seqs, float scale, int window, int n_splits, float* part_o,
+                                  float* part_ml, int* counters, int* err, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1) return (int)cudaErrorInvalidValue;
-#define QF_CASE(DIM)                                                                                                \
-    case DIM:                                                                                                       \
-        return launch<DIM>(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads, n_heads, \
+    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan) return (int)cudaErrorInvalidValue;
+#define QF_CASE(DIM)                                                                                                   \
+    case DIM:                                                                                                          \
+        return launch<DIM>(q, out, cu_q, (const int4*)plan, base, table, page_elems, table_stride, kv_heads, n_heads, \
                            n_seqs, scale, window, n_splits, part_o, part_ml, counters, err, stream);
     switch (head_dim) {
         QF_CASE(32)
@@ -435,16 +553,16 @@ QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, con
 // ------------------------------------------------------------------------------------------------------------------
 // The same split-K decode attention for callers that must not allocate (declared in attention_decode_noalloc.h).
 // The partial results and the ticket counters live in ONE file-scope device array instead of caller-provided
-// scratch. Every GPU that loads this library holds the array (QF_NOALLOC_BYTES, about 4.1 MB) until the process ends.
+// scratch. Every GPU that loads this library holds the array (QF_NOALLOC_BYTES, about 4.4 MB) until the process ends.
 #include <stdio.h>
 
 #include "attention_decode_noalloc.h"
 
 #define QF_NOALLOC_PART_ML_FLOATS (QF_NOALLOC_MAX_ROWS * 2)
 #define QF_NOALLOC_PART_O_FLOATS (QF_NOALLOC_MAX_ROWS * QF_NOALLOC_MAX_HEAD_DIM)
-#define QF_NOALLOC_BYTES ((QF_NOALLOC_PART_O_FLOATS + QF_NOALLOC_PART_ML_FLOATS + QF_NOALLOC_MAX_COUNTERS) * 4)
+#define QF_NOALLOC_BYTES ((QF_NOALLOC_PART_O_FLOATS + QF_NOALLOC_PART_ML_FLOATS + QF_NOALLOC_MAX_COUNTERS + 4 * QF_NOALLOC_MAX_PAIRS) * 4)
 
-// layout: [part_o floats][part_ml floats][counters ints]
+// layout: [part_o floats][part_ml floats][counters ints][plan records of four ints]
 static __device__ __align__(256) unsigned char qf_noalloc_scratch[QF_NOALLOC_BYTES];
 
 #define QF_NOALLOC_MAX_DEVICES 64
@@ -466,6 +584,13 @@ QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* c
     }
     const long long rows = (long long)n_seqs * n_heads * n_splits;
     const long long n_counters = (long long)n_seqs * kv_heads * ((n_heads / kv_heads + 15) / 16);
+    const long long pairs = qf_attention_decode_plan_size(n_seqs, kv_heads, n_heads, n_splits);
+    if (pairs > QF_NOALLOC_MAX_PAIRS) {
+        snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
+                 "qf_attention_decode_noalloc: a plan of %lld blocks per kv head (limit %d): beyond the built-in scratch; "
+                 "use fewer sequences per call or qf_attention_decode", pairs, QF_NOALLOC_MAX_PAIRS);
+        return QF_NOALLOC_TOO_LARGE;
+    }
     if (n_splits > 1 && (rows > QF_NOALLOC_MAX_ROWS || head_dim > QF_NOALLOC_MAX_HEAD_DIM || n_counters > QF_NOALLOC_MAX_COUNTERS)) {
         snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
                  "qf_attention_decode_noalloc: n_seqs * n_heads * n_splits = %lld (limit %d), head_dim %d (limit %d), "
@@ -495,14 +620,16 @@ QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* c
     float* part_o = reinterpret_cast<float*>(qf_noalloc_ptr[device]);
     float* part_ml = part_o + QF_NOALLOC_PART_O_FLOATS;
     int* counters = reinterpret_cast<int*>(part_ml + QF_NOALLOC_PART_ML_FLOATS);
+    void* plan = counters + QF_NOALLOC_MAX_COUNTERS;  // 16-byte aligned: every part before it is a multiple of 16 bytes
     if (n_splits > 1) {
         // the array keeps whatever the last call left: the ticket counters must start at zero
         e = cudaMemsetAsync(counters, 0, (size_t)n_counters * sizeof(int), stream);
         if (e != cudaSuccess) return (int)e;
     }
-    const int code = qf_attention_decode(q, out, cu_q, tok_pos, slots, base, table, page_elems, table_stride, kv_heads,
-                                         head_dim, n_heads, n_seqs, scale, window, n_splits, part_o, part_ml, counters,
-                                         err, stream);
+    int code = qf_attention_decode_plan(cu_q, tok_pos, slots, n_seqs, kv_heads, head_dim, n_heads, window, n_splits, plan, stream);
+    if (code == 0)
+        code = qf_attention_decode(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads,
+                                   n_seqs, scale, window, n_splits, part_o, part_ml, counters, err, stream);
     if (code == (int)cudaErrorInvalidValue)
         snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
                  "qf_attention_decode_noalloc: head_dim %d has no kernel (32, 64, 96, 128)", head_dim);

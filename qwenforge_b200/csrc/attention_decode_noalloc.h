@@ -9,12 +9,16 @@
 
    qf_attention_decode_noalloc takes the arguments of qf_attention_decode without the three scratch
    pointers. Its scratch is one array inside the library, QF_NOALLOC_MAX_ROWS x QF_NOALLOC_MAX_HEAD_DIM
-   floats plus small tables (about 4.1 MB), which every GPU that loads the library keeps until the
+   floats plus small tables (about 4.4 MB), which every GPU that loads the library keeps until the
    process exits. The function calls no cudaMalloc, cudaFree or any allocating routine.
+
+   n_splits is the most blocks that share one (sequence, kv head); the kernel gives each sequence as many of them
+   as its share of the batch's pages asks for.
 
    Limits: n_seqs * n_heads * n_splits <= QF_NOALLOC_MAX_ROWS, head_dim <= QF_NOALLOC_MAX_HEAD_DIM,
    n_seqs * kv_heads * ceil(group / 16) <= QF_NOALLOC_MAX_COUNTERS (all only when n_splits > 1: one split
-   needs no scratch). Larger calls return QF_NOALLOC_TOO_LARGE and qf_attention_decode_noalloc_error()
+   needs no scratch), and in every call min(n_seqs * n_splits, n_seqs + SMs / (kv_heads * ceil(group / 16))) <=
+   QF_NOALLOC_MAX_PAIRS (the plan of which block takes which run of which sequence). Larger calls return QF_NOALLOC_TOO_LARGE and qf_attention_decode_noalloc_error()
    says which limit was passed; nothing is launched.
 
    First call on a device: it looks up the array's device address (once per device, with that device
@@ -32,6 +36,7 @@
 #define QF_NOALLOC_MAX_ROWS 8192
 #define QF_NOALLOC_MAX_HEAD_DIM 128
 #define QF_NOALLOC_MAX_COUNTERS 4096
+#define QF_NOALLOC_MAX_PAIRS 8192
 #define QF_NOALLOC_TOO_LARGE (-2)
 
 #ifdef __cplusplus

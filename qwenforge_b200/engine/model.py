@@ -118,6 +118,7 @@ class Model:
     # ------------------------------------------------------------------ the step
     def forward(self, ctx: StepContext, cache: SequenceCache) -> Optional[torch.Tensor]:
         """Run the schedule over the context's tokens; logits of ctx.want_rows (None if nothing is wanted)."""
+        ctx.step_memo = {}
         hidden = self.embedding.forward(ctx.token_ids, ctx)
         delta = None
         if self.observer is not None:

@@ -35,6 +35,9 @@ class StepContext:
     # token's index in its sequence (positions on several axes, token types). `tok_pos` stays the index that
     # orders the cache and the causal mask.
     extras: Optional[dict] = None
+    # what the parts of one step share: the model empties it before every run of its schedule; a part keeps there
+    # what it works out once per step for all layers of its kind (key: a tuple that starts with the part's own name)
+    step_memo: Optional[dict] = None
     # host copies, for parts that plan on the host (absent when a captured graph replays the step)
     host_slots: Optional[list] = None
     host_starts: Optional[list] = None

@@ -303,6 +303,13 @@ class DecodeScratch:
     def __init__(self, device):
         self.device = device
         self.part_o = self.part_ml = self.counters = None
+        self.plans: dict = {}   # attention shape -> int32 [records, 4]: which block takes which run of which sequence
+
+    def plan(self, key: tuple, records: int) -> torch.Tensor:
+        held = self.plans.get(key)
+        if held is None or held.shape[0] < records:
+            held = self.plans[key] = torch.empty((records, 4), dtype=torch.int32, device=self.device)
+        return held
 
     def ensure(self, n_seqs: int, n_heads: int, n_splits: int, head_dim: int, n_counters: int) -> None:
         rows = n_seqs * n_heads * n_splits
@@ -314,10 +321,34 @@ class DecodeScratch:
             self.counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
 
 
+def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, kv_heads: int, head_dim: int,
+                          n_heads: int, n_seqs: int, window: int, n_splits: int, scratch: DecodeScratch) -> torch.Tensor:
+    """The plan of one decode step for attention of this shape: which block takes which run of which sequence, worked
+    out on the device from the batch's lengths (sequences of unequal lengths get blocks of about equal work; a batch
+    that fills the SMs unsplit stays unsplit). One plan serves every layer of the step with this shape. `n_splits` is
+    the most runs one sequence may get. The tensor belongs to `scratch` and is overwritten by the next plan of the
+    same shape."""
+    for name, t in (("cu_q", cu_q), ("tok_pos", tok_pos), ("slots", slots)):
+        _dev(name, t, torch.int32)
+    if not 1 <= n_splits <= 128:
+        raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..128")
+    if kv_heads <= 0 or n_heads % kv_heads:
+        raise KernelError(f"attention_decode: {n_heads} heads do not divide into {kv_heads} groups")
+    lib = library("attention_decode")
+    lib.qf_attention_decode_plan_size.restype = ctypes.c_longlong
+    records = int(lib.qf_attention_decode_plan_size(_I(n_seqs), _I(kv_heads), _I(n_heads), _I(n_splits)))
+    plan = scratch.plan((n_seqs, kv_heads, n_heads, head_dim, window, n_splits), records)
+    _check(lib.qf_attention_decode_plan(_ptr(cu_q), _ptr(tok_pos), _ptr(slots), _I(n_seqs), _I(kv_heads), _I(head_dim),
+                                        _I(n_heads), _I(window), _I(n_splits), _ptr(plan), _stream()), "attention_decode_plan")
+    return plan
+
+
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, scale: float, window: int,
-                     n_splits: int, scratch: DecodeScratch, err: torch.Tensor) -> None:
-    """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128."""
+                     n_splits: int, scratch: DecodeScratch, err: torch.Tensor, plan: Optional[torch.Tensor] = None) -> None:
+    """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128.
+    `n_splits` is the most blocks that share one (sequence, kv head); `plan` (attention_decode_plan with the same
+    shape, made in this step; made here when absent) says how many of them each sequence gets."""
     _dev("q", q, torch.bfloat16)
     _dev("out", out, torch.bfloat16)
     _dev("cache", site.storage, torch.bfloat16)
@@ -329,12 +360,14 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok
         raise KernelError("attention_decode: wants exactly one token per sequence, q [n_seqs, n_heads * head_dim]")
     if not 1 <= n_splits <= 128:
         raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..128")
+    if plan is None:
+        plan = attention_decode_plan(cu_q, tok_pos, slots, site.kv_heads, d, n_heads, n_seqs, window, n_splits, scratch)
     group = n_heads // site.kv_heads
     n_counters = n_seqs * site.kv_heads * ((group + 15) // 16)
     if n_splits > 1:
         scratch.ensure(n_seqs, n_heads, n_splits, d, n_counters)
     _check(library("attention_decode").qf_attention_decode(
-        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(tok_pos), _ptr(slots), _ptr(site.storage), _ptr(site.table),
+        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(plan), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _F(scale),
         _I(window), _I(n_splits), _ptr(scratch.part_o if n_splits > 1 else None),
         _ptr(scratch.part_ml if n_splits > 1 else None), _ptr(scratch.counters if n_splits > 1 else None), _ptr(err),

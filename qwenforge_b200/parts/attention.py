@@ -100,6 +100,9 @@ class GqaAttention(Mixer):
 
     def forward(self, x, ctx, site, writes_cache):
         n = x.shape[0]
+        fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16
+                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS)
+        plan = self.decode_plan(ctx) if fast and ctx.is_decode else None
         rotary = self.position.fused_rotary() if self.position is not None else None
         # (The product with bias, rotation and cache write in its epilogue, `ops.tc_gemm_qkv`, was measured inside the
         # prompt graph of 2,048 tokens at Qwen2.5-0.5B sizes: 2.88 ms for the step against 2.76 with the library product
@@ -116,11 +119,9 @@ class GqaAttention(Mixer):
         ops.rope_cache_write(qkv, ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim, self.n_heads, q, args,
                              writes_cache, ctx.err, bias=self.qkv_bias_t if late_bias else None)
         attended = torch.empty_like(q)
-        fast = (ctx.attention == "auto" and x.dtype == torch.bfloat16
-                and self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS)
         if fast and ctx.is_decode:
             ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                                 self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
+                                 self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err, plan)
         elif fast:
             # the tcgen05 kernel works on blocks of 128 query rows, a long chain of pages per block: it pays for steps
             # with many rows
@@ -160,6 +161,7 @@ class GqaAttention(Mixer):
     def fused_forward(self, hidden, rms, ctx, site, writes_cache, delta=None):
         n = hidden.shape[0]
         qkv_way, o_way = self._ways(ctx)
+        plan = self.decode_plan(ctx)
         inv_freq, rot_dim = self.position.fused_rotary() if self.position is not None else (None, 0)
         args = ops.KvSiteArgs(site.storage, site.table, self.n_kv, self.head_dim)
         q = torch.empty((n, self.q_width), dtype=torch.bfloat16, device=hidden.device)
@@ -177,7 +179,7 @@ class GqaAttention(Mixer):
                                  self.n_heads, q, args, writes_cache, ctx.err, bias=self.qkv_bias_t)
         attended = torch.empty_like(q)
         ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                             self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err)
+                             self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err, plan)
         if o_way == "skinny":
             ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
         elif o_way == "wide":
@@ -185,16 +187,27 @@ class GqaAttention(Mixer):
         else:
             ops.residual_add(hidden, ops.linear(attended, self.o_weight))
 
+    def decode_plan(self, ctx) -> torch.Tensor:
+        """Which block of the decode attention takes which run of which sequence: made once per step, by the first
+        layer of this shape that runs, and shared through the step's memo by the others."""
+        n_splits = self.decode_splits(ctx)
+        key = ("gqa_attention.decode_plan", self.n_kv, self.n_heads, self.head_dim, self.window, n_splits)
+        memo = ctx.step_memo if ctx.step_memo is not None else {}
+        plan = memo.get(key)
+        if plan is None:
+            plan = memo[key] = ops.attention_decode_plan(ctx.cu_q, ctx.tok_pos, ctx.slots, self.n_kv, self.head_dim,
+                                                         self.n_heads, ctx.n_seqs, self.window, n_splits, ctx.decode_scratch)
+        return plan
+
     def decode_splits(self, ctx) -> int:
-        """How many blocks share one (sequence, kv head): a block's warps take one page each (8 warps up to head size
-        64, else 4), so at most one split per that many pages, and no more splits than leave one block per SM: every
-        split costs a round of partial results. Depends on the batch's shape only (fixed inside a captured graph)."""
+        """The most blocks that may share one (sequence, kv head): a block's warps take one page each (8 warps up to
+        head size 64, else 4), so at most one split per that many pages of the longest sequence that the step allows.
+        How many of them a sequence gets is the kernel's decision, from the lengths on the device; this number sizes
+        its grid and scratch and depends on the batch's shape only (fixed inside a captured graph)."""
         span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + PAGE_TOKENS)
         pages = max(1, -(-span // PAGE_TOKENS))
         warps = 8 if self.head_dim <= 64 else 4
-        blocks = ctx.n_seqs * self.n_kv * (-(-(self.n_heads // self.n_kv) // 16))
-        # measured on B200 (context 4096): batch 64 is fastest unsplit, batch 8 with 8 splits, batch 1 with 8 to 16
-        return max(1, min(-(-pages // warps), ops.sm_count(ctx.err.device) // blocks, 64))
+        return max(1, min(-(-pages // warps), 64))
 
 
 register_part("mixer", "gqa_attention", GqaAttention)

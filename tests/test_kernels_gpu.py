@@ -475,6 +475,65 @@ def test_attention_decode(ops, nh, kvh, d, lengths, window, n_splits):
     assert max_err(out, want) <= 3e-2
 
 
+@pytest.mark.parametrize("nh,kvh,d,n_splits", [(16, 2, 128, 9), (14, 2, 64, 5)])
+def test_attention_decode_of_many_unequal_sequences(ops, nh, kvh, d, n_splits):
+    """More sequences than a warp has lanes (the kernel's plan walks them 32 at a time), lengths from one token to a
+    few thousand, padding entries among them: long sequences are cut into several blocks, short ones into one."""
+    g = torch.Generator().manual_seed(5)
+    lengths = [int(v) for v in torch.randint(1, 400, (41,), generator=g)]
+    lengths[3], lengths[17], lengths[40] = 2275, 1, 1500
+    slots = list(range(41))[::-1]
+    slots[5] = slots[33] = -1
+    out, want = run_decode(ops, nh, kvh, d, lengths, 0, n_splits, slots=slots)
+    assert max_err(out, want) <= 3e-2
+    assert float(out[5].float().abs().max()) == 0.0 and float(out[33].float().abs().max()) == 0.0
+
+
+def decode_plan_records(ops, lengths, kvh, nh, d, n_splits, slots=None, window=0):
+    n = len(lengths)
+    slots = slots if slots is not None else list(range(n))
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([length - 1 for length in lengths], dtype=torch.int32, device=DEV)
+    plan = ops.attention_decode_plan(cu, tok_pos, torch.tensor(slots, dtype=torch.int32, device=DEV), kvh, d, nh, n,
+                                     window, n_splits, ops.DecodeScratch(DEV))
+    return plan.cpu().tolist()
+
+
+def test_attention_decode_plan(ops):
+    """Every sequence has its runs, numbered, one after another; together they fill the SMs at most once unless every
+    sequence has only one; equal sequences get equal numbers; the rest of the grid is marked as empty."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    g = torch.Generator().manual_seed(11)
+    ragged = [int(v) for v in torch.randint(64, 2300, (16,), generator=g)]
+    cases = [([4096] * 8, 2, 14, 64, 8, None), ([4096] * 64, 2, 14, 64, 8, None), ([4096], 2, 14, 64, 8, None),
+             (ragged, 2, 16, 128, 9, None), ([300, 5000, 1] + [70] * 40, 1, 40, 32, 10, [2, -1, 0] + list(range(3, 43)))]
+    for lengths, kvh, nh, d, n_splits, slots in cases:
+        records = decode_plan_records(ops, lengths, kvh, nh, d, n_splits, slots)
+        slots = slots if slots is not None else list(range(len(lengths)))
+        kvc = kvh * (-(-(nh // kvh) // 16))
+        at, runs = 0, []
+        for s, (length, slot) in enumerate(zip(lengths, slots)):
+            n = records[at][1] >> 16
+            assert 1 <= n <= n_splits
+            for k in range(n):
+                assert records[at + k] == [s, k | (n << 16), length if slot >= 0 else 0, slot], (lengths, s, k)
+            pages = -(-length // 64) if slot >= 0 else 0
+            assert n <= max(pages, 1) and (slot >= 0 or n == 1)
+            runs.append(n)
+            at += n
+        assert all(r == [-1, 0, 0, -1] for r in records[at:])
+        assert sum(runs) * kvc <= sms or all(n == 1 for n in runs), (lengths, runs)
+        if len(set(zip(lengths, slots))) == 1 or len(set(lengths)) == 1 and min(slots) >= 0:
+            assert len(set(runs)) == 1
+    if sms == 148:   # the shapes that the split rule was measured at
+        assert decode_plan_records(ops, [4096] * 8, 2, 14, 64, 8)[0][1] >> 16 == 8
+        assert decode_plan_records(ops, [4096] * 64, 2, 14, 64, 8)[0][1] >> 16 == 1
+        assert decode_plan_records(ops, [4096], 2, 14, 64, 8)[0][1] >> 16 == 8
+        longest = max(range(16), key=lambda i: ragged[i])
+        records = decode_plan_records(ops, ragged, 2, 16, 128, 9)
+        assert max(r[1] >> 16 for r in records if r[0] == longest) >= 4   # the long one among short ones gets many blocks
+
+
 def test_attention_decode_padding_and_far_key(ops):
     out, want = run_decode(ops, 4, 2, 64, [100, 50, 9], 0, 3, slots=[1, -1, 0])
     assert max_err(out, want) <= 3e-2 and float(out[1].float().abs().max()) == 0.0
