@@ -32,14 +32,18 @@
 // block); where the rounding up gives more blocks than SMs, target grows until they fit, so that no block waits for
 // a free SM while others are done. Sequences of unequal lengths thus get blocks of about
 // equal work, and a batch that fills the SMs unsplit stays unsplit.
-// plan[j] for j < n_pairs: x = sequence (batch entry; -1: no such block), y = run | runs << 16, z = the sequence's
-// length with the new token, w = its cache slot (-1: a padding entry, whose one block writes zeros).
+// The plan starts with the number of runs of every sequence (n_seqs ints, padded to a multiple of four), for whoever
+// folds the partial results later; the block records follow. Record j < n_pairs: x = sequence (batch entry; -1: no such
+// block), y = run | runs << 16, z = the sequence's length with the new token, w = its cache slot (-1: a padding entry,
+// whose one block writes zeros).
 // The kernel does not let its dependents start early: whatever runs later in the stream may read the plan without
 // waiting for anything but its own predecessor.
 __global__ void __launch_bounds__(32)
 decode_plan_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos, const int* __restrict__ slots, int n_seqs,
-                   int kvc, int sms, int warps, int window, int max_splits, int4* __restrict__ plan, int n_pairs) {
+                   int kvc, int sms, int warps, int window, int max_splits, int4* __restrict__ plan_all, int n_pairs) {
     const int lane = threadIdx.x;
+    int* runs = reinterpret_cast<int*>(plan_all);
+    int4* plan = plan_all + (n_seqs + 3) / 4;
     auto length_of = [&](int s) -> int { return s < n_seqs && slots[s] >= 0 ? tok_pos[cu_q[s]] + 1 : 0; };
     auto pages_of = [&](int len) -> int {
         if (len <= 0) return 0;
@@ -85,6 +89,7 @@ decode_plan_kernel(const int* __restrict__ cu_q, const int* __restrict__ tok_pos
             if (lane >= o) upto += t;
         }
         const int first = before + upto - n;
+        if (s < n_seqs) runs[s] = n;
         for (int k = 0; k < n; ++k)
             if (first + k < n_pairs) plan[first + k] = make_int4(s, k | (n << 16), len, len > 0 ? slots[s] : -1);
         before += __shfl_sync(0xffffffffu, upto, 31);
@@ -96,8 +101,8 @@ template <int D, int WARPS, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                     const int* __restrict__ cu_q, const int4* __restrict__ plan, KvSite<bf16> site, int n_heads, int chunks, float scale_log2,
-                    int window, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                    int* __restrict__ counters, int* err) {
+                    int window, int max_splits, int n_seqs, int fold_later, float* __restrict__ part_o,
+                    float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
     constexpr int LD = TMA ? D : D + 8;  // shared-memory row (bf16 elements): padded, or swizzled blocks of 64 columns
     constexpr int KS = D / 16;          // k-steps of Q K^T
@@ -116,7 +121,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     // the plan end here.
     const int kvc = site.kv_heads * chunks;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int4 record = __ldg(plan + blockIdx.x / kvc);
+    const int4 record = __ldg(plan + (n_seqs + 3) / 4 + blockIdx.x / kvc);
     const int seq = record.x;
     if (seq < 0) return;
     const int split = record.y & 0xffff, n_splits = record.y >> 16;
@@ -130,10 +135,15 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     const int q_width = n_heads * D;
     bf16* out_row = out + (size_t)tok * q_width + (size_t)head0 * D;
 
-    if (slot < 0) {  // padding entry: defined output, no cache access, no ticket
+    if (slot < 0) {  // padding entry: defined output (or a partial result that folds to zero), no cache access, no ticket
         grid_dependency_wait();
-        if (split == 0)
+        if (split == 0 && !fold_later)
             for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) out_row[i] = __float2bfloat16_rn(0.f);
+        if (split == 0 && fold_later && threadIdx.x < n_g) {
+            float* ml = part_ml + (((size_t)seq * n_heads + head0 + threadIdx.x) * max_splits) * 2;
+            ml[0] = QF_NEG_BIG;
+            ml[1] = 0.f;
+        }
         return;
     }
     const int L = record.z;
@@ -377,7 +387,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         float num = 0.f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) num += reinterpret_cast<const float*>(smem_raw + (size_t)w * PAGE_BYTES)[r * OLD + d];
-        if (n_splits == 1) {
+        if (n_splits == 1 && !fold_later) {
             float l = 0.f;
 #pragma unroll
             for (int w = 0; w < DEC_WARPS; ++w) l += l_s[w][r];
@@ -386,7 +396,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             part_o[(part_row0 + (size_t)r * max_splits + split) * D + d] = num;
         }
     }
-    if (n_splits == 1) return;
+    if (n_splits == 1 && !fold_later) return;
     if (threadIdx.x < n_g) {
         const int r = threadIdx.x;
         float m = m_s[0][r], l = 0.f;
@@ -397,6 +407,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         part_ml[(part_row0 + (size_t)r * max_splits + split) * 2] = m;
         part_ml[(part_row0 + (size_t)r * max_splits + split) * 2 + 1] = l;
     }
+    if (fold_later) return;  // the kernel that comes next folds the partial results itself
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -487,7 +498,7 @@ static long long plan_pairs(int n_seqs, int kv_heads, int n_heads, int n_splits)
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int4* plan, void* base, const int* table,
                   long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
-                  int n_splits, float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
+                  int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
     constexpr int WARPS = D <= 64 ? 8 : 4;  // two half-page buffers per warp: 16 to 18 KB at D = 64, 33 to 35 KB at D = 128
     constexpr bool TMA = D % 64 == 0;
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
@@ -504,13 +515,14 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
     dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
                            (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
-                           part_o, part_ml, counters, err);
+                           n_seqs, fold_later, part_o, part_ml, counters, err);
 }
 
-// How many int4 records a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode reads).
+// How many 16-byte units a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode
+// reads): the sequences' numbers of runs, then the block records.
 QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int n_heads, int n_splits) {
     if (n_seqs <= 0 || kv_heads <= 0 || n_heads % kv_heads || n_splits < 1) return 0;
-    return plan_pairs(n_seqs, kv_heads, n_heads, n_splits);
+    return (n_seqs + 3) / 4 + plan_pairs(n_seqs, kv_heads, n_heads, n_splits);
 }
 
 // The plan of one step for attention of this shape (see decode_plan_kernel); the same plan serves every layer of the
@@ -526,19 +538,22 @@ QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, cons
                            (int)plan_pairs(n_seqs, kv_heads, n_heads, n_splits));
 }
 
-// Scratch (used when n_splits > 1): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml float32
-// [n_seqs * n_heads * n_splits * 2], counters int32 [n_seqs * kv_heads * ceil(group / 16)], zero before the first
-// call (the kernel leaves them zero). Returns cudaErrorInvalidValue for a head size without an instantiation.
+// Scratch (used when n_splits > 1 or fold_later): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml
+// float32 [n_seqs * n_heads * n_splits * 2], counters int32 [n_seqs * kv_heads * ceil(group / 16)], zero before the
+// first call (the kernel leaves them zero; not used with fold_later). With fold_later the kernel stops at the partial
+// results (every sequence's runs, as many as the plan's first part says) and writes no `out`: the caller's next
+// kernel folds them. Returns cudaErrorInvalidValue for a head size without an instantiation.
 QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, const void* plan, void* base,
                                   const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
-                                  int n_heads, int n_seqs, float scale, int window, int n_splits, float* part_o,
-                                  float* part_ml, int* counters, int* err, cudaStream_t stream) {
+                                  int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
+                                  float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan) return (int)cudaErrorInvalidValue;
+    if (fold_later ? (!part_o || !part_ml) : !out) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                   \
     case DIM:                                                                                                          \
         return launch<DIM>(q, out, cu_q, (const int4*)plan, base, table, page_elems, table_stride, kv_heads, n_heads, \
-                           n_seqs, scale, window, n_splits, part_o, part_ml, counters, err, stream);
+                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -587,7 +602,7 @@ QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* c
     const long long pairs = qf_attention_decode_plan_size(n_seqs, kv_heads, n_heads, n_splits);
     if (pairs > QF_NOALLOC_MAX_PAIRS) {
         snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
-                 "qf_attention_decode_noalloc: a plan of %lld blocks per kv head (limit %d): beyond the built-in scratch; "
+                 "qf_attention_decode_noalloc: a plan of %lld units of 16 bytes (limit %d): beyond the built-in scratch; "
                  "use fewer sequences per call or qf_attention_decode", pairs, QF_NOALLOC_MAX_PAIRS);
         return QF_NOALLOC_TOO_LARGE;
     }
@@ -629,7 +644,7 @@ QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* c
     int code = qf_attention_decode_plan(cu_q, tok_pos, slots, n_seqs, kv_heads, head_dim, n_heads, window, n_splits, plan, stream);
     if (code == 0)
         code = qf_attention_decode(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads,
-                                   n_seqs, scale, window, n_splits, part_o, part_ml, counters, err, stream);
+                                   n_seqs, scale, window, n_splits, 0, part_o, part_ml, counters, err, stream);
     if (code == (int)cudaErrorInvalidValue)
         snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
                  "qf_attention_decode_noalloc: head_dim %d has no kernel (32, 64, 96, 128)", head_dim);

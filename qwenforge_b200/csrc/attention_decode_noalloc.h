@@ -17,8 +17,8 @@
 
    Limits: n_seqs * n_heads * n_splits <= QF_NOALLOC_MAX_ROWS, head_dim <= QF_NOALLOC_MAX_HEAD_DIM,
    n_seqs * kv_heads * ceil(group / 16) <= QF_NOALLOC_MAX_COUNTERS (all only when n_splits > 1: one split
-   needs no scratch), and in every call min(n_seqs * n_splits, n_seqs + SMs / (kv_heads * ceil(group / 16))) <=
-   QF_NOALLOC_MAX_PAIRS (the plan of which block takes which run of which sequence). Larger calls return QF_NOALLOC_TOO_LARGE and qf_attention_decode_noalloc_error()
+   needs no scratch), and in every call ceil(n_seqs / 4) + min(n_seqs * n_splits, n_seqs + SMs / (kv_heads * ceil(group / 16)))
+   <= QF_NOALLOC_MAX_PAIRS (the plan of which block takes which run of which sequence). Larger calls return QF_NOALLOC_TOO_LARGE and qf_attention_decode_noalloc_error()
    says which limit was passed; nothing is launched.
 
    First call on a device: it looks up the array's device address (once per device, with that device

@@ -345,18 +345,22 @@ def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torc
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok_pos: torch.Tensor,
                      slots: torch.Tensor, site: KvSiteArgs, n_heads: int, n_seqs: int, scale: float, window: int,
-                     n_splits: int, scratch: DecodeScratch, err: torch.Tensor, plan: Optional[torch.Tensor] = None) -> None:
+                     n_splits: int, scratch: DecodeScratch, err: torch.Tensor, plan: Optional[torch.Tensor] = None,
+                     fold_later: bool = False) -> None:
     """Split-K flash decoding: ONE new token per sequence over its cache; bfloat16, head sizes 32/64/96/128.
     `n_splits` is the most blocks that share one (sequence, kv head); `plan` (attention_decode_plan with the same
-    shape, made in this step; made here when absent) says how many of them each sequence gets."""
+    shape, made in this step; made here when absent) says how many of them each sequence gets. With `fold_later` the
+    kernel stops at the runs' partial results in `scratch` and writes no `out` (which may be None): `fold_project`
+    folds them on its way into the output projection."""
     _dev("q", q, torch.bfloat16)
-    _dev("out", out, torch.bfloat16)
+    if not fold_later:
+        _dev("out", out, torch.bfloat16)
     _dev("cache", site.storage, torch.bfloat16)
     d = site.head_dim
     if d not in FAST_ATTENTION_HEAD_DIMS:
         raise KernelError(f"attention_decode: head_dim {d} has no tensor-core kernel (have {FAST_ATTENTION_HEAD_DIMS}); "
                           "use attention_generic")
-    if q.shape != (n_seqs, n_heads * d) or out.shape != q.shape:
+    if q.shape != (n_seqs, n_heads * d) or (not fold_later and out.shape != q.shape):
         raise KernelError("attention_decode: wants exactly one token per sequence, q [n_seqs, n_heads * head_dim]")
     if not 1 <= n_splits <= 128:
         raise KernelError(f"attention_decode: n_splits {n_splits} outside 1..128")
@@ -364,14 +368,48 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, tok
         plan = attention_decode_plan(cu_q, tok_pos, slots, site.kv_heads, d, n_heads, n_seqs, window, n_splits, scratch)
     group = n_heads // site.kv_heads
     n_counters = n_seqs * site.kv_heads * ((group + 15) // 16)
-    if n_splits > 1:
+    partials = n_splits > 1 or fold_later
+    if partials:
         scratch.ensure(n_seqs, n_heads, n_splits, d, n_counters)
     _check(library("attention_decode").qf_attention_decode(
-        _ptr(q), _ptr(out), _ptr(cu_q), _ptr(plan), _ptr(site.storage), _ptr(site.table),
+        _ptr(q), _ptr(None if fold_later else out), _ptr(cu_q), _ptr(plan), _ptr(site.storage), _ptr(site.table),
         _LL(site.page_elems), _I(site.table_stride), _I(site.kv_heads), _I(d), _I(n_heads), _I(n_seqs), _F(scale),
-        _I(window), _I(n_splits), _ptr(scratch.part_o if n_splits > 1 else None),
-        _ptr(scratch.part_ml if n_splits > 1 else None), _ptr(scratch.counters if n_splits > 1 else None), _ptr(err),
+        _I(window), _I(n_splits), _I(1 if fold_later else 0), _ptr(scratch.part_o if partials else None),
+        _ptr(scratch.part_ml if partials else None), _ptr(scratch.counters if partials else None), _ptr(err),
         _stream()), "attention_decode")
+
+
+class _FoldProjectArgs(ctypes.Structure):
+    _fields_ = [("part_o", _P), ("part_ml", _P), ("runs", _P), ("w", _P), ("hidden", _P), ("rows", _I), ("n", _I),
+                ("ldw", _I), ("n_heads", _I), ("head_dim", _I), ("max_splits", _I)]
+
+
+def fold_project_takes(rows: int, weight: torch.Tensor, hidden: torch.Tensor, n_heads: int, head_dim: int) -> bool:
+    """Whether `fold_project` takes the output projection `weight` [N, n_heads * head_dim] for a step of `rows` rows."""
+    if weight.dtype != torch.bfloat16 or hidden.dtype != torch.float32 or weight.dim() != 2 or weight.stride(1) != 1:
+        return False
+    if weight.shape[1] != n_heads * head_dim or not hidden.is_contiguous() or hidden.shape != (rows, weight.shape[0]):
+        return False
+    return bool(library("fold_project").qf_fold_project_takes(
+        _I(rows), _I(weight.shape[0]), _I(weight.stride(0)), _I(n_heads), _I(head_dim), _ptr(weight), _ptr(hidden)))
+
+
+def fold_project(plan: torch.Tensor, scratch: DecodeScratch, weight: torch.Tensor, hidden: torch.Tensor, n_heads: int,
+                 head_dim: int, n_splits: int) -> None:
+    """hidden[r, :] += fold(the partial results of sequence r) @ weight^T, after `attention_decode(..., fold_later=True)`
+    with the same `plan`, `scratch` and `n_splits` in a step whose row r is sequence r (one token per sequence).
+    bfloat16 weight [N, n_heads * head_dim], float32 hidden [rows, N]; the blocks' shares are added with atomic
+    reductions, in no fixed order."""
+    _dev("weight", weight, torch.bfloat16, contiguous=False)
+    _dev("hidden", hidden, torch.float32)
+    rows = hidden.shape[0]
+    if not fold_project_takes(rows, weight, hidden, n_heads, head_dim):
+        raise KernelError(f"fold_project: does not take {rows} rows, weight {tuple(weight.shape)}, {n_heads} heads of {head_dim}")
+    if scratch.part_o is None or scratch.part_o.numel() < rows * n_heads * n_splits * head_dim:
+        raise KernelError("fold_project: the scratch does not hold this step's partial results")
+    a = _FoldProjectArgs(scratch.part_o.data_ptr(), scratch.part_ml.data_ptr(), plan.data_ptr(), weight.data_ptr(),
+                         hidden.data_ptr(), rows, weight.shape[0], weight.stride(0), n_heads, head_dim, n_splits)
+    _check(library("fold_project").qf_fold_project(ctypes.byref(a), _stream()), "fold_project")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

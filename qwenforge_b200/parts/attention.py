@@ -78,7 +78,7 @@ class GqaAttention(Mixer):
         if dtype == torch.float32:
             libs.add("gemm_f32")
         elif self.head_dim in ops.FAST_ATTENTION_HEAD_DIMS:
-            libs |= {"attention_decode", "attention_prefill", "skinny_gemm", "wide_gemm"}
+            libs |= {"attention_decode", "attention_prefill", "skinny_gemm", "wide_gemm", "fold_project"}
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 libs.add("attention_prefill_tc")
         return libs
@@ -177,9 +177,16 @@ class GqaAttention(Mixer):
             ops.add_rms_norm(hidden, delta, rms[0], rms[1], x)   # the norm kernel adds the pending delta on its way
             ops.rope_cache_write(ops.linear(x, self.qkv_weight), ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim,
                                  self.n_heads, q, args, writes_cache, ctx.err, bias=self.qkv_bias_t)
+        n_splits = self.decode_splits(ctx)
+        if o_way == "skinny" and n == ctx.n_seqs and ops.fold_project_takes(n, self.o_weight, hidden, self.n_heads, self.head_dim):
+            # the attention kernel stops at its runs' partial results; the projection folds them on its way in
+            ops.attention_decode(q, None, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, self.scale,
+                                 self.window, n_splits, ctx.decode_scratch, ctx.err, plan, fold_later=True)
+            ops.fold_project(plan, ctx.decode_scratch, self.o_weight, hidden, self.n_heads, self.head_dim, n_splits)
+            return
         attended = torch.empty_like(q)
         ops.attention_decode(q, attended, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs,
-                             self.scale, self.window, self.decode_splits(ctx), ctx.decode_scratch, ctx.err, plan)
+                             self.scale, self.window, n_splits, ctx.decode_scratch, ctx.err, plan)
         if o_way == "skinny":
             ops.skinny_gemm(ops.EPI_RESIDUAL, self.o_weight, x=attended, residual=hidden)
         elif o_way == "wide":

@@ -496,7 +496,13 @@ def decode_plan_records(ops, lengths, kvh, nh, d, n_splits, slots=None, window=0
     tok_pos = torch.tensor([length - 1 for length in lengths], dtype=torch.int32, device=DEV)
     plan = ops.attention_decode_plan(cu, tok_pos, torch.tensor(slots, dtype=torch.int32, device=DEV), kvh, d, nh, n,
                                      window, n_splits, ops.DecodeScratch(DEV))
-    return plan.cpu().tolist()
+    table = plan.cpu().flatten()[:n].tolist()   # the plan's first part: every sequence's number of runs
+    records = plan.cpu()[(n + 3) // 4:].tolist()
+    at = 0
+    for count in table:
+        assert records[at][1] >> 16 == count
+        at += count
+    return records
 
 
 def test_attention_decode_plan(ops):
@@ -532,6 +538,67 @@ def test_attention_decode_plan(ops):
         longest = max(range(16), key=lambda i: ragged[i])
         records = decode_plan_records(ops, ragged, 2, 16, 128, 9)
         assert max(r[1] >> 16 for r in records if r[0] == longest) >= 4   # the long one among short ones gets many blocks
+
+
+@pytest.mark.parametrize("nh,kvh,d,lengths,n_out,n_splits,slots", [
+    (14, 2, 64, [700, 64, 1, 2275, 130, 4000, 9, 333], 896, 8, None),     # the engine's shape at batch 8
+    (16, 2, 128, [1200, 5], 2048, 5, None),
+    (6, 3, 96, [300, 77, 1000], 272, 4, [2, -1, 0]),                      # a padding entry; outputs no multiple of 64
+    (4, 4, 32, [50], 48, 1, None),                                        # one run only: partial results all the same
+    (28, 4, 128, [600] * 16, 400, 3, None),                               # sixteen rows
+])
+def test_fold_project(ops, nh, kvh, d, lengths, n_out, n_splits, slots):
+    """The decode attention stopped at its partial results, and the projection that folds them on its way in, against
+    the attention kernel's own fold followed by a float64 product, and against the plain attention."""
+    n = len(lengths)
+    slots = slots if slots is not None else list(range(n))[::-1]
+    site = FakeSite(n, max(lengths), kvh, d, torch.bfloat16, 31)
+    for slot, length in zip(slots, lengths):
+        if slot >= 0:
+            fill_site(site, slot, length, 31 + slot, torch.bfloat16)
+    g = torch.Generator().manual_seed(32)
+    q = torch.randn(n, nh * d, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n_out, nh * d, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    before = torch.randn(n, n_out, generator=g).to(DEV)
+    cu = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([length - 1 for length in lengths], dtype=torch.int32, device=DEV)
+    slots_t = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    args = ops.KvSiteArgs(site.storage, site.table, kvh, d)
+    e = err_word()
+    assert ops.fold_project_takes(n, w, before, nh, d)
+    scratch = ops.DecodeScratch(DEV)
+    for _ in range(2):   # twice: nothing of the first call may be left in the scratch's way
+        hidden = before.clone()
+        plan = ops.attention_decode_plan(cu, tok_pos, slots_t, kvh, d, nh, n, 0, n_splits, scratch)
+        ops.attention_decode(q, None, cu, tok_pos, slots_t, args, nh, n, d ** -0.5, 0, n_splits, scratch, e, plan, fold_later=True)
+        ops.fold_project(plan, scratch, w, hidden, nh, d, n_splits)
+    attended = torch.empty_like(q)
+    ops.attention_decode(q, attended, cu, tok_pos, slots_t, args, nh, n, d ** -0.5, 0, n_splits, ops.DecodeScratch(DEV), e)
+    assert int(e) == 0
+    own = before.double() + attended.double() @ w.double().T
+    bound = max(1.0, float(own.abs().max()))
+    assert max_err(hidden, own) <= 1e-3 * bound
+    plain = torch.empty_like(q)
+    ref.attention_generic(q, plain, cu, tok_pos, slots_t, site, nh, n, 1, d ** -0.5, 0, None)
+    assert max_err(hidden, before.double() + plain.double() @ w.double().T) <= 2e-2 * bound
+    for r, slot in enumerate(slots):
+        if slot < 0:
+            assert torch.equal(hidden[r], before[r])
+
+
+def test_fold_project_refuses_what_it_cannot_take(ops):
+    hidden = torch.zeros(4, 100, device=DEV)
+    w = torch.zeros(100, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops.fold_project_takes(4, w, hidden, 4, 64)           # outputs no multiple of 16
+    w = torch.zeros(96, 4 * 48, dtype=torch.bfloat16, device=DEV)
+    assert not ops.fold_project_takes(4, w, torch.zeros(4, 96, device=DEV), 4, 48)    # a head is no multiple of 32 inputs
+    w = torch.zeros(4096, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops.fold_project_takes(4, w, torch.zeros(4, 4096, device=DEV), 4, 64)  # the slice does not fit shared memory
+    w = torch.zeros(96, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops.fold_project_takes(17, w, torch.zeros(17, 96, device=DEV), 4, 64)  # too many rows
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.fold_project(torch.zeros(8, 4, dtype=torch.int32, device=DEV), ops.DecodeScratch(DEV), w,
+                         torch.zeros(17, 96, device=DEV), 4, 64, 2)
 
 
 def test_attention_decode_padding_and_far_key(ops):
