@@ -102,8 +102,17 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, bf16* __restrict__ out,
                     const int* __restrict__ cu_q, const int4* __restrict__ plan, KvSite<bf16> site, int n_heads, int chunks, float scale_log2,
                     int window, int max_splits, int n_seqs, int fold_later, float* __restrict__ part_o,
-                    float* __restrict__ part_ml, int* __restrict__ counters, int* err) {
+                    float* __restrict__ part_ml, int* __restrict__ counters, int* err, unsigned long long* stamps) {
     constexpr int DEC_WARPS = WARPS, DEC_THREADS = WARPS * 32;
+    // measuring aid: if `stamps` is given, thread 0 leaves nanosecond time stamps of the block's phases in stamps[block][8]
+    auto stamp = [&](int phase) {
+        if (stamps && threadIdx.x == 0) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            stamps[(size_t)blockIdx.x * 8 + phase] = now;
+        }
+    };
+    stamp(0);
     constexpr int LD = TMA ? D : D + 8;  // shared-memory row (bf16 elements): padded, or swizzled blocks of 64 columns
     constexpr int KS = D / 16;          // k-steps of Q K^T
     constexpr int NT = D / 8;           // n-tiles of P V
@@ -223,7 +232,9 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     const int page0_end = (p_begin + warp + 1) * QF_PAGE;
     const int n_early = n_halves == 0 ? 0 : page0_end <= L - 1 ? 2 : page0_end - HALF <= L - 1 ? 1 : 0;
     for (int i = 0; i < n_early; ++i) issue(i);
+    stamp(1);
     grid_dependency_wait();
+    stamp(2);
 
     // Q fragments: row r = lane / 4 (and r + 8) is query head head0 + r; rows beyond the group are zero
     uint32_t qa[KS][4];
@@ -254,6 +265,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
             // the barrier of this buffer is on its (i / 2)-th use; only halves that were fetched are waited for
             if (live && !mbar_wait(&bars[warp][i & 1], tma_uses[i & 1] & 1) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
             if (live) ++tma_uses[i & 1];
+            if (i == 0) stamp(3);
         } else {
             cp_async_wait<1>();
             __syncwarp();  // each lane waited for its own copies; together the half page is complete
@@ -350,6 +362,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         __syncwarp();  // every lane has read this buffer before the copies of half i + 2 overwrite it
     }
     if (!TMA) cp_async_wait<0>();
+    stamp(4);
 
     // ---- merge the warps: every warp leaves its numerators, rescaled to the block's maximum, in its own page buffer
     // (its copies are complete and nobody else read it); then all threads add the warps up, in warp order
@@ -380,6 +393,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         *reinterpret_cast<float2*>(o_w + r1 * OLD + c) = make_float2(o[nt][2] * f[1], o[nt][3] * f[1]);
     }
     __syncthreads();
+    stamp(5);
     // block result: row r: maximum max_w m_s[w][r], sum sum_w l_s[w][r], numerator sum_w (warp w's buffer)[r][:]
     const size_t part_row0 = ((size_t)seq * n_heads + head0) * max_splits;  // partial index of (row 0, split 0)
     for (int i = threadIdx.x; i < n_g * D; i += DEC_THREADS) {
@@ -407,7 +421,10 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         part_ml[(part_row0 + (size_t)r * max_splits + split) * 2] = m;
         part_ml[(part_row0 + (size_t)r * max_splits + split) * 2 + 1] = l;
     }
-    if (fold_later) return;  // the kernel that comes next folds the partial results itself
+    if (fold_later) {  // the kernel that comes next folds the partial results itself
+        stamp(6);
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -422,6 +439,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         ticket_s = ticket;
     }
     __syncthreads();
+    stamp(6);
     if (ticket_s != n_splits - 1) return;
     // Every group of four output elements folds its row's partials in split order, eight at a time, keeping a running
     // maximum: out = sum_s exp2(m_s - M) o_s / sum_s exp2(m_s - M) l_s. A thread takes two groups at once, which covers
@@ -486,6 +504,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
                 *reinterpret_cast<uint2*>(out_row + (size_t)(i0 + x * DEC_THREADS) * 4) = packed;
             }
     }
+    stamp(7);
 }
 
 // (sequence, run) pairs of any plan: every sequence has one, and the runs beyond that fill the SMs at most once
@@ -498,7 +517,8 @@ static long long plan_pairs(int n_seqs, int kv_heads, int n_heads, int n_splits)
 template <int D>
 static int launch(const void* q, void* out, const int* cu_q, const int4* plan, void* base, const int* table,
                   long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
-                  int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
+                  int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err,
+                  unsigned long long* stamps, cudaStream_t stream) {
     constexpr int WARPS = D <= 64 ? 8 : 4;  // two half-page buffers per warp: 16 to 18 KB at D = 64, 33 to 35 KB at D = 128
     constexpr bool TMA = D % 64 == 0;
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
@@ -515,7 +535,7 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
     dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
                            (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
-                           n_seqs, fold_later, part_o, part_ml, counters, err);
+                           n_seqs, fold_later, part_o, part_ml, counters, err, stamps);
 }
 
 // How many 16-byte units a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode
@@ -543,17 +563,17 @@ QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, cons
 // first call (the kernel leaves them zero; not used with fold_later). With fold_later the kernel stops at the partial
 // results (every sequence's runs, as many as the plan's first part says) and writes no `out`: the caller's next
 // kernel folds them. Returns cudaErrorInvalidValue for a head size without an instantiation.
-QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, const void* plan, void* base,
-                                  const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
-                                  int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
-                                  float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
+static int decode_run(const void* q, void* out, const int* cu_q, const void* plan, void* base, const int* table,
+                      long long page_elems, int table_stride, int kv_heads, int head_dim, int n_heads, int n_seqs,
+                      float scale, int window, int n_splits, int fold_later, float* part_o, float* part_ml, int* counters,
+                      int* err, unsigned long long* stamps, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !plan) return (int)cudaErrorInvalidValue;
     if (fold_later ? (!part_o || !part_ml) : !out) return (int)cudaErrorInvalidValue;
 #define QF_CASE(DIM)                                                                                                   \
     case DIM:                                                                                                          \
         return launch<DIM>(q, out, cu_q, (const int4*)plan, base, table, page_elems, table_stride, kv_heads, n_heads, \
-                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stream);
+                           n_seqs, scale, window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, stream);
     switch (head_dim) {
         QF_CASE(32)
         QF_CASE(64)
@@ -563,6 +583,27 @@ QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, con
             return (int)cudaErrorInvalidValue;
     }
 #undef QF_CASE
+}
+
+QF_EXPORT int qf_attention_decode(const void* q, void* out, const int* cu_q, const void* plan, void* base,
+                                  const int* table, long long page_elems, int table_stride, int kv_heads, int head_dim,
+                                  int n_heads, int n_seqs, float scale, int window, int n_splits, int fold_later,
+                                  float* part_o, float* part_ml, int* counters, int* err, cudaStream_t stream) {
+    return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, nullptr, stream);
+}
+
+// A measuring aid: the same launch, with every block's thread 0 writing nanosecond time stamps to stamps[block][8]:
+// entry, early copies issued, the kernel before done, first half page arrived, pages done, warps merged, ticket drawn
+// (or partial results written, with fold_later), fold done (the folding blocks only). The grid has
+// kv_heads * ceil(group / 16) * (qf_attention_decode_plan_size(...) - ceil(n_seqs / 4)) blocks.
+QF_EXPORT int qf_attention_decode_stamped(const void* q, void* out, const int* cu_q, const void* plan, void* base,
+                                          const int* table, long long page_elems, int table_stride, int kv_heads,
+                                          int head_dim, int n_heads, int n_seqs, float scale, int window, int n_splits,
+                                          int fold_later, float* part_o, float* part_ml, int* counters, int* err,
+                                          unsigned long long* stamps, cudaStream_t stream) {
+    return decode_run(q, out, cu_q, plan, base, table, page_elems, table_stride, kv_heads, head_dim, n_heads, n_seqs, scale,
+                      window, n_splits, fold_later, part_o, part_ml, counters, err, stamps, stream);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

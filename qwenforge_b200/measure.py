@@ -7,6 +7,7 @@ attention kernels compare. Every figure is the mean of CUDA-graph replays timed 
     python -m qwenforge_b200.measure chain    --preset qwen2.5-0.5b --rows 8
     python -m qwenforge_b200.measure phases   --preset qwen2.5-0.5b --rows 1,64
     python -m qwenforge_b200.measure attention --tokens 1024,2048,4096 --heads 14 --kv-heads 2 --head-dim 64
+    python -m qwenforge_b200.measure decode-attention --lengths 4000,4000,4000,4000,4000,4000,4000,4000 --splits 8
     python -m qwenforge_b200.measure gemm --preset qwen2.5-0.5b --rows 2048,16384
 
 products   per product of a layer (output projection, gate/up, down, query/key/value): the weight-streaming kernel of
@@ -16,6 +17,9 @@ chain      the four products after attention as separate kernels, as ONE persist
            (skinny_chain.cu), and all layers' products inside one launch (the persistent kernel's steady state)
 phases     wide_gemm.cu's own time stamps: when a block's copies, products, exchange and epilogue end
 attention  the mma.sync and the tcgen05 prefill attention on one prompt, with a tile's pages shared or not
+decode-attention  the split-K decode attention's own time stamps (launched alone, cold caches): which runs the plan
+           gives every sequence, and when a block's copies, pages, merge, ticket and fold end; with and without the
+           projection that folds the partial results
 gemm       a feed-forward's gate/up product on many rows: the library product, the library product and the gate kernel,
            this library's tcgen05 product (one tile per block, and persistent) plain and with the gate in its epilogue
 """
@@ -275,6 +279,76 @@ def measure_attention(args) -> None:
             raise RuntimeError(f"a kernel reported error word {int(err)}")
 
 
+DECODE_PHASES = ["entry", "early copies issued", "the kernel before done", "first half page arrived", "pages done",
+                 "warps merged", "ticket drawn / partial results written", "fold done"]
+
+
+def measure_decode_attention(args) -> None:
+    """Time stamps of the phases of the split-K decode attention's blocks (and of the projection that folds its partial
+    results), launched alone on cold caches: --lengths gives the sequences' lengths, --heads/--kv-heads/--head-dim the
+    shape, --splits the most runs per sequence."""
+    from .csrc import library
+    from .ops import kernels
+    lib = library("attention_decode")
+    lib.qf_attention_decode_plan_size.restype = ctypes.c_longlong
+    heads, kv_heads, d, lengths, n_splits = args.heads, args.kv_heads, args.head_dim, args.lengths, args.splits
+    n = len(lengths)
+    pages = Pages(n, max(lengths), kv_heads, d, "cuda", 1)
+    pages.storage.copy_(torch.randn(pages.storage.shape, device="cuda").to(torch.bfloat16))
+    q = torch.randn(n, heads * d, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    cu = torch.arange(n + 1, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([length - 1 for length in lengths], dtype=torch.int32, device="cuda")
+    slots = torch.arange(n, dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    scratch = ops.DecodeScratch("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    site = pages.args()
+    kvc = kv_heads * (-(-(heads // kv_heads) // 16))
+    records = int(lib.qf_attention_decode_plan_size(n, kv_heads, heads, n_splits)) - (n + 3) // 4
+    hidden = torch.zeros(n, heads * d, device="cuda")
+    o_w = (torch.randn(heads * d, heads * d, device="cuda") * 0.05).bfloat16()
+    folds = n <= 16 and ops.fold_project_takes(n, o_w, hidden, heads, d)
+    for fold_later in ([False, True] if folds else [False]):
+        stamps = torch.zeros(records * kvc, 8, dtype=torch.int64, device="cuda")
+        for it in range(4):
+            flush.fill_(it)
+            stamps.zero_()
+            plan = ops.attention_decode_plan(cu, pos, slots, kv_heads, d, heads, n, 0, n_splits, scratch)
+            scratch.ensure(n, heads, n_splits, d, n * kvc)
+            torch.cuda.synchronize()
+            start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            start.record()
+            kernels._check(lib.qf_attention_decode_stamped(
+                kernels._ptr(q), kernels._ptr(out), kernels._ptr(cu), kernels._ptr(plan), kernels._ptr(site.storage),
+                kernels._ptr(site.table), ctypes.c_longlong(site.page_elems), ctypes.c_int(site.table_stride),
+                ctypes.c_int(kv_heads), ctypes.c_int(d), ctypes.c_int(heads), ctypes.c_int(n), ctypes.c_float(d ** -0.5),
+                ctypes.c_int(0), ctypes.c_int(n_splits), ctypes.c_int(int(fold_later)), kernels._ptr(scratch.part_o),
+                kernels._ptr(scratch.part_ml), kernels._ptr(scratch.counters), kernels._ptr(err),
+                kernels._ptr(stamps), kernels._stream()), "attention_decode")
+            mid.record()
+            if fold_later:
+                ops.fold_project(plan, scratch, o_w, hidden, heads, d, n_splits)
+            end.record()
+            torch.cuda.synchronize()
+        if int(err):
+            raise RuntimeError(f"a kernel reported error word {int(err)}")
+        st = stamps.cpu()
+        st = st[st[:, 0] > 0]
+        t0 = int(st[:, 0].min())
+        runs = plan.cpu().flatten()[:n].tolist()
+        mb = sum(lengths) * kv_heads * d * 2 * 2 / 1e6
+        how = "stopping at the partial results" if fold_later else "folding its partial results itself"
+        print(f"{n} sequences of {min(lengths)} to {max(lengths)} tokens, {heads}/{kv_heads} heads of {d}, {how}: {st.shape[0]} blocks, "
+              f"runs per sequence {runs}, {mb:.1f} MB of keys and values; launched alone on cold caches: "
+              f"{start.elapsed_time(mid) * 1e3:.1f} us" + (f", then the projection that folds {mid.elapsed_time(end) * 1e3:.1f} us" if fold_later else ""))
+        for k, name in enumerate(DECODE_PHASES):
+            col = st[:, k]
+            col = (col[col > 0] - t0).double() / 1e3
+            if len(col):
+                print(f"    {name:40s} mean {float(col.mean()):6.2f}  last {float(col.max()):6.2f} us  ({len(col)} blocks)")
+
+
 def measure_gemm(args) -> None:
     from .csrc import library
     hidden, inter, _, _, _ = sizes_of(args.preset)
@@ -341,7 +415,7 @@ def measure_gemm(args) -> None:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="qwenforge_b200.measure", description=__doc__.split("\n\n")[0])
-    p.add_argument("what", choices=["products", "chain", "phases", "attention", "gemm"])
+    p.add_argument("what", choices=["products", "chain", "phases", "attention", "decode-attention", "gemm"])
     p.add_argument("--preset", default="qwen2.5-0.5b")
     p.add_argument("--rows", default="8", type=lambda text: [int(v) for v in text.split(",")])
     p.add_argument("--repeat", type=int, default=12, help="layers, each with weights of its own, captured into one graph")
@@ -349,11 +423,14 @@ def main(argv=None) -> int:
     p.add_argument("--heads", type=int, default=14)
     p.add_argument("--kv-heads", type=int, default=2)
     p.add_argument("--head-dim", type=int, default=64)
+    p.add_argument("--lengths", default="4000,4000,4000,4000,4000,4000,4000,4000", type=lambda text: [int(v) for v in text.split(",")],
+                   help="decode-attention: the sequences' lengths")
+    p.add_argument("--splits", type=int, default=8, help="decode-attention: the most runs of pages per sequence")
     args = p.parse_args(argv)
     ops.require_cuda("cuda", "the measurement")
     with torch.inference_mode():
         {"products": measure_products, "chain": measure_chain, "phases": measure_phases, "attention": measure_attention,
-         "gemm": measure_gemm}[args.what](args)
+         "decode-attention": measure_decode_attention, "gemm": measure_gemm}[args.what](args)
     return 0
 
 
