@@ -225,7 +225,7 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         }
         if (!TMA) cp_async_commit();  // one group per half, empty when there is nothing to fetch
     };
-    uint32_t tma_uses[2] = {0, 0};  // completed fetches into each buffer (the parity the next wait looks for)
+    uint32_t uses_even = 0, uses_odd = 0;  // completed fetches into each buffer (the parity the next wait looks for)
     // Positions before the new token lie in the cache since earlier steps: the halves of the warp's first page that
     // hold only such positions are fetched before this kernel waits for the one that wrote the new token's query,
     // key and value.
@@ -263,8 +263,12 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
         const bool live = half_live(i, page_i, key0);
         if (TMA) {
             // the barrier of this buffer is on its (i / 2)-th use; only halves that were fetched are waited for
-            if (live && !mbar_wait(&bars[warp][i & 1], tma_uses[i & 1] & 1) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
-            if (live) ++tma_uses[i & 1];
+            const uint32_t parity = ((i & 1) ? uses_odd : uses_even) & 1;
+            if (live && !mbar_wait(&bars[warp][i & 1], parity) && lane == 0) atomicOr(err, QF_ERR_COPY_TIMEOUT);
+            if (live) {
+                uses_even += (i & 1) ^ 1;
+                uses_odd += i & 1;
+            }
             if (i == 0) stamp(3);
         } else {
             cp_async_wait<1>();
