@@ -28,9 +28,9 @@
 // ---- The plan of a step: which block takes which run of which sequence. The lengths live on the device (a captured
 // graph replays these launches with other lengths every step), so one warp works the plan out once per step, for every
 // layer whose attention has the same shape. A sequence of P pages is cut into ceil(P / target) runs of equal size,
-// target being the pages per block at which the batch's pages fill the SMs once (and at least one page per warp of a
-// block); where the rounding up gives more blocks than SMs, target grows until they fit, so that no block waits for
-// a free SM while others are done. Sequences of unequal lengths thus get blocks of about
+// target being the pages per block at which the batch's pages fill the device's block slots once (and at least one
+// page per warp of a block); where the rounding up gives more blocks than slots, target grows until they fit, so that
+// no block waits for a free slot while others are done. Sequences of unequal lengths thus get blocks of about
 // equal work, and a batch that fills the SMs unsplit stays unsplit.
 // The plan starts with the number of runs of every sequence (n_seqs ints, padded to a multiple of four), for whoever
 // folds the partial results later; the block records follow. Record j < n_pairs: x = sequence (batch entry; -1: no such
@@ -511,11 +511,54 @@ decode_split_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __re
     stamp(7);
 }
 
-// (sequence, run) pairs of any plan: every sequence has one, and the runs beyond that fill the SMs at most once
-static long long plan_pairs(int n_seqs, int kv_heads, int n_heads, int n_splits) {
+// Warps of a block: each has two half-page buffers (16 to 18 KB at D = 64, 33 to 35 KB at D = 128). Eight up to head
+// size 64, four beyond. (Three at head size 128, so that two blocks share an SM and a batch of 64 sequences x 4 kv heads
+// is resident at once instead of in two unequal waves, was measured: 537 MB in 104 microseconds against 99.)
+constexpr int decode_warps(int d) { return d <= 64 ? 8 : 4; }
+constexpr bool decode_tma(int d) { return d % 64 == 0; }
+constexpr size_t decode_smem(int d) {
+    return (size_t)decode_warps(d) * 2 * QF_PAGE * (decode_tma(d) ? d : d + 8) * sizeof(bf16) + 1024;
+}
+
+// Blocks of decode_split_kernel<D> that one SM holds at once (0: no kernel for this head size).
+template <int D>
+static int resident_blocks() {
+    static int held = -1;
+    if (held < 0) {
+        auto kernel = decode_split_kernel<D, decode_warps(D), decode_tma(D)>;
+        int n = 0;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(D)) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, decode_warps(D) * 32, decode_smem(D)) != cudaSuccess)
+            n = 1;
+        held = n > 0 ? n : 1;
+    }
+    return held;
+}
+
+// Block slots of the device for this head size: what a plan may fill once.
+static int decode_slots(int head_dim) {
     const int sms = qf_sm_count() > 0 ? qf_sm_count() : 1;
+    switch (head_dim) {
+        case 32: return sms * resident_blocks<32>();
+        case 64: return sms * resident_blocks<64>();
+        case 96: return sms * resident_blocks<96>();
+        case 128: return sms * resident_blocks<128>();
+        default: return 0;
+    }
+}
+
+// (sequence, run) pairs of any plan: every sequence has one, and the runs beyond that fill the block slots at most once
+static long long plan_pairs(int n_seqs, int kv_heads, int n_heads, int head_dim, int n_splits) {
     const long long kvc = (long long)kv_heads * ((n_heads / kv_heads + 15) / 16);
-    return std::min((long long)n_seqs * n_splits, (long long)n_seqs + sms / kvc);
+    return std::min((long long)n_seqs * n_splits, (long long)n_seqs + decode_slots(head_dim) / kvc);
+}
+
+// Blocks of the decode attention that the device holds at once at this head size (0: no kernel for this head size).
+QF_EXPORT int qf_attention_decode_slots(int head_dim) { return decode_slots(head_dim); }
+
+// Warps of a block at this head size: the pages that one run should hold at least (0: no kernel for this head size).
+QF_EXPORT int qf_attention_decode_warps(int head_dim) {
+    return head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128 ? decode_warps(head_dim) : 0;
 }
 
 template <int D>
@@ -523,10 +566,10 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
                   long long page_elems, int table_stride, int kv_heads, int n_heads, int n_seqs, float scale, int window,
                   int n_splits, int fold_later, float* part_o, float* part_ml, int* counters, int* err,
                   unsigned long long* stamps, cudaStream_t stream) {
-    constexpr int WARPS = D <= 64 ? 8 : 4;  // two half-page buffers per warp: 16 to 18 KB at D = 64, 33 to 35 KB at D = 128
-    constexpr bool TMA = D % 64 == 0;
+    constexpr int WARPS = decode_warps(D);
+    constexpr bool TMA = decode_tma(D);
     const int G = n_heads / kv_heads, chunks = (G + 15) / 16;
-    const size_t smem = (size_t)WARPS * 2 * QF_PAGE * (TMA ? D : D + 8) * sizeof(bf16) + 1024;
+    const size_t smem = decode_smem(D);
     cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D, WARPS, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     KvSite<bf16> site{(bf16*)base, table, page_elems, table_stride, kv_heads, D};
@@ -536,7 +579,7 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
         // (its extent only bounds what a copy may address; copies address rows of held pages only).
         if (!qf_make_map_bf16(&kv_map, base, 1ll << 31, D, D, QF_PAGE / 2)) return (int)cudaErrorNotSupported;
     }
-    dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, n_splits) * kv_heads * chunks));
+    dim3 grid((unsigned)(plan_pairs(n_seqs, kv_heads, n_heads, D, n_splits) * kv_heads * chunks));
     return (int)launch_pdl(decode_split_kernel<D, WARPS, TMA>, grid, dim3(WARPS * 32), smem, stream, kv_map, (const bf16*)q,
                            (bf16*)out, cu_q, plan, site, n_heads, chunks, scale * 1.4426950408889634f, window, n_splits,
                            n_seqs, fold_later, part_o, part_ml, counters, err, stamps);
@@ -544,9 +587,9 @@ static int launch(const void* q, void* out, const int* cu_q, const int4* plan, v
 
 // How many 16-byte units a plan of this shape holds (what qf_attention_decode_plan writes and qf_attention_decode
 // reads): the sequences' numbers of runs, then the block records.
-QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int n_heads, int n_splits) {
-    if (n_seqs <= 0 || kv_heads <= 0 || n_heads % kv_heads || n_splits < 1) return 0;
-    return (n_seqs + 3) / 4 + plan_pairs(n_seqs, kv_heads, n_heads, n_splits);
+QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int n_heads, int head_dim, int n_splits) {
+    if (n_seqs <= 0 || kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || !qf_attention_decode_warps(head_dim)) return 0;
+    return (n_seqs + 3) / 4 + plan_pairs(n_seqs, kv_heads, n_heads, head_dim, n_splits);
 }
 
 // The plan of one step for attention of this shape (see decode_plan_kernel); the same plan serves every layer of the
@@ -554,12 +597,12 @@ QF_EXPORT long long qf_attention_decode_plan_size(int n_seqs, int kv_heads, int 
 QF_EXPORT int qf_attention_decode_plan(const int* cu_q, const int* tok_pos, const int* slots, int n_seqs, int kv_heads,
                                        int head_dim, int n_heads, int window, int n_splits, void* plan, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || n_splits > 0x7fff) return (int)cudaErrorInvalidValue;
-    const int sms = qf_sm_count() > 0 ? qf_sm_count() : 1;
+    if (kv_heads <= 0 || n_heads % kv_heads || n_splits < 1 || n_splits > 0x7fff || !qf_attention_decode_warps(head_dim))
+        return (int)cudaErrorInvalidValue;
     const int kvc = kv_heads * ((n_heads / kv_heads + 15) / 16);
-    return (int)launch_pdl(decode_plan_kernel, dim3(1), dim3(32), 0, stream, cu_q, tok_pos, slots, n_seqs, kvc, sms,
-                           head_dim <= 64 ? 8 : 4, window, n_splits, (int4*)plan,
-                           (int)plan_pairs(n_seqs, kv_heads, n_heads, n_splits));
+    return (int)launch_pdl(decode_plan_kernel, dim3(1), dim3(32), 0, stream, cu_q, tok_pos, slots, n_seqs, kvc,
+                           decode_slots(head_dim), qf_attention_decode_warps(head_dim), window, n_splits, (int4*)plan,
+                           (int)plan_pairs(n_seqs, kv_heads, n_heads, head_dim, n_splits));
 }
 
 // Scratch (used when n_splits > 1 or fold_later): part_o float32 [n_seqs * n_heads * n_splits * head_dim], part_ml
@@ -644,7 +687,7 @@ QF_EXPORT int qf_attention_decode_noalloc(const void* q, void* out, const int* c
     }
     const long long rows = (long long)n_seqs * n_heads * n_splits;
     const long long n_counters = (long long)n_seqs * kv_heads * ((n_heads / kv_heads + 15) / 16);
-    const long long pairs = qf_attention_decode_plan_size(n_seqs, kv_heads, n_heads, n_splits);
+    const long long pairs = qf_attention_decode_plan_size(n_seqs, kv_heads, n_heads, head_dim, n_splits);
     if (pairs > QF_NOALLOC_MAX_PAIRS) {
         snprintf(qf_noalloc_message, sizeof qf_noalloc_message,
                  "qf_attention_decode_noalloc: a plan of %lld units of 16 bytes (limit %d): beyond the built-in scratch; "

@@ -305,7 +305,7 @@ def measure_decode_attention(args) -> None:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     site = pages.args()
     kvc = kv_heads * (-(-(heads // kv_heads) // 16))
-    records = int(lib.qf_attention_decode_plan_size(n, kv_heads, heads, n_splits)) - (n + 3) // 4
+    records = int(lib.qf_attention_decode_plan_size(n, kv_heads, heads, d, n_splits)) - (n + 3) // 4
     hidden = torch.zeros(n, heads * d, device="cuda")
     o_w = (torch.randn(heads * d, heads * d, device="cuda") * 0.05).bfloat16()
     folds = n <= 16 and ops.fold_project_takes(n, o_w, hidden, heads, d)

@@ -321,6 +321,12 @@ class DecodeScratch:
             self.counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
 
 
+def attention_decode_warps(head_dim: int) -> int:
+    """Warps of a block of the decode attention at this head size (each takes one page at a time): the fewest pages
+    that a run of a sequence should hold."""
+    return int(library("attention_decode").qf_attention_decode_warps(_I(head_dim)))
+
+
 def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor, kv_heads: int, head_dim: int,
                           n_heads: int, n_seqs: int, window: int, n_splits: int, scratch: DecodeScratch) -> torch.Tensor:
     """The plan of one decode step for attention of this shape: which block takes which run of which sequence, worked
@@ -336,7 +342,9 @@ def attention_decode_plan(cu_q: torch.Tensor, tok_pos: torch.Tensor, slots: torc
         raise KernelError(f"attention_decode: {n_heads} heads do not divide into {kv_heads} groups")
     lib = library("attention_decode")
     lib.qf_attention_decode_plan_size.restype = ctypes.c_longlong
-    records = int(lib.qf_attention_decode_plan_size(_I(n_seqs), _I(kv_heads), _I(n_heads), _I(n_splits)))
+    records = int(lib.qf_attention_decode_plan_size(_I(n_seqs), _I(kv_heads), _I(n_heads), _I(head_dim), _I(n_splits)))
+    if records <= 0:
+        raise KernelError(f"attention_decode: head_dim {head_dim} has no tensor-core kernel (have {FAST_ATTENTION_HEAD_DIMS})")
     plan = scratch.plan((n_seqs, kv_heads, n_heads, head_dim, window, n_splits), records)
     _check(lib.qf_attention_decode_plan(_ptr(cu_q), _ptr(tok_pos), _ptr(slots), _I(n_seqs), _I(kv_heads), _I(head_dim),
                                         _I(n_heads), _I(window), _I(n_splits), _ptr(plan), _stream()), "attention_decode_plan")

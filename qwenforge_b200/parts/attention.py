@@ -207,13 +207,13 @@ class GqaAttention(Mixer):
         return plan
 
     def decode_splits(self, ctx) -> int:
-        """The most blocks that may share one (sequence, kv head): a block's warps take one page each (8 warps up to
-        head size 64, else 4), so at most one split per that many pages of the longest sequence that the step allows.
+        """The most blocks that may share one (sequence, kv head): a block's warps take one page each
+        (`ops.attention_decode_warps`), so at most one split per that many pages of the longest sequence that the step allows.
         How many of them a sequence gets is the kernel's decision, from the lengths on the device; this number sizes
         its grid and scratch and depends on the batch's shape only (fixed inside a captured graph)."""
         span = ctx.max_kv_len if self.window <= 0 else min(ctx.max_kv_len, self.window + PAGE_TOKENS)
         pages = max(1, -(-span // PAGE_TOKENS))
-        warps = 8 if self.head_dim <= 64 else 4
+        warps = ops.attention_decode_warps(self.head_dim)
         return max(1, min(-(-pages // warps), 64))
 
 
