@@ -83,15 +83,22 @@ class _GraphSession:
         cache.flush()
         self.graph.load(self.slots, [r[1] for r in rows], [cache.lengths[r[0]] for r in rows], [r[3] for r in rows],
                         [r[4] for r in rows], [r[2] for r in rows], stop_token_ids)
+        self.in_flight = 0   # steps already on the stream whose tokens have not been read
 
     def run(self, n_steps: int) -> list:
-        produced = self.graph.run(n_steps)
+        """The next chunk's tokens, per step and row. The rows' state lives on the device, and a row that ends turns
+        into a padding entry there by itself, so the chunk after this one goes onto the stream as soon as the device
+        says that some row is still live, before the host has looked at a single token: the GPU works on it while the
+        caller applies its decisions to this chunk."""
+        n = self.in_flight or self.graph.enqueue(n_steps)
+        produced, left, err = self.graph.collect(n)
+        self.in_flight = self.graph.enqueue(left) if left > 0 else 0
         cache = self.stepper.cache
         for row, slot in enumerate(self.slots):
             fed = sum(1 for step_tokens in produced if step_tokens[row] >= 0)
             if fed:
                 cache.advance(slot, fed)
-        if int(self.stepper.model.err.item()):
+        if err:
             self.stepper.model.raise_on_kernel_error()
         return [step_tokens[:len(self.slots)] for step_tokens in produced]
 

@@ -127,14 +127,28 @@ class DecodeGraph:
         self.cursor.zero_()
         self.slots.copy_(saved)
 
-    def run(self, n_steps: int) -> list:
-        """Replay `n_steps` (<= CHUNK_STEPS) steps; returns per step the rows' produced tokens (-1: none)."""
+    def enqueue(self, n_steps: int) -> int:
+        """Put `n_steps` (at most CHUNK_STEPS) steps on the stream; returns how many. Their tokens overwrite those of the
+        chunk before: collect that one first."""
         n_steps = min(n_steps, CHUNK_STEPS)
         self.cursor.zero_()
         for _ in range(n_steps):
             self.graph.replay()
         ops.kernels.launches += self.kernels_per_step * n_steps
-        return self.out_tokens[:n_steps].tolist()
+        return n_steps
+
+    def collect(self, n_steps: int) -> tuple:
+        """Wait for the enqueued chunk of `n_steps` steps and read it back in ONE copy: per step the rows' produced
+        tokens (-1: none), the most steps any row still has to go (0: every row has ended), the device error word."""
+        rows = self.rows
+        left = torch.where(self.slots >= 0, self.budgets - self.steps, torch.zeros_like(self.steps))
+        packed = torch.cat((self.out_tokens[:n_steps].flatten(), left, self.model.err)).tolist()
+        tokens = [packed[i * rows:(i + 1) * rows] for i in range(n_steps)]
+        return tokens, max(packed[n_steps * rows:n_steps * rows + rows], default=0), packed[-1]
+
+    def run(self, n_steps: int) -> list:
+        """Replay `n_steps` (<= CHUNK_STEPS) steps; returns per step the rows' produced tokens (-1: none)."""
+        return self.collect(self.enqueue(n_steps))[0]
 
 
 class GraphDecoder:

@@ -227,3 +227,56 @@ def test_prompt_steps_are_rounded_to_shapes_that_come_back():
     exact = [(0, 0, list(range(128)))]
     same = PrefillGraphs.rounded(pack_step(exact, None), exact, None)
     assert same.shape_key == (128, 1, 128, 1) and same.host_slots == [0]
+
+
+def test_decode_session_keeps_the_next_chunk_on_the_stream():
+    """The graph session's order of events with a scripted graph: a chunk is enqueued once, the chunk after it goes
+    onto the stream as soon as the device says that a row is live and before the caller sees a token, nothing is
+    enqueued after every row has ended, and the cache learns how many tokens each slot was fed."""
+    from qwenforge_b200.engine.engine import _GraphSession
+    from qwenforge_b200.engine.graphs import CHUNK_STEPS
+
+    events = []
+
+    class ScriptedGraph:
+        """Two rows: row 0 runs 40 steps, row 1 ends after 5 (a stop token)."""
+        def __init__(self):
+            self.done = 0
+        def load(self, *state):
+            events.append("load")
+        def enqueue(self, n):
+            n = min(n, CHUNK_STEPS)
+            events.append(("enqueue", n))
+            self.pending = n
+            return n
+        def collect(self, n):
+            assert n == self.pending
+            tokens = [[100 + self.done + i, 200 + self.done + i if self.done + i < 5 else -1] for i in range(n)]
+            self.done += n
+            events.append(("collect", n))
+            return tokens, max(40 - self.done, 0), 0
+
+    class Cache:
+        lengths = {3: 10, 4: 7}
+        advanced = {3: 0, 4: 0}
+        def flush(self):
+            pass
+        def advance(self, slot, n):
+            self.advanced[slot] += n
+
+    class Decoder:
+        def get(self, rows, longest, sampler):
+            assert rows == 2 and longest == 10 + 40
+            return ScriptedGraph()
+
+    class Stepper:
+        cache, graph_decoder, sampler, model = Cache(), Decoder(), None, None
+
+    session = _GraphSession(Stepper(), [(3, 9, 0, 0, 40), (4, 8, 1, 0, 40)], (2,))
+    first = session.run(40)
+    assert events == ["load", ("enqueue", 32), ("collect", 32), ("enqueue", 8)]   # the next chunk is out before we look
+    assert len(first) == 32 and first[0] == [100, 200] and first[5] == [105, -1]
+    second = session.run(8)
+    assert events[4:] == [("collect", 8)] and len(second) == 8 and second[-1] == [139, -1]   # nothing after the end
+    assert session.in_flight == 0
+    assert Cache.advanced == {3: 40, 4: 5}
