@@ -80,6 +80,13 @@ class DecodeGraph:
             want_rows=arange[:rows].clone(), err=model.err, dtype=model.dtype, attention=model.attention,
             decode_scratch=ops.DecodeScratch(device))  # the graph's own: its addresses are baked into the capture
         self.sample_scratch = ops.SampleScratch()
+        # Where the embedding is a plain lookup, the kernel that advances the rows' state also embeds their next tokens,
+        # and a step starts at its first layer.
+        lookup = getattr(model.embedding, "lookup_table", None)
+        self.table = lookup() if lookup is not None else None
+        if self.table is not None:
+            self.ctx.embedded = torch.zeros((rows, self.table.shape[1]), dtype=torch.float32, device=device)
+            self.ticket = torch.zeros(1, **i32)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
         self.last_logits: Optional[torch.Tensor] = None  # float32 [rows, vocab] of the newest replayed step
@@ -88,8 +95,13 @@ class DecodeGraph:
         logits = self.model.forward(self.ctx, self.cache)
         self.last_logits = logits  # inside a capture this is the graph's own buffer: every replay refills it
         self.sampler(logits, self.seq_ids, self.steps, out=self.sampled, scratch=self.sample_scratch)
-        ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
-                           self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor)
+        if self.table is not None:
+            ops.decode_advance_embed(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
+                                     self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor, self.table,
+                                     self.ctx.embedded, self.ticket, self.model.err)
+        else:
+            ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.slots, self.steps, self.budgets,
+                               self.stop_ids, MAX_STOP_IDS, self.out_tokens, self.cursor)
 
     def load(self, slots, tokens, positions, steps, budgets, seq_ids, stop_ids) -> None:
         """Set the rows' state (rows beyond the given ones are padding)."""
@@ -105,6 +117,8 @@ class DecodeGraph:
         self.seq_ids.copy_(torch.tensor(list(seq_ids) + [0] * pad, dtype=torch.int64).to(self.seq_ids.device))
         stops = list(stop_ids)[:MAX_STOP_IDS]
         self.stop_ids.copy_(torch.tensor(stops + [-1] * (MAX_STOP_IDS - len(stops)), dtype=torch.int32))
+        if self.table is not None:   # the first step's rows; every later step's come from the step before it
+            ops.embed_gather(self.token_ids, self.table, self.ctx.embedded, self.model.err)
 
     def capture(self) -> None:
         """Two eager steps on a side stream (they size every scratch buffer), then the capture. The rows are all

@@ -119,7 +119,7 @@ class Model:
     def forward(self, ctx: StepContext, cache: SequenceCache) -> Optional[torch.Tensor]:
         """Run the schedule over the context's tokens; logits of ctx.want_rows (None if nothing is wanted)."""
         ctx.step_memo = {}
-        hidden = self.embedding.forward(ctx.token_ids, ctx)
+        hidden = ctx.embedded if ctx.embedded is not None else self.embedding.forward(ctx.token_ids, ctx)
         delta = None
         if self.observer is not None:
             self.observer(0, hidden, None)
@@ -131,7 +131,14 @@ class Model:
                 self.observer(index + 1, hidden, delta)
         if ctx.want_rows is None:
             return None
-        rows = torch.empty((ctx.want_rows.numel(), hidden.shape[1]), dtype=torch.float32, device=hidden.device)
+        shape = (ctx.want_rows.numel(), hidden.shape[1])
+        rms = self.final_norm.fused_rms()
+        if rms is not None and (delta is None or delta.dtype == rms[0].dtype):
+            # the wanted rows are gathered and normalised by one kernel
+            normed = torch.empty(shape, dtype=rms[0].dtype, device=hidden.device)
+            ops.gather_rows_norm(hidden, delta, ctx.want_rows, rms[0], rms[1], normed, ctx.err)
+            return self.head.forward(normed)
+        rows = torch.empty(shape, dtype=torch.float32, device=hidden.device)
         ops.gather_rows(hidden, delta, ctx.want_rows, rows, ctx.err)
         return self.head.forward(self.final_norm.forward(rows, None))
 

@@ -35,6 +35,9 @@ class StepContext:
     # token's index in its sequence (positions on several axes, token types). `tok_pos` stays the index that
     # orders the cache and the causal mask.
     extras: Optional[dict] = None
+    # the step's tokens already embedded into the float32 stream [T, W] (a decode graph's state kernel leaves the next
+    # step's rows there); the model then starts at its first layer
+    embedded: Optional[torch.Tensor] = None
     # what the parts of one step share: the model empties it before every run of its schedule; a part keeps there
     # what it works out once per step for all layers of its kind (key: a tuple that starts with the part's own name)
     step_memo: Optional[dict] = None

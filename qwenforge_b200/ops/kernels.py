@@ -144,6 +144,26 @@ def gather_rows(hidden: torch.Tensor, delta: Optional[torch.Tensor], rows: torch
                                            _I(rows.numel()), _I(n_in), _I(width), _ptr(err), _stream()), "gather_rows")
 
 
+def gather_rows_norm(hidden: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, weight: torch.Tensor,
+                     eps: float, out: torch.Tensor, err: torch.Tensor) -> None:
+    """out[r] = rmsnorm(hidden[rows[r]] + delta[rows[r]]) * weight, the sums in float32; delta may be None. hidden float32
+    [T, W]; delta, weight and out share a dtype."""
+    _dev("hidden", hidden, torch.float32)
+    _dev("rows", rows, torch.int32)
+    _dev("weight", weight)
+    _dev("out", out, weight.dtype)
+    n_in, width = hidden.shape
+    if delta is not None:
+        _dev("delta", delta, weight.dtype)
+        if delta.shape != hidden.shape:
+            raise KernelError("gather_rows_norm: delta and hidden differ in shape")
+    if out.shape != (rows.numel(), width) or weight.numel() != width:
+        raise KernelError("gather_rows_norm: out must be [rows, width], weight [width]")
+    _check(library("embed").qf_gather_rows_norm(_I(_is_bf16(weight.dtype)), _ptr(hidden), _ptr(delta), _ptr(rows),
+                                                _ptr(weight), _ptr(out), _I(rows.numel()), _I(n_in), _I(width), _F(eps),
+                                                _ptr(err), _stream()), "gather_rows_norm")
+
+
 def add_rms_norm(hidden: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                  out: torch.Tensor) -> None:
     """hidden += delta (if given); out = rmsnorm(hidden) * weight. hidden float32 [R, W]; out, weight, delta share a dtype."""
@@ -496,6 +516,30 @@ def decode_advance(sampled: torch.Tensor, token_ids: torch.Tensor, tok_pos: torc
     _check(library("decode_state").qf_decode_advance(
         _ptr(sampled), _ptr(token_ids), _ptr(tok_pos), _ptr(slots), _ptr(steps), _ptr(budgets), _ptr(stop_ids),
         _I(n_stop), _ptr(out_tokens), _ptr(cursor), _I(out_tokens.shape[0]), _I(n), _stream()), "decode_advance")
+
+
+def decode_advance_embed(sampled: torch.Tensor, token_ids: torch.Tensor, tok_pos: torch.Tensor, slots: torch.Tensor,
+                         steps: torch.Tensor, budgets: torch.Tensor, stop_ids: torch.Tensor, n_stop: int,
+                         out_tokens: torch.Tensor, cursor: torch.Tensor, table: torch.Tensor, hidden: torch.Tensor,
+                         ticket: torch.Tensor, err: torch.Tensor) -> None:
+    """`decode_advance`, and the next step's embedding with it: hidden[r] = float32(table[the row's next input token]).
+    `ticket` is one int32 that is zero before the first call."""
+    for name, t in (("sampled", sampled), ("token_ids", token_ids), ("tok_pos", tok_pos), ("slots", slots),
+                    ("steps", steps), ("budgets", budgets), ("stop_ids", stop_ids), ("out_tokens", out_tokens),
+                    ("cursor", cursor), ("ticket", ticket)):
+        _dev(name, t, torch.int32)
+    _dev("table", table)
+    _dev("hidden", hidden, torch.float32)
+    n = token_ids.numel()
+    if out_tokens.dim() != 2 or out_tokens.shape[1] != n or n_stop > stop_ids.numel():
+        raise KernelError("decode_advance_embed: out_tokens must be [max_steps, rows]; n_stop within stop_ids")
+    if table.dim() != 2 or hidden.shape != (n, table.shape[1]):
+        raise KernelError("decode_advance_embed: hidden must be [rows, width of the table]")
+    _check(library("decode_state").qf_decode_advance_embed(
+        _ptr(sampled), _ptr(token_ids), _ptr(tok_pos), _ptr(slots), _ptr(steps), _ptr(budgets), _ptr(stop_ids),
+        _I(n_stop), _ptr(out_tokens), _ptr(cursor), _I(out_tokens.shape[0]), _I(n), _I(_is_bf16(table.dtype)),
+        _ptr(table), _I(table.shape[0]), _I(table.shape[1]), _ptr(hidden), _ptr(ticket), _ptr(err), _stream()),
+        "decode_advance_embed")
 
 
 # ---------------------------------------------------------------------------------------------- fused skinny products

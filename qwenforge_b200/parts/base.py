@@ -91,6 +91,17 @@ class Part:
         return []
 
 
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
+        """The float32 residual stream [T, width] of the step's token ids."""
+        raise NotImplementedError
+
+    def lookup_table(self):
+        """The table [vocab, width] if this embedding is a plain row lookup (row id -> stream row, nothing added or
+        scaled), which the kernel that advances a decode graph's state may then do for the next step; else None."""
+        return None
+
+
 class Norm(Part):
     def forward(self, hidden: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         raise NotImplementedError

@@ -5,11 +5,11 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, TensorSpec
+from .base import Embedding, Part, TensorSpec
 from .registry import register_part
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """params: vocab_size, width. tensors: weight [vocab_size, width]."""
 
     def __init__(self, spec):
@@ -26,6 +26,9 @@ class TokenEmbedding(Part):
 
     def bind(self, tensors, dtype, device):
         self.weight = tensors[self.file_name("weight")]
+
+    def lookup_table(self):
+        return self.weight
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         hidden = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)

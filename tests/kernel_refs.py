@@ -29,6 +29,14 @@ def gather_rows(hidden, delta, rows, out, err):
     out.copy_(picked)
 
 
+def gather_rows_norm(hidden, delta, rows, weight, eps, out, err):
+    picked = hidden[rows.long()]
+    if delta is not None:
+        picked = picked + delta[rows.long()].to(torch.float32)
+    x = _f(picked)
+    out.copy_((x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * _f(weight)).to(out.dtype))
+
+
 def add_rms_norm(hidden, delta, weight, eps, out):
     if delta is not None:
         hidden += delta.to(torch.float32)
@@ -138,6 +146,6 @@ def sample(logits, temperature, seed, seq_ids, steps, out, scratch=None):
         out[r] = token
 
 
-ALL = dict(embed_gather=embed_gather, gather_rows=gather_rows, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
+ALL = dict(embed_gather=embed_gather, gather_rows=gather_rows, gather_rows_norm=gather_rows_norm, add_rms_norm=add_rms_norm, gemm_f32=gemm_f32,
            linear=linear, rope_cache_write=rope_cache_write, attention_generic=attention_generic, swiglu=swiglu,
            sample=sample)

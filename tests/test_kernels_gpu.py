@@ -61,6 +61,67 @@ def test_gather_rows(ops, dtype):
     assert int(e) & ops.ERR_ROW_RANGE
 
 
+@pytest.mark.parametrize("embed", [False, True])
+def test_decode_advance(ops, embed):
+    """The kernel that ends a decode step, alone and with the next step's embedding, against the rules written out:
+    a live row records its token, feeds it back, moves on one position and one step, and retires on a stop token or a
+    spent budget; a retired row records -1 and keeps its state; a full chunk records nothing and moves nothing."""
+    rows, width, vocab, chunk = 5, 24, 40, 3
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    token_ids, tok_pos, slots = i32([1, 2, 3, 4, 5]), i32([10, 20, 30, 40, 50]), i32([0, -1, 2, 3, 4])
+    steps, budgets, stop_ids = i32([1, 1, 1, 1, 6]), i32([9, 9, 9, 2, 9]), i32([33, 7, -1, -1])
+    out_tokens, cursor = torch.full((chunk, rows), -7, dtype=torch.int32, device=DEV), i32([0])
+    g = torch.Generator().manual_seed(4)
+    table = torch.randn(vocab, width, generator=g).to(torch.bfloat16).to(DEV)
+    hidden, ticket, e = torch.zeros(rows, width, device=DEV), i32([0]), err_word()
+    def step(sampled):
+        if embed:
+            ops.decode_advance_embed(i32(sampled), token_ids, tok_pos, slots, steps, budgets, stop_ids, 4, out_tokens, cursor,
+                                     table, hidden, ticket, e)
+        else:
+            ops.decode_advance(i32(sampled), token_ids, tok_pos, slots, steps, budgets, stop_ids, 4, out_tokens, cursor)
+    step([11, 12, 7, 14, 15])      # row 2 draws a stop token, row 3 spends its budget, row 1 is a padding entry
+    assert out_tokens[0].tolist() == [11, -1, 7, 14, 15] and int(cursor) == 1
+    assert token_ids.tolist() == [11, 2, 7, 14, 15] and tok_pos.tolist() == [11, 20, 31, 41, 51]
+    assert slots.tolist() == [0, -1, -1, -1, 4] and steps.tolist() == [2, 1, 2, 2, 7]
+    step([21, 22, 23, 24, 33])     # the retired rows stay as they are; row 4 draws the other stop token
+    assert out_tokens[1].tolist() == [21, -1, -1, -1, 33] and int(cursor) == 2
+    assert token_ids.tolist() == [21, 2, 7, 14, 33] and slots.tolist() == [0, -1, -1, -1, -1]
+    step([31, 0, 0, 0, 0])
+    assert out_tokens[2].tolist() == [31, -1, -1, -1, -1] and int(cursor) == 3 and tok_pos[0].item() == 13
+    step([39, 0, 0, 0, 0])         # the chunk is full: nothing is recorded, nothing moves
+    assert int(cursor) == 3 and token_ids[0].item() == 31 and tok_pos[0].item() == 13 and steps[0].item() == 4
+    if embed:
+        assert int(ticket) == 0 and int(e) == 0
+        assert torch.equal(hidden, table[token_ids.long()].float())
+        token_ids[1] = vocab       # a token outside the table: zeros and the error word, as the embedding kernel does
+        cursor.zero_()
+        step([1, 1, 1, 1, 1])
+        assert int(e) & ops.ERR_TOKEN_RANGE and float(hidden[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,eps", [(70, 1e-6), (896, 1e-5), (3584, 1e-6), (1, 1e-3), (5001, 1e-6)])
+def test_gather_rows_norm(ops, dtype, width, eps):
+    g = torch.Generator().manual_seed(3)
+    hidden = (torch.randn(19, width, generator=g) * 3).to(DEV)
+    delta = torch.randn(19, width, generator=g).to(dtype).to(DEV)
+    weight = (1 + 0.1 * torch.randn(width, generator=g)).to(dtype).to(DEV)
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32, device=DEV)
+    e = err_word()
+    for d in (delta, None):
+        out = torch.empty(4, width, dtype=dtype, device=DEV)
+        want = torch.empty(4, width, dtype=torch.float32, device=DEV)
+        ops.gather_rows_norm(hidden, d, rows, weight, eps, out, e)
+        ref.gather_rows_norm(hidden, d, rows, weight, eps, want, None)
+        assert int(e) == 0
+        assert max_err(out, want) <= (2e-2 if dtype == torch.bfloat16 else 2e-5) * max(1.0, float(want.abs().max()))
+        assert torch.equal(out[2], out[3])
+    rows[1] = 19
+    ops.gather_rows_norm(hidden, None, rows, weight, eps, out, e)
+    assert int(e) & ops.ERR_ROW_RANGE and float(out[1].float().abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,width,eps", [(5, 64, 1e-6), (3, 120, 1e-5), (17, 896, 1e-6), (2, 3584, 1e-6), (1, 1, 1e-3)])
 def test_add_rms_norm(ops, dtype, rows, width, eps):
