@@ -4,6 +4,7 @@
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+    grid_chain_entry();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / inter, c = i % inter;
         const float g = Num<T>::to_f(gu[t * 2 * inter + c]);
@@ -14,6 +15,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 // Eight bf16 elements per thread (16-byte loads and stores); needs inter % 8 == 0 and 16-byte aligned rows.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter, size_t total8) {
+    grid_chain_entry();
     const int per_row = inter / 8;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / per_row, c = (i % per_row) * 8;
@@ -37,13 +39,14 @@ QF_EXPORT int qf_swiglu(int is_bf16, const void* gu, void* out, int rows, int in
     if (total == 0) return 0;
     const size_t most = (size_t)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 16;  // blocks that a grid-stride loop is given
     const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+    int code;
     if (is_bf16 && inter % 8 == 0 && ((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
         const size_t total8 = total / 8;
         const int b8 = (int)((total8 + 255) / 256 < most ? (total8 + 255) / 256 : most);
-        swiglu_bf16x8_kernel<<<b8, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total8);
+        code = (int)launch_pdl(swiglu_bf16x8_kernel, dim3(b8), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, inter, total8);
     } else if (is_bf16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total);
+        code = (int)launch_pdl(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, (bf16*)out, inter, total);
     else
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, inter, total);
-    return (int)cudaGetLastError();
+        code = (int)launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, total);
+    return code;
 }

@@ -107,6 +107,13 @@ static inline int qf_sm_count() {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The first statement of a small kernel that has nothing to do before its input is there: it lets the kernel after it
+// start its own preamble (weight copies, page-table walks) at once, then waits for the kernel before it.
+__device__ __forceinline__ void grid_chain_entry() {
+    grid_launch_dependents();
+    grid_dependency_wait();
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                      Args... args) {

@@ -10,6 +10,7 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       const int* __restrict__ budgets, const int* __restrict__ stop_ids, int n_stop,
                                       int* __restrict__ out_tokens, int* __restrict__ cursor, int max_steps,
                                       int n_rows) {
+    grid_chain_entry();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     const int at = cursor[0];
     if (r < n_rows && at < max_steps) {
@@ -38,9 +39,8 @@ QF_EXPORT int qf_decode_advance(const int* sampled, int* token_ids, int* tok_pos
                                 int max_steps, int n_rows, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (n_rows > 1024) return (int)cudaErrorInvalidValue;  // one block, so that the cursor has one writer
-    decode_advance_kernel<<<1, n_rows, 0, stream>>>(sampled, token_ids, tok_pos, slots, steps, budgets, stop_ids,
+    return (int)launch_pdl(decode_advance_kernel, dim3(1), dim3(n_rows), 0, stream, sampled, token_ids, tok_pos, slots, steps, budgets, stop_ids,
                                                     n_stop, out_tokens, cursor, max_steps, n_rows);
-    return (int)cudaGetLastError();
 }
 
 // The same step of the rows' state, and the NEXT step's first kernel with it: a block per row updates the row as above
@@ -54,6 +54,7 @@ decode_advance_embed_kernel(const int* __restrict__ sampled, int* __restrict__ t
                             const int* __restrict__ stop_ids, int n_stop, int* __restrict__ out_tokens,
                             int* __restrict__ cursor, int max_steps, const T* __restrict__ table, int vocab, int width,
                             float* __restrict__ hidden, int* __restrict__ ticket, int* err) {
+    grid_chain_entry();
     __shared__ int next_s, at_s;
     const int r = blockIdx.x, n_rows = gridDim.x;
     if (threadIdx.x == 0) {
@@ -102,13 +103,14 @@ QF_EXPORT int qf_decode_advance_embed(const int* sampled, int* token_ids, int* t
                                       int max_steps, int n_rows, int is_bf16, const void* table, int vocab, int width,
                                       float* hidden, int* ticket, int* err, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    int code;
     if (is_bf16)
-        decode_advance_embed_kernel<bf16><<<n_rows, 128, 0, stream>>>(sampled, token_ids, tok_pos, slots, steps, budgets,
+        code = (int)launch_pdl(decode_advance_embed_kernel<bf16>, dim3(n_rows), dim3(128), 0, stream, sampled, token_ids, tok_pos, slots, steps, budgets,
                                                                      stop_ids, n_stop, out_tokens, cursor, max_steps,
                                                                      (const bf16*)table, vocab, width, hidden, ticket, err);
     else
-        decode_advance_embed_kernel<float><<<n_rows, 128, 0, stream>>>(sampled, token_ids, tok_pos, slots, steps, budgets,
+        code = (int)launch_pdl(decode_advance_embed_kernel<float>, dim3(n_rows), dim3(128), 0, stream, sampled, token_ids, tok_pos, slots, steps, budgets,
                                                                       stop_ids, n_stop, out_tokens, cursor, max_steps,
                                                                       (const float*)table, vocab, width, hidden, ticket, err);
-    return (int)cudaGetLastError();
+    return code;
 }

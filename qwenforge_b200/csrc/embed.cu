@@ -5,6 +5,7 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                     int vocab, int width, int* err) {
+    grid_chain_entry();
     const int t = blockIdx.x;
     int id = ids[t];
     const bool bad = id < 0 || id >= vocab;
@@ -22,6 +23,7 @@ template <typename T>
 __global__ void gather_rows_kernel(const float* __restrict__ hidden, const T* __restrict__ delta,
                                    const int* __restrict__ rows, float* __restrict__ out, int n_rows_in, int width,
                                    int* err) {
+    grid_chain_entry();
     const int r = blockIdx.x;
     int src = rows[r];
     const bool bad = src < 0 || src >= n_rows_in;
@@ -88,16 +90,14 @@ template <typename T>
 static int embed_launch(const int* ids, const void* table, float* out, int n_tokens, int vocab, int width, int* err,
                         cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    embed_gather_kernel<T><<<n_tokens, 256, 0, stream>>>(ids, (const T*)table, out, vocab, width, err);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(embed_gather_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, ids, (const T*)table, out, vocab, width, err);
 }
 
 template <typename T>
 static int gather_launch(const float* hidden, const void* delta, const int* rows, float* out, int n_out, int n_in,
                          int width, int* err, cudaStream_t stream) {
     if (n_out <= 0) return 0;
-    gather_rows_kernel<T><<<n_out, 256, 0, stream>>>(hidden, (const T*)delta, rows, out, n_in, width, err);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(gather_rows_kernel<T>, dim3(n_out), dim3(256), 0, stream, hidden, (const T*)delta, rows, out, n_in, width, err);
 }
 
 QF_EXPORT int qf_embed_gather(int is_bf16, const int* ids, const void* table, float* out, int n_tokens, int vocab,

@@ -6,6 +6,7 @@
 template <typename T>
 __global__ void add_rms_norm_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                     const T* __restrict__ weight, T* __restrict__ out, int width, float eps) {
+    grid_chain_entry();
     __shared__ float scratch[33];
     float* h = hidden + (size_t)blockIdx.x * width;
     const T* d = delta ? delta + (size_t)blockIdx.x * width : nullptr;
@@ -51,6 +52,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 add_rms_norm_vec_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const T* __restrict__ weight,
                         T* __restrict__ out, int width, float eps) {
+    grid_chain_entry();
     __shared__ float scratch[33];
     float* h = hidden + (size_t)blockIdx.x * width;
     const T* d = delta ? delta + (size_t)blockIdx.x * width : nullptr;
@@ -96,6 +98,7 @@ template <typename T>
 __global__ void __launch_bounds__(NW_ROWS * 32)
 add_rms_norm_warp_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const T* __restrict__ weight,
                          T* __restrict__ out, int rows, int width, float eps) {
+    grid_chain_entry();
     const int row = blockIdx.x * NW_ROWS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     float* h = hidden + (size_t)row * width;
@@ -139,16 +142,13 @@ static int launch(float* hidden, const void* delta, const void* weight, void* ou
     if (rows <= 0) return 0;
     const uintptr_t align = (uintptr_t)hidden | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out;
     if (width % 4 == 0 && width <= 4 * 32 * NW_MAX && align % 16 == 0) {
-        add_rms_norm_warp_kernel<T><<<(rows + NW_ROWS - 1) / NW_ROWS, NW_ROWS * 32, 0, stream>>>(hidden, (const T*)delta, (const T*)weight,
+        return (int)launch_pdl(add_rms_norm_warp_kernel<T>, dim3((rows + NW_ROWS - 1) / NW_ROWS), dim3(NW_ROWS * 32), 0, stream, hidden, (const T*)delta, (const T*)weight,
                                                                                               (T*)out, rows, width, eps);
-        return (int)cudaGetLastError();
     }
     if (width % 4 == 0 && width <= 4096 && align % 16 == 0) {
-        add_rms_norm_vec_kernel<T><<<rows, 256, 0, stream>>>(hidden, (const T*)delta, (const T*)weight, (T*)out, width, eps);
-        return (int)cudaGetLastError();
+        return (int)launch_pdl(add_rms_norm_vec_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)delta, (const T*)weight, (T*)out, width, eps);
     }
-    add_rms_norm_kernel<T><<<rows, 256, 0, stream>>>(hidden, (const T*)delta, (const T*)weight, (T*)out, width, eps);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(add_rms_norm_kernel<T>, dim3(rows), dim3(256), 0, stream, hidden, (const T*)delta, (const T*)weight, (T*)out, width, eps);
 }
 
 QF_EXPORT int qf_add_rms_norm(int is_bf16, float* hidden, const void* delta, const void* weight, void* out, int rows,
@@ -158,6 +158,7 @@ QF_EXPORT int qf_add_rms_norm(int is_bf16, float* hidden, const void* delta, con
 }
 
 template <typename T> __global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ delta, long long n) {
+    grid_chain_entry();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
         hidden[i] += Num<T>::to_f(delta[i]);
 }
@@ -168,8 +169,6 @@ QF_EXPORT int qf_residual_add(int is_bf16, float* hidden, const void* delta, lon
     const long long most = (long long)(qf_sm_count() > 0 ? qf_sm_count() : 1) * 8;
     const int blocks = (int)((n + 255) / 256 < most ? (n + 255) / 256 : most);
     if (is_bf16)
-        residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(hidden, (const bf16*)delta, n);
-    else
-        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(hidden, (const float*)delta, n);
-    return (int)cudaGetLastError();
+        return (int)launch_pdl(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, hidden, (const bf16*)delta, n);
+    return (int)launch_pdl(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, hidden, (const float*)delta, n);
 }

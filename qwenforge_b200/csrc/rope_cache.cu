@@ -16,6 +16,7 @@ __global__ void rope_cache_kernel(const T* __restrict__ qkv, const T* __restrict
                                   const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                   const float* __restrict__ inv_freq, int rot_dim, int n_heads, T* __restrict__ q_out,
                                   KvSite<T> site, int write_cache, int* err) {
+    grid_chain_entry();
     const int t = blockIdx.x;
     const int D = site.head_dim, KVH = site.kv_heads;
     const int pos = tok_pos[t];
@@ -91,6 +92,7 @@ rope_cache_vec_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bia
                       const int* __restrict__ tok_pos, const int* __restrict__ slots, const float* __restrict__ inv_freq,
                       int rot_dim, int n_heads, bf16* __restrict__ q_out, KvSite<bf16> site, int write_cache, int n_tokens,
                       int* err) {
+    grid_chain_entry();
     const int D = site.head_dim, KVH = site.kv_heads;
     const int half = rot_dim / 2, pass = D - rot_dim;
     const int q_width = n_heads * D, kv_width = KVH * D;
@@ -198,14 +200,12 @@ static int launch(const void* qkv, const void* bias, int qkv_stride, const int* 
     if (!inv_freq) rot_dim = 0;
     if (sizeof(T) == 2 && head_dim % 16 == 0 && rot_dim % 16 == 0 && qkv_stride % 8 == 0 && head_dim <= 256 &&
         ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)base | (uintptr_t)bias) % 16 == 0 && page_elems % 8 == 0) {
-        rope_cache_vec_kernel<<<(n_tokens + RC_TOKENS - 1) / RC_TOKENS, 256, 0, stream>>>(
+        return (int)launch_pdl(rope_cache_vec_kernel, dim3((n_tokens + RC_TOKENS - 1) / RC_TOKENS), dim3(256), 0, stream,
             (const bf16*)qkv, (const bf16*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq, rot_dim, n_heads, (bf16*)q_out,
             KvSite<bf16>{(bf16*)base, table, page_elems, table_stride, kv_heads, head_dim}, write_cache, n_tokens, err);
-        return (int)cudaGetLastError();
     }
-    rope_cache_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)qkv, (const T*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq,
+    return (int)launch_pdl(rope_cache_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)qkv, (const T*)bias, qkv_stride, tok_seq, tok_pos, slots, inv_freq,
                                                        rot_dim, n_heads, (T*)q_out, site, write_cache, err);
-    return (int)cudaGetLastError();
 }
 
 // qkv: [n_tokens][qkv_stride] with q heads, then k heads, then v heads; bias: [(n_heads + 2 kv_heads) * head_dim] or null; q_out: [n_tokens][n_heads * head_dim].
@@ -226,6 +226,7 @@ QF_EXPORT int qf_rope_cache_write(int is_bf16, const void* qkv, const void* bias
 // the same expression as in the kernels above.
 __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, int n_tokens, int half,
                                   float2* __restrict__ table) {
+    grid_chain_entry();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens * half) return;
     float sn, c;
@@ -236,6 +237,5 @@ __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* 
 QF_EXPORT int qf_rope_table(const int* tok_pos, const float* inv_freq, int n_tokens, int half, void* table, cudaStream_t stream) {
     if (n_tokens <= 0 || half <= 0) return 0;
     const long long total = (long long)n_tokens * half;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(tok_pos, inv_freq, n_tokens, half, (float2*)table);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, tok_pos, inv_freq, n_tokens, half, (float2*)table);
 }

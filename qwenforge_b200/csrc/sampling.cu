@@ -34,6 +34,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, long long row_stride,
               unsigned long long seed, const long long* __restrict__ seq_ids, const int* __restrict__ steps,
               int* __restrict__ out, int chunks, float* __restrict__ part_v, int* __restrict__ part_i,
               int* __restrict__ counters) {
+    grid_chain_entry();
     __shared__ float best_v[8];
     __shared__ int best_i[8];
     __shared__ int ticket;
@@ -157,7 +158,6 @@ QF_EXPORT int qf_sample(const float* logits, int rows, int vocab, long long row_
                         float* part_v, int* part_i, int* counters, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (chunks < 1 || (chunks > 1 && (!part_v || !part_i || !counters))) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, row_stride, temperature, seed, seq_ids, steps, out,
+    return (int)launch_pdl(sample_kernel, dim3(chunks, rows), dim3(256), 0, stream, logits, vocab, row_stride, temperature, seed, seq_ids, steps, out,
                                                           chunks, part_v, part_i, counters);
-    return (int)cudaGetLastError();
 }
