@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(PF_THREADS * G, (D <= 64 ? 4 : 2) / G)
 prefill_flash_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const int* __restrict__ cu_q,
                      const int* __restrict__ tok_pos, const int* __restrict__ slots, KvSite<bf16> site, int n_heads,
                      int n_seqs, int n_tiles, int wave, float scale_log2, int window, int* err) {
+    grid_chain_entry();
     constexpr int LD = D + 8;
     constexpr int KS = D / 16;
     constexpr int NT = D / 8;
@@ -286,10 +287,9 @@ static int launch_groups(const void* q, void* out, const int* cu_q, const int* t
     const int n_tiles = (max_q_len + PF_BM - 1) / PF_BM;
     const long long blocks = (long long)n_tiles * n_heads * n_seqs;
     if (blocks > 0x7fffffffll) return (int)cudaErrorInvalidValue;
-    prefill_flash_kernel<D, G><<<(unsigned)blocks, PF_THREADS * G, smem, stream>>>((const bf16*)q, (bf16*)out, cu_q, tok_pos, slots, site,
-                                                                                     n_heads, n_seqs, n_tiles, qf_sm_count(),
-                                                                                     scale * 1.4426950408889634f, window, err);
-    return (int)cudaGetLastError();
+    return (int)launch_pdl(prefill_flash_kernel<D, G>, dim3((unsigned)blocks), dim3(PF_THREADS * G), smem, stream, (const bf16*)q,
+                           (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs, n_tiles, qf_sm_count(),
+                           scale * 1.4426950408889634f, window, err);
 }
 
 template <int D>

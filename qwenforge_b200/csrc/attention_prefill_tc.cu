@@ -58,6 +58,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     float* merge_s = reinterpret_cast<float*>(smem);
     constexpr int STRIDE = SPLIT ? 2 : 1;               // this block takes every STRIDE-th page of the tile
     const int rank = SPLIT ? (int)(blockIdx.x & 1) : 0;
+    // Launched as a programmatic dependent: what a block works out and sets up before its first copy (its tile, the
+    // barriers, its tensor memory) runs under the tail of the kernel before, which wrote the queries and the new keys
+    // and values; they are read, and the output written, only after the wait.
+    grid_launch_dependents();
     __shared__ __align__(8) uint64_t bar_q, bar_kv[2], bar_s, bar_sfree, bar_pv, bar_p;
     __shared__ uint32_t tmem_base_s;
 
@@ -80,6 +84,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int kvh = head / (n_heads / site.kv_heads);
     bf16* out_row = out + (size_t)(q_begin + row0 + t) * q_width + (size_t)head * D;
     if (slot < 0) {  // padding entry: defined output, no cache access
+        grid_dependency_wait();
         if (t < n_rows)
             for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(out_row + c) = make_uint4(0, 0, 0, 0);
         return;
@@ -106,6 +111,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    grid_dependency_wait();
     const uint32_t tmem = tmem_base_s;
     bool timed_out = false;
     float m_ref = QF_NEG_BIG, l_run = 0.f;  // row threads: the reference maximum of the exponentials, and their sum
@@ -387,13 +393,15 @@ static int launch_variant(const CUtensorMap& q_map, const CUtensorMap& kv_map, v
     config.blockDim = dim3(TA_THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     config.attrs = attr;
-    config.numAttrs = SPLIT ? 1 : 0;
+    config.numAttrs = SPLIT ? 2 : 1;
     return (int)cudaLaunchKernelEx(&config, kernel, q_map, kv_map, (bf16*)out, cu_q, tok_pos, slots, site, n_heads, n_seqs,
                                    row_tiles, SPLIT ? qf_sm_count() / 2 : qf_sm_count(), scale * 1.4426950408889634f, window, err);
 }
