@@ -422,6 +422,17 @@ def fold_project_takes(rows: int, weight: torch.Tensor, hidden: torch.Tensor, n_
         _I(rows), _I(weight.shape[0]), _I(weight.stride(0)), _I(n_heads), _I(head_dim), _ptr(weight), _ptr(hidden)))
 
 
+FOLD_PROJECT_MAX_REDUCTIONS = 150_000
+
+
+def fold_project_pays(rows: int, weight: torch.Tensor) -> bool:
+    """Whether `fold_project` is the faster way for this projection. What it saves is the attention kernel's life after
+    its pages (about 3 microseconds); what it costs grows with the 16-byte reductions into the stream, rows x N / 4 from
+    each of its K / 32 blocks. Measured: 50,000 of them (8 rows, 896 x 896) gain 2.2 microseconds per layer, 524,000 (16
+    rows, 2048 x 2048) lose 1."""
+    return rows * weight.shape[0] * (weight.shape[1] // 32) // 4 <= FOLD_PROJECT_MAX_REDUCTIONS
+
+
 def fold_project(plan: torch.Tensor, scratch: DecodeScratch, weight: torch.Tensor, hidden: torch.Tensor, n_heads: int,
                  head_dim: int, n_splits: int) -> None:
     """hidden[r, :] += fold(the partial results of sequence r) @ weight^T, after `attention_decode(..., fold_later=True)`

@@ -178,7 +178,8 @@ class GqaAttention(Mixer):
             ops.rope_cache_write(ops.linear(x, self.qkv_weight), ctx.tok_seq, ctx.tok_pos, ctx.slots, inv_freq, rot_dim,
                                  self.n_heads, q, args, writes_cache, ctx.err, bias=self.qkv_bias_t)
         n_splits = self.decode_splits(ctx)
-        if o_way == "skinny" and n == ctx.n_seqs and ops.fold_project_takes(n, self.o_weight, hidden, self.n_heads, self.head_dim):
+        if (o_way == "skinny" and n == ctx.n_seqs and ops.fold_project_pays(n, self.o_weight)
+                and ops.fold_project_takes(n, self.o_weight, hidden, self.n_heads, self.head_dim)):
             # the attention kernel stops at its runs' partial results; the projection folds them on its way in
             ops.attention_decode(q, None, ctx.cu_q, ctx.tok_pos, ctx.slots, args, self.n_heads, ctx.n_seqs, self.scale,
                                  self.window, n_splits, ctx.decode_scratch, ctx.err, plan, fold_later=True)
